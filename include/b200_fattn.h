@@ -1,0 +1,251 @@
+/*
+ * b200_fattn.h — C-ABI of the B200-native fused attention path.
+ *
+ * This library implements exactly one operator of the CrispASR/ggml stack,
+ * GGML_OP_FLASH_ATTN_EXT, plus the two pieces of host plumbing that feed it
+ * (a KV-cache slab allocator and a per-GPU segment scheduler).  Every entry
+ * point is plain C: pointers, sizes and enums, no C++ or torch types.
+ *
+ * Tensor descriptors use ggml conventions throughout: ne[0] is the fastest
+ * dimension, nb[i] is the stride of dimension i in BYTES, nb[0] is the size of
+ * one element (or of one quantised block), `data` is a DEVICE pointer unless an
+ * entry point says otherwise.
+ *
+ * Operator contract (reference call sites: src/crispasr.cpp:2821,3220,3280;
+ * src/core/attention.h:478,572,992; src/core/fastconformer.h:933;
+ * src/core/cross_attn.h:148; src/canary.cpp:971,994):
+ *
+ *   Q    [hd,  Tq, H,   B]  F32 or F16, nb[0] == element size
+ *   K    [hd,  Lk, Hkv, Bk] F16, F32 or Q8_0 (34-byte blocks of 32), H % Hkv == 0, B % Bk == 0
+ *   V    [hdv, Lk, Hkv, Bk] same type as K (hdv == hd in this library)
+ *   mask [Lk,  Tq, 1|H, 1|B] F16 or NULL; 0 = attend, -inf = masked, any finite value = additive bias
+ *   dst  [hdv, H,  Tq,  B]  F32, contiguous
+ *
+ *   s[k]   = scale * sum_c Q[c,q,h,b] * K[c,k,h/(H/Hkv),b/(B/Bk)]
+ *   s[k]   = softcap * tanh(s[k] / softcap)                (only when logit_softcap != 0)
+ *   s[k]  += slope(h) * mask[k,q,h%mask.ne2,b%mask.ne3]    (slope == 1 when max_bias == 0)
+ *   dst[:,h,q,b] = sum_k softmax_k(s)[k] * V[:,k,...]      (fp32 softmax, fp32 accumulation)
+ *
+ * Q is rounded to F16 before the dot product (it is the tensor-core operand
+ * type); K/V quantised blocks are dequantised as fp32(d) * q.  A row whose keys
+ * are all masked yields zeros.
+ */
+#ifndef B200_FATTN_H
+#define B200_FATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200_API
+#else
+#define B200_API __attribute__((visibility("default")))
+#endif
+
+/* Numeric ids equal ggml's GGML_TYPE_* / gguf-py GGMLQuantizationType (F32=0, F16=1, Q8_0=8). */
+typedef enum b200_type {
+    B200_TYPE_F32 = 0,
+    B200_TYPE_F16 = 1,
+    B200_TYPE_Q8_0 = 8,
+} b200_type;
+
+/* Mirrors the fields of `struct ggml_tensor` the operator reads (data, type, ne, nb). */
+typedef struct b200_tensor {
+    void* data;
+    int32_t type; /* b200_type */
+    int32_t reserved;
+    int64_t ne[4];
+    uint64_t nb[4];
+} b200_tensor;
+
+/* op_params of ggml_flash_attn_ext(ctx, q, k, v, mask, scale, max_bias, logit_softcap)
+ * (+ ggml_flash_attn_ext_set_prec). prec_f32 is accepted and ignored: softmax and
+ * accumulation are always fp32. */
+typedef struct b200_fattn_params {
+    float scale;
+    float max_bias;
+    float logit_softcap;
+    int32_t prec_f32;
+} b200_fattn_params;
+
+/* Optional fused extensions. A NULL pointer or an all-zero struct is the plain ggml op. */
+typedef struct b200_fattn_ext {
+    /* FastConformer relative-position bias, replacing the materialised F16 mask that
+     * src/core/fastconformer.h:880-918 builds (MUL_MAT(R,Q_v) -> rel_shift -> scale -> cast F16):
+     *   bias[k,q,h] = f16( scale * sum_c q_v[c,q,h] * r[c, (Tq-1) + k - q, h] )
+     * q_v has the shape and type rules of Q; r is [hd, 2*Tq-1, H, 1|B] F16 or F32. Requires
+     * Lk == Tq. May be combined with `mask` (added after the bias) and kv_len. */
+    const b200_tensor* q_v;
+    const b200_tensor* r;
+    /* Implicit causal mask of src/voxtral.cpp:1187-1194: key k is masked iff k > n_past + q. */
+    int32_t causal;
+    int32_t n_past;
+    /* Device array [B] of valid key counts per batch entry (keys >= kv_len[b] are masked); NULL = Lk.
+     * Read on the device at run time, so a captured launch follows a growing cache. */
+    const int32_t* kv_len;
+    /* If non-zero the relative-position bias is NOT rounded to F16 (diagnostic; the reference rounds). */
+    int32_t relpos_bias_f32;
+    int32_t reserved;
+} b200_fattn_ext;
+
+/* Error codes (negative). 0 is success. Nothing in this library aborts or throws. */
+enum {
+    B200_OK = 0,
+    B200_E_NULL = -1,        /* a required pointer is NULL */
+    B200_E_TYPE = -2,        /* operand type not supported by the op contract */
+    B200_E_SHAPE = -3,       /* shapes disagree (head dims, Lk, GQA ratio, mask dims, dst dims) */
+    B200_E_STRIDE = -4,      /* nb[0] is not the element size, or a stride is not a multiple of it */
+    B200_E_ALIGN = -5,       /* base pointer alignment below what the element type needs */
+    B200_E_UNSUPPORTED = -6, /* legal ggml op that this library has no kernel for (e.g. head_dim 160) */
+    B200_E_WORKSPACE = -7,   /* workspace NULL or smaller than b200_fattn_workspace_bytes */
+    B200_E_CUDA = -8,        /* a CUDA runtime/driver call failed; see b200_last_cuda_error */
+    B200_E_NO_DEVICE = -9,   /* no CUDA device, or the device is not compute capability 10.x */
+    B200_E_LIMIT = -10,      /* a size exceeds a documented fixed limit of the entry point */
+    B200_E_STATE = -11,      /* object used in the wrong state (scheduler/allocator) */
+    B200_E_DEVICE_WAIT = -12 /* a bounded device-side wait ran out; reported via the status word */
+};
+
+/* Which kernel family a launch used (b200_fattn_plan / b200_last_kernel). */
+enum {
+    B200_KERNEL_NONE = 0,
+    B200_KERNEL_TILE_MMA = 1,   /* general tiled kernel, mma.sync tensor path, every operand form */
+    B200_KERNEL_DECODE_SPLIT = 2, /* split-KV streaming kernel for <=16 query rows per KV head + LSE merge */
+    B200_KERNEL_PREFILL_TC5 = 3 /* TMA + tcgen05.mma + TMEM prefill kernel (F16 K/V) */
+};
+
+/* Force a kernel family for A/B tests (B200_KERNEL_NONE restores automatic choice). Process-wide. */
+B200_API int b200_set_kernel_override(int kernel);
+
+B200_API const char* b200_strerror(int code);
+B200_API const char* b200_version(void);
+/* Text of the last CUDA error seen by the calling thread ("" if none). */
+B200_API const char* b200_last_cuda_error(void);
+
+/*
+ * b200_fattn_supports — replaces ggml_backend_dev_supports_op(dev, op) for
+ * GGML_OP_FLASH_ATTN_EXT (asked by the scheduler at src/crispasr.cpp:1977).
+ * Returns 1 if b200_fattn_launch will accept these operands, 0 if not; never
+ * touches the device. `why` (may be NULL) receives the negative code on refusal.
+ */
+B200_API int b200_fattn_supports(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                 const b200_tensor* mask, const b200_tensor* dst,
+                                 const b200_fattn_params* params, const b200_fattn_ext* ext, int* why);
+
+/*
+ * b200_fattn_plan — which kernel would run and how many KV splits it would use.
+ * Pure function of the descriptors. Returns 0 or a negative code.
+ */
+B200_API int b200_fattn_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                             const b200_tensor* mask, const b200_tensor* dst,
+                             const b200_fattn_params* params, const b200_fattn_ext* ext,
+                             int* kernel, int* n_splits);
+
+/*
+ * b200_fattn_workspace_bytes — scratch the launch needs (split-KV partial O/m/l).
+ * Mirrors ggml's per-op work buffer sizing (the reference sizes it inside
+ * ggml_backend_sched_alloc_graph, src/voxtral.cpp:1196-1198). May return 0 bytes.
+ */
+B200_API int b200_fattn_workspace_bytes(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                        const b200_tensor* mask, const b200_tensor* dst,
+                                        const b200_fattn_params* params, const b200_fattn_ext* ext,
+                                        size_t* bytes);
+
+/*
+ * b200_fattn_launch — replaces the backend's GGML_OP_FLASH_ATTN_EXT compute
+ * (reached through ggml_backend_sched_graph_compute, src/crispasr.cpp:273,
+ * src/parakeet.cpp:997, src/voxtral.cpp:1209).  Enqueues the kernels on
+ * `cuda_stream` (a cudaStream_t, NULL = legacy default stream) of the CURRENT
+ * device and returns without synchronising.  Allocates nothing; `workspace`
+ * must be a device buffer of at least b200_fattn_workspace_bytes (256-byte
+ * aligned) and may be NULL when that size is 0.  Returns 0 or a negative code.
+ */
+B200_API int b200_fattn_launch(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                               const b200_tensor* mask, const b200_tensor* dst,
+                               const b200_fattn_params* params, const b200_fattn_ext* ext,
+                               void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * b200_fattn_forward_host — the same operator for callers that hold HOST
+ * buffers, i.e. the ggml_backend_tensor_set -> graph_compute -> tensor_get
+ * round trip of src/voxtral.cpp:1196-1223 in one call.  All `data` pointers
+ * (and ext->kv_len) are host pointers; operands are staged through a per-thread
+ * device arena that grows on demand, copied in, computed and copied back, and
+ * the call returns after the result is in `dst->data`.
+ */
+B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                     const b200_tensor* mask, const b200_tensor* dst,
+                                     const b200_fattn_params* params, const b200_fattn_ext* ext);
+/* Frees the calling thread's staging arena of b200_fattn_forward_host. */
+B200_API void b200_host_arena_release(void);
+
+/* The kernel family the calling thread's most recent successful launch used. */
+B200_API int b200_last_kernel(void);
+
+/* ------------------------------------------------------------------------------------------
+ * KV-cache slabs.  Replaces the cache tensors of core_attn (layout (hd, max_ctx, n_kv, n_layers),
+ * src/core/attention.h:593-595) and whisper's kv_self / kv_cross buffers
+ * (src/crispasr.cpp:1471-1516): one contiguous, 1024-byte aligned slab per layer and per K/V,
+ * head-major rows, so that every (layer, kv-head) row range is a single flat byte range that
+ * TMA boxes (F16) or 128-bit streaming loads (Q8_0) can cover.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b200_kv_cache b200_kv_cache; /* opaque */
+
+typedef struct b200_kv_config {
+    int32_t type;     /* B200_TYPE_F16 or B200_TYPE_Q8_0 */
+    int32_t head_dim; /* 64 or 128 (multiple of 32) */
+    int32_t n_kv_heads;
+    int32_t n_layers;
+    int32_t max_ctx;  /* rows per (layer, head, stream) */
+    int32_t n_streams; /* independent sequences / beams sharing the geometry (ne[3]) */
+} b200_kv_config;
+
+/* Allocates 2 * n_layers slabs on the current device. Returns 0 or a negative code. */
+B200_API int b200_kv_create(const b200_kv_config* cfg, b200_kv_cache** out);
+B200_API void b200_kv_destroy(b200_kv_cache* kv);
+B200_API size_t b200_kv_bytes(const b200_kv_cache* kv);
+/* Fills K and V descriptors viewing rows [0, n_rows) of `layer` for all heads and streams
+ * (the view_3d of src/core/attention.h:887-895). */
+B200_API int b200_kv_view(const b200_kv_cache* kv, int layer, int64_t n_rows, b200_tensor* k, b200_tensor* v);
+/*
+ * b200_kv_append — replaces core_attn::kv_cache_write (src/core/attention.h:342-378) and the
+ * write branch at :840-867 (ggml_cpy for F16, ggml_set_rows for quantised caches): converts
+ * F32 rows k_new/v_new [hd, n_new, n_kv_heads, n_streams] (device, generic strides) to the cache
+ * type and stores them at rows pos[s] .. pos[s]+n_new-1 of each stream s (`pos` is a device
+ * array [n_streams], or NULL meaning `pos0` for all).  Asynchronous on `cuda_stream`.
+ */
+B200_API int b200_kv_append(b200_kv_cache* kv, int layer, const b200_tensor* k_new, const b200_tensor* v_new,
+                            const int32_t* pos, int32_t pos0, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Segment scheduler.  Replaces the `-p N` worker instances with an atomic next-slice cursor
+ * (examples/cli/crispasr_run.cpp:1882-1930) and whisper_full_parallel (src/crispasr.cpp:8755-8880)
+ * for the attention path: independent units (audio segments, beams groups, streams, utterances)
+ * are handed to one host worker thread per GPU; there is no inter-GPU exchange.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b200_sched b200_sched; /* opaque */
+
+/* Called on a worker thread with its device current: process unit `unit` on `cuda_stream`.
+ * Return 0, or non-zero to report failure (the unit is retried once on another worker, then
+ * recorded as failed — the deferred-retry rule of crispasr_run.cpp:1819-1844). */
+typedef int (*b200_unit_fn)(void* user, int device, int unit, void* cuda_stream);
+
+/* devices == NULL means devices 0..n_devices-1. n_devices == 0 builds a host-only scheduler
+ * (workers run without touching CUDA; used by CPU tests) with `n_host_workers` threads. */
+B200_API int b200_sched_create(const int* devices, int n_devices, int n_host_workers, b200_sched** out);
+B200_API void b200_sched_destroy(b200_sched* s);
+/* Runs units [0, n_units): a contiguous range per worker first, then stealing from the shared
+ * cursor.  Blocks until every unit has finished or failed twice.  `unit_device` (may be NULL,
+ * else [n_units]) receives the worker index that completed each unit, -1 for a failed unit.
+ * Returns the number of failed units (>= 0) or a negative code. */
+B200_API int b200_sched_run(b200_sched* s, int n_units, b200_unit_fn fn, void* user, int* unit_device);
+/* Static part of the partition: first unit and count owned by worker `w` of `n_workers`. */
+B200_API void b200_sched_partition(int n_units, int n_workers, int w, int* first, int* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_FATTN_H */
