@@ -1,0 +1,416 @@
+// fattn_api.cu — the C-ABI of include/b200_fattn.h for the attention operator: operand
+// validation (ggml shape rules, returned as codes, never asserts), kernel choice, workspace
+// sizing, launch, and the host-buffer round trip.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "fattn_common.cuh"
+#include "fattn_tc5.cuh"
+
+namespace b200 {
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+thread_local int g_last_kernel = B200_KERNEL_NONE;
+int g_override = B200_KERNEL_NONE;
+
+int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+    return B200_E_CUDA;
+}
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+    bool ok = false;
+};
+
+// Properties of the current device, cached per device ordinal.
+int device_info(DeviceInfo* out) {
+    static std::mutex mu;
+    static DeviceInfo cache[64];
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaGetDevice");
+        return B200_E_NO_DEVICE;
+    }
+    if (dev < 0 || dev >= 64) return B200_E_NO_DEVICE;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cache[dev].ok) {
+        int sm = 0, major = 0;
+        if ((e = cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+            (e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) {
+            cuda_fail(e, "cudaDeviceGetAttribute");
+            return B200_E_NO_DEVICE;
+        }
+        cache[dev].sm_count = sm;
+        cache[dev].cc_major = major;
+        cache[dev].ok = true;
+    }
+    *out = cache[dev];
+    return out->cc_major == 10 ? B200_OK : B200_E_NO_DEVICE;
+}
+
+size_t type_size(int t) {
+    switch (t) {
+        case B200_TYPE_F32: return 4;
+        case B200_TYPE_F16: return 2;
+        case B200_TYPE_Q8_0: return 34;
+        default: return 0;
+    }
+}
+
+bool is_vec16(const b200_tensor* t) {
+    return ((uintptr_t)t->data % 16 == 0) && t->nb[1] % 16 == 0 && t->nb[2] % 16 == 0 && t->nb[3] % 16 == 0;
+}
+
+View make_view(const b200_tensor* t) {
+    View v;
+    v.p = (const uint8_t*)t->data;
+    v.nb1 = (int64_t)t->nb[1];
+    v.nb2 = (int64_t)t->nb[2];
+    v.nb3 = (int64_t)t->nb[3];
+    v.type = t->type;
+    v.vec16 = is_vec16(t) ? 1 : 0;
+    return v;
+}
+
+// Type, nb[0], alignment and stride-granularity rules of one operand.
+int check_operand(const b200_tensor* t, bool allow_f32, bool allow_f16, bool allow_q8) {
+    if (!t->data) return B200_E_NULL;
+    const size_t es = type_size(t->type);
+    if (es == 0) return B200_E_TYPE;
+    if (t->type == B200_TYPE_F32 && !allow_f32) return B200_E_TYPE;
+    if (t->type == B200_TYPE_F16 && !allow_f16) return B200_E_TYPE;
+    if (t->type == B200_TYPE_Q8_0 && !allow_q8) return B200_E_TYPE;
+    if (t->nb[0] != es) return B200_E_STRIDE;
+    const size_t align = t->type == B200_TYPE_F32 ? 4 : 2;
+    if ((uintptr_t)t->data % align) return B200_E_ALIGN;
+    for (int i = 1; i < 4; i++)
+        if (t->nb[i] % align) return B200_E_STRIDE;
+    for (int i = 0; i < 4; i++)
+        if (t->ne[i] <= 0) return B200_E_SHAPE;
+    if (t->type == B200_TYPE_Q8_0 && t->ne[0] % 32) return B200_E_SHAPE;
+    return B200_OK;
+}
+
+struct Plan {
+    FattnArgs args;
+    int kernel;
+    size_t ws_bytes;
+};
+
+// Validates the operands against the op contract and fills the kernel argument block.
+// `need_device` = false keeps the call free of CUDA (supports / plan on a CPU-only host assume 148 SMs).
+int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, const b200_tensor* mask,
+              const b200_tensor* dst, const b200_fattn_params* p, const b200_fattn_ext* ext, bool need_device,
+              Plan* plan) {
+    if (!q || !k || !v || !dst || !p) return B200_E_NULL;
+    int rc;
+    if ((rc = check_operand(q, true, true, false))) return rc;
+    if ((rc = check_operand(k, true, true, true))) return rc;
+    if ((rc = check_operand(v, true, true, true))) return rc;
+    if ((rc = check_operand(dst, true, false, false))) return rc;
+    if (k->type != v->type) return B200_E_TYPE;
+
+    const int64_t hd = q->ne[0], Tq = q->ne[1], H = q->ne[2], B = q->ne[3];
+    const int64_t Lk = k->ne[1], Hkv = k->ne[2], Bk = k->ne[3];
+    if (k->ne[0] != hd || v->ne[0] != hd) return v->ne[0] != hd && k->ne[0] == hd ? B200_E_UNSUPPORTED : B200_E_SHAPE;
+    if (v->ne[1] != Lk || v->ne[2] != Hkv || v->ne[3] != Bk) return B200_E_SHAPE;
+    if (H % Hkv || B % Bk) return B200_E_SHAPE;
+    if (dst->ne[0] != hd || dst->ne[1] != H || dst->ne[2] != Tq || dst->ne[3] != B) return B200_E_SHAPE;
+    if (dst->nb[1] != (uint64_t)hd * 4 || dst->nb[2] != (uint64_t)hd * H * 4 ||
+        dst->nb[3] != (uint64_t)hd * H * Tq * 4)
+        return B200_E_STRIDE;
+    if (hd > 128) return B200_E_UNSUPPORTED;
+    if (Tq > INT32_MAX / 2 || Lk > INT32_MAX / 2 || H > 65535 || B > 65535) return B200_E_LIMIT;
+    if (!std::isfinite(p->scale) || !std::isfinite(p->max_bias) || !std::isfinite(p->logit_softcap))
+        return B200_E_SHAPE;
+
+    FattnArgs& a = plan->args;
+    memset(&a, 0, sizeof(a));
+    if (mask) {
+        if ((rc = check_operand(mask, false, true, false))) return rc;
+        if (mask->ne[0] != Lk || mask->ne[1] < Tq) return B200_E_SHAPE;
+        if (mask->ne[2] != 1 && mask->ne[2] != H) return B200_E_SHAPE;
+        if (mask->ne[3] != 1 && mask->ne[3] != B) return B200_E_SHAPE;
+        a.mask = make_view(mask);
+        a.mask_ne2 = (int)mask->ne[2];
+        a.mask_ne3 = (int)mask->ne[3];
+        a.has_mask = 1;
+    } else {
+        a.mask_ne2 = a.mask_ne3 = 1;
+    }
+    a.q = make_view(q);
+    a.k = make_view(k);
+    a.v = make_view(v);
+    a.dst = (float*)dst->data;
+    a.hd = (int)hd, a.Tq = (int)Tq, a.H = (int)H, a.B = (int)B;
+    a.Lk = (int)Lk, a.Hkv = (int)Hkv, a.gqa = (int)(H / Hkv), a.bq = (int)(B / Bk);
+    a.relscale = p->scale;
+    a.softcap = p->logit_softcap;
+    a.scale = p->logit_softcap != 0.0f ? p->scale / p->logit_softcap : p->scale;
+    if (p->max_bias > 0.0f) {
+        a.n2 = 1 << (int)floorf(log2f((float)H));
+        a.m0 = powf(2.0f, -p->max_bias / (float)a.n2);
+        a.m1 = powf(2.0f, -(p->max_bias / 2.0f) / (float)a.n2);
+    }
+    if (ext) {
+        if ((ext->q_v != nullptr) != (ext->r != nullptr)) return B200_E_NULL;
+        if (ext->q_v) {
+            const b200_tensor *qv = ext->q_v, *r = ext->r;
+            if ((rc = check_operand(qv, true, true, false))) return rc;
+            if ((rc = check_operand(r, true, true, false))) return rc;
+            for (int i = 0; i < 4; i++)
+                if (qv->ne[i] != q->ne[i]) return B200_E_SHAPE;
+            if (Lk != Tq) return B200_E_SHAPE;
+            if (r->ne[0] != hd || r->ne[1] != 2 * Tq - 1 || r->ne[2] != H) return B200_E_SHAPE;
+            if (r->ne[3] != 1 && r->ne[3] != B) return B200_E_SHAPE;
+            a.qv = make_view(qv);
+            a.r = make_view(r);
+            a.r_ne3 = (int)r->ne[3];
+            a.relpos = 1;
+            a.relpos_f32 = ext->relpos_bias_f32 ? 1 : 0;
+        }
+        a.causal = ext->causal ? 1 : 0;
+        a.n_past = ext->n_past;
+        a.kv_len = ext->kv_len;
+    }
+
+    int sm_count = 148;
+    if (need_device) {
+        DeviceInfo di;
+        if ((rc = device_info(&di))) return rc;
+        sm_count = di.sm_count;
+    }
+
+    // kernel choice
+    int kernel = B200_KERNEL_TILE_MMA;
+    const bool decode_ok = !a.relpos && Tq * (H / Hkv) <= 16;
+    const bool tc5_ok = tc5_supported(a);
+    if (decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
+    else if (tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
+    if (g_override == B200_KERNEL_TILE_MMA) kernel = B200_KERNEL_TILE_MMA;
+    if (g_override == B200_KERNEL_DECODE_SPLIT && decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
+    if (g_override == B200_KERNEL_PREFILL_TC5 && tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
+    plan->kernel = kernel;
+    a.n_splits = 1;
+    plan->ws_bytes = 0;
+    if (kernel == B200_KERNEL_DECODE_SPLIT) {
+        a.n_splits = decode_split_choose(a.B, a.Hkv, a.Lk, sm_count);
+        plan->ws_bytes = decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
+    }
+    return B200_OK;
+}
+
+int do_launch(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st) {
+    FattnArgs& a = plan.args;
+    if (plan.ws_bytes) {
+        if (!workspace || ws_bytes < plan.ws_bytes || (uintptr_t)workspace % 256) return B200_E_WORKSPACE;
+        const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
+        const size_t units = (size_t)a.B * a.Hkv * a.n_splits;
+        const size_t o = ((units * 16 * hdp * sizeof(float) + 255) / 256) * 256;
+        a.ws_o = (float*)workspace;
+        a.ws_ml = (float*)((uint8_t*)workspace + o);
+    }
+    int e = 0;
+    switch (plan.kernel) {
+        case B200_KERNEL_DECODE_SPLIT: e = launch_decode_split(a, st); break;
+        case B200_KERNEL_PREFILL_TC5: {
+            const int rc = launch_prefill_tc5(a, st, g_cuda_err, sizeof(g_cuda_err));
+            if (rc != B200_OK) return rc;
+            break;
+        }
+        default: e = launch_tile_mma(a, st); break;
+    }
+    if (e != 0) return cuda_fail((cudaError_t)e, "kernel launch");
+    g_last_kernel = plan.kernel;
+    return B200_OK;
+}
+
+// ---- per-thread staging arena of the host-buffer entry point ----
+struct Arena {
+    uint8_t* base = nullptr;
+    size_t cap = 0;
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    ~Arena() { release(); }
+    void release() {
+        if (base) cudaFree(base);
+        if (stream) cudaStreamDestroy(stream);
+        base = nullptr, cap = 0, stream = nullptr, device = -1;
+    }
+};
+thread_local Arena g_arena;
+
+// Bytes spanned by a strided tensor (offset of the last element + one element/block).
+size_t span_bytes(const b200_tensor* t) {
+    size_t last = 0;
+    const int64_t n0 = t->type == B200_TYPE_Q8_0 ? t->ne[0] / 32 : t->ne[0];
+    last += (size_t)(n0 - 1) * t->nb[0];
+    for (int i = 1; i < 4; i++) last += (size_t)(t->ne[i] - 1) * t->nb[i];
+    return last + t->nb[0];
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+B200_API const char* b200_version(void) { return "b200-fattn 0.1 (sm_100a)"; }
+
+B200_API const char* b200_strerror(int code) {
+    switch (code) {
+        case B200_OK: return "ok";
+        case B200_E_NULL: return "a required pointer is NULL";
+        case B200_E_TYPE: return "operand type not allowed by the flash_attn_ext contract";
+        case B200_E_SHAPE: return "operand shapes disagree";
+        case B200_E_STRIDE: return "stride not allowed (nb[0] must be the element size; dst must be contiguous)";
+        case B200_E_ALIGN: return "operand base pointer is misaligned for its type";
+        case B200_E_UNSUPPORTED: return "legal operator form without a kernel in this library";
+        case B200_E_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+        case B200_E_CUDA: return "CUDA call failed (see b200_last_cuda_error)";
+        case B200_E_NO_DEVICE: return "no sm_100 CUDA device is current";
+        case B200_E_LIMIT: return "size exceeds a fixed limit of this entry point";
+        case B200_E_STATE: return "object used in the wrong state";
+        case B200_E_DEVICE_WAIT: return "a bounded device-side wait ran out";
+        default: return "unknown error code";
+    }
+}
+
+B200_API const char* b200_last_cuda_error(void) { return g_cuda_err; }
+B200_API int b200_last_kernel(void) { return g_last_kernel; }
+
+B200_API int b200_set_kernel_override(int kernel) {
+    if (kernel < B200_KERNEL_NONE || kernel > B200_KERNEL_PREFILL_TC5) return B200_E_SHAPE;
+    g_override = kernel;
+    return B200_OK;
+}
+
+B200_API int b200_fattn_supports(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                 const b200_tensor* mask, const b200_tensor* dst, const b200_fattn_params* params,
+                                 const b200_fattn_ext* ext, int* why) {
+    Plan plan;
+    const int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
+    if (why) *why = rc;
+    return rc == B200_OK ? 1 : 0;
+}
+
+B200_API int b200_fattn_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                             const b200_tensor* mask, const b200_tensor* dst, const b200_fattn_params* params,
+                             const b200_fattn_ext* ext, int* kernel, int* n_splits) {
+    Plan plan;
+    const int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
+    if (rc != B200_OK) return rc;
+    if (kernel) *kernel = plan.kernel;
+    if (n_splits) *n_splits = plan.args.n_splits;
+    return B200_OK;
+}
+
+B200_API int b200_fattn_workspace_bytes(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                        const b200_tensor* mask, const b200_tensor* dst,
+                                        const b200_fattn_params* params, const b200_fattn_ext* ext, size_t* bytes) {
+    if (!bytes) return B200_E_NULL;
+    Plan plan;
+    const int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
+    if (rc != B200_OK) return rc;
+    *bytes = plan.ws_bytes;
+    return B200_OK;
+}
+
+B200_API int b200_fattn_launch(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                               const b200_tensor* mask, const b200_tensor* dst, const b200_fattn_params* params,
+                               const b200_fattn_ext* ext, void* workspace, size_t workspace_bytes,
+                               void* cuda_stream) {
+    Plan plan;
+    // The split count must match b200_fattn_workspace_bytes, which assumes 148 SMs; the device is
+    // only queried to refuse non-sm_100 parts.
+    int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
+    if (rc != B200_OK) return rc;
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    return do_launch(plan, workspace, workspace_bytes, (cudaStream_t)cuda_stream);
+}
+
+B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                     const b200_tensor* mask, const b200_tensor* dst,
+                                     const b200_fattn_params* params, const b200_fattn_ext* ext) {
+    Plan plan;
+    int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
+    if (rc != B200_OK) return rc;
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    int dev = 0;
+    cudaGetDevice(&dev);
+
+    // operands to stage: q, k, v, [mask], [q_v, r], [kv_len]; then dst and workspace
+    const b200_tensor* in[6] = {q, k, v, mask, ext ? ext->q_v : nullptr, ext ? ext->r : nullptr};
+    size_t off[6], total = 0;
+    auto bump = [&](size_t n) {
+        const size_t o = total;
+        total += (n + 255) / 256 * 256;
+        return o;
+    };
+    for (int i = 0; i < 6; i++) off[i] = in[i] ? bump(span_bytes(in[i])) : 0;
+    const size_t kvlen_off = (ext && ext->kv_len) ? bump((size_t)q->ne[3] * 4) : 0;
+    const size_t dst_bytes = (size_t)dst->ne[0] * dst->ne[1] * dst->ne[2] * dst->ne[3] * 4;
+    const size_t dst_off = bump(dst_bytes);
+    const size_t ws_off = bump(plan.ws_bytes);
+
+    Arena& ar = g_arena;
+    cudaError_t e;
+    if (ar.device != dev) ar.release();
+    if (!ar.stream) {
+        if ((e = cudaStreamCreateWithFlags(&ar.stream, cudaStreamNonBlocking)) != cudaSuccess)
+            return cuda_fail(e, "cudaStreamCreate");
+        ar.device = dev;
+    }
+    if (ar.cap < total) {
+        if (ar.base) cudaFree(ar.base);
+        ar.base = nullptr, ar.cap = 0;
+        if ((e = cudaMalloc((void**)&ar.base, total)) != cudaSuccess) return cuda_fail(e, "cudaMalloc(arena)");
+        ar.cap = total;
+    }
+    b200_tensor dt[6];
+    for (int i = 0; i < 6; i++) {
+        if (!in[i]) continue;
+        dt[i] = *in[i];
+        dt[i].data = ar.base + off[i];
+        if ((e = cudaMemcpyAsync(dt[i].data, in[i]->data, span_bytes(in[i]), cudaMemcpyHostToDevice, ar.stream)) !=
+            cudaSuccess)
+            return cuda_fail(e, "cudaMemcpyAsync(H2D)");
+    }
+    b200_fattn_ext dext;
+    memset(&dext, 0, sizeof(dext));
+    if (ext) {
+        dext = *ext;
+        dext.q_v = ext->q_v ? &dt[4] : nullptr;
+        dext.r = ext->r ? &dt[5] : nullptr;
+        if (ext->kv_len) {
+            if ((e = cudaMemcpyAsync(ar.base + kvlen_off, ext->kv_len, (size_t)q->ne[3] * 4, cudaMemcpyHostToDevice,
+                                     ar.stream)) != cudaSuccess)
+                return cuda_fail(e, "cudaMemcpyAsync(kv_len)");
+            dext.kv_len = (const int32_t*)(ar.base + kvlen_off);
+        }
+    }
+    b200_tensor ddst = *dst;
+    ddst.data = ar.base + dst_off;
+    rc = make_plan(&dt[0], &dt[1], &dt[2], mask ? &dt[3] : nullptr, &ddst, params, ext ? &dext : nullptr, false, &plan);
+    if (rc != B200_OK) return rc;
+    rc = do_launch(plan, plan.ws_bytes ? ar.base + ws_off : nullptr, plan.ws_bytes, ar.stream);
+    if (rc != B200_OK) return rc;
+    if ((e = cudaMemcpyAsync(dst->data, ddst.data, dst_bytes, cudaMemcpyDeviceToHost, ar.stream)) != cudaSuccess)
+        return cuda_fail(e, "cudaMemcpyAsync(D2H)");
+    if ((e = cudaStreamSynchronize(ar.stream)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return B200_OK;
+}
+
+B200_API void b200_host_arena_release(void) { g_arena.release(); }
+
+}  // extern "C"

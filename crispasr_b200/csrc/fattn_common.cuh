@@ -1,0 +1,62 @@
+// fattn_common.cuh — argument block shared by the attention kernels, and small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200_fattn.h"
+
+namespace b200 {
+
+// One operand as the kernels see it: base pointer plus byte strides of dims 1..3.
+struct View {
+    const uint8_t* p;
+    int64_t nb1, nb2, nb3;
+    int32_t type;    // b200_type
+    int32_t vec16;   // base and all strides are multiples of 16 bytes: 128-bit loads are legal
+};
+
+struct FattnArgs {
+    View q, k, v, mask, qv, r;
+    float* dst;  // contiguous [hd, H, Tq, B]
+    int32_t hd, Tq, H, B;
+    int32_t Lk, Hkv, gqa, bq;  // bq = B / Bk
+    int32_t mask_ne2, mask_ne3, r_ne3, has_mask;
+    float scale;      // already divided by softcap when softcap != 0
+    float softcap;    // 0 = off
+    float relscale;   // the caller's scale (bias uses it undivided)
+    float m0, m1;     // ALiBi bases
+    int32_t n2;       // ALiBi head split; 0 = max_bias off
+    int32_t causal, n_past;
+    const int32_t* kv_len;
+    int32_t relpos, relpos_f32;
+    // split-KV
+    int32_t n_splits;
+    float* ws_o;   // [B][Hkv][n_splits][16][hd]
+    float* ws_ml;  // [B][Hkv][n_splits][16][2]
+};
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float alibi_slope(const FattnArgs& a, int h) {
+    if (a.n2 == 0) return 1.0f;
+    return h < a.n2 ? powf(a.m0, (float)(h + 1)) : powf(a.m1, (float)(2 * (h - a.n2) + 1));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Launchers implemented per kernel family; each returns a cudaError_t-compatible int (0 = ok).
+int launch_tile_mma(const FattnArgs& a, cudaStream_t st);
+int launch_decode_split(const FattnArgs& a, cudaStream_t st);
+size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd);
+int decode_split_choose(int B, int Hkv, int Lk, int sm_count);
+
+}  // namespace b200

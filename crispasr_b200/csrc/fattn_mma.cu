@@ -1,0 +1,610 @@
+// fattn_mma.cu — the general tiled attention kernel and the split-KV decode kernel.
+//
+// Both kernels stage K/V tiles as fp16 in XOR-swizzled shared memory (F16 rows are copied,
+// F32 rows are rounded, Q8_0 blocks are dequantised as fp32(d)*q and rounded to fp16), run
+// Q.K^T and P.V on the mma.sync m16n8k16 tensor path with fp32 accumulators and keep the
+// online softmax in fp32 registers.
+//
+//  * fattn_tile_mma_kernel  — 64 query rows x 64 keys per step, one (q-tile, head, batch) per
+//    CTA.  Covers every operand form of the op contract: explicit F16 mask ([Lk,Tq,1|H,1|B]),
+//    implicit causal mask, per-batch kv_len, softcap, ALiBi, GQA, generic strides, and the
+//    fused FastConformer relative-position bias (per-warp band GEMM + diagonal gather).
+//  * fattn_decode_split_kernel — for <= 16 query rows per KV head (single-token decode with
+//    GQA, beams sharing a cross-attention cache): one (split, kv-head, batch) per CTA streams its
+//    share of the keys once, the four warps own 16-key slices of each tile, and partial
+//    (O, m, l) go to the workspace; fattn_merge_kernel combines splits with a log-sum-exp merge.
+#include "fattn_common.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kThreads = 128;
+
+template <int HD>
+__device__ __forceinline__ int swz(int row, int ch) {
+    if (HD >= 64) return ch ^ (row & 7);
+    return ch ^ ((row >> 1) & 3);
+}
+
+template <int HD>
+__device__ __forceinline__ uint32_t tile_addr(const __half* sm, int row, int ch) {
+    return smem_u32(sm) + (uint32_t)((row * (HD / 8) + swz<HD>(row, ch)) * 16);
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Eight consecutive elements [c0, c0+8) of one row, converted to fp16 (zero beyond hd).
+__device__ __forceinline__ uint4 load8_as_half(const uint8_t* rowp, int type, int c0, int hd, bool vec16) {
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (c0 >= hd) return out;
+    if (type == B200_TYPE_F16) {
+        if (vec16 && c0 + 8 <= hd) return __ldg(reinterpret_cast<const uint4*>(rowp + 2 * c0));
+        __half tmp[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            tmp[i] = (c0 + i < hd) ? *reinterpret_cast<const __half*>(rowp + 2 * (c0 + i)) : __float2half(0.0f);
+        out = *reinterpret_cast<uint4*>(tmp);
+    } else if (type == B200_TYPE_F32) {
+        float f[8];
+        if (vec16 && c0 + 8 <= hd) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(rowp + 4 * c0));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(rowp + 4 * c0 + 16));
+            f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                f[i] = (c0 + i < hd) ? *reinterpret_cast<const float*>(rowp + 4 * (c0 + i)) : 0.0f;
+        }
+        out.x = pack_half2(f[0], f[1]);
+        out.y = pack_half2(f[2], f[3]);
+        out.z = pack_half2(f[4], f[5]);
+        out.w = pack_half2(f[6], f[7]);
+    } else {  // Q8_0: 34-byte blocks {fp16 d; int8 q[32]}; rows are only 2-byte aligned
+        const uint8_t* blk = rowp + 34 * (c0 >> 5);
+        const float d = __half2float(*reinterpret_cast<const __half*>(blk));
+        const uint16_t* qs = reinterpret_cast<const uint16_t*>(blk + 2 + (c0 & 31));
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint16_t w = qs[i];
+            f[2 * i] = d * (float)(int8_t)(w & 0xFF);
+            f[2 * i + 1] = d * (float)(int8_t)(w >> 8);
+        }
+        out.x = pack_half2(f[0], f[1]);
+        out.y = pack_half2(f[2], f[3]);
+        out.z = pack_half2(f[4], f[5]);
+        out.w = pack_half2(f[6], f[7]);
+    }
+    return out;
+}
+
+// Rows [row0, row0+NROWS) of a strided 2-D slice -> swizzled fp16 tile; rows outside
+// [row_lo, row_hi) are zero-filled.
+template <int HD, int NROWS>
+__device__ __forceinline__ void load_tile(__half* sm, const uint8_t* base, int64_t nb1, int type, bool vec16,
+                                          int row0, int row_lo, int row_hi, int hd, int tid) {
+    constexpr int CPR = HD / 8;
+    for (int idx = tid; idx < NROWS * CPR; idx += kThreads) {
+        const int row = idx / CPR, ch = idx % CPR;
+        const int grow = row0 + row;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (grow >= row_lo && grow < row_hi) val = load8_as_half(base + (int64_t)grow * nb1, type, ch * 8, hd, vec16);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * CPR + swz<HD>(row, ch)) * 16) = val;
+    }
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    return v;
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+__device__ __forceinline__ int clamp_len(const FattnArgs& a, int b) {
+    if (!a.kv_len) return a.Lk;
+    const int v = a.kv_len[b];
+    return v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
+}
+
+// ------------------------------------------------------------------------------------------
+// General tiled kernel
+// ------------------------------------------------------------------------------------------
+constexpr int kXStride = 88;  // floats per row of the per-warp bias band buffer (80 used)
+
+template <int HD, bool RELPOS>
+__global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArgs a) {
+    constexpr int BM = 64, BN = 64;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __half* sQ = reinterpret_cast<__half*>(smem_raw);
+    __half* sK = sQ + BM * HD;
+    __half* sV = sK + BN * HD;
+    __half* sQv = sV + BN * HD;                             // RELPOS only
+    __half* sR = sQv + BM * HD;                             // RELPOS only, 128 rows
+    float* sX = reinterpret_cast<float*>(sR + 128 * HD);    // RELPOS only, [4][16][kXStride]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int q0 = blockIdx.x * BM, h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / a.gqa, bk = b / a.bq;
+    const float ninf = -INFINITY;
+
+    load_tile<HD, BM>(sQ, a.q.p + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.nb1, a.q.type, a.q.vec16, q0, 0,
+                      a.Tq, a.hd, tid);
+    if (RELPOS)
+        load_tile<HD, BM>(sQv, a.qv.p + (int64_t)h * a.qv.nb2 + (int64_t)b * a.qv.nb3, a.qv.nb1, a.qv.type,
+                          a.qv.vec16, q0, 0, a.Tq, a.hd, tid);
+
+    const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
+    const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
+    const uint8_t* rbase = RELPOS ? a.r.p + (int64_t)h * a.r.nb2 + (int64_t)(a.r_ne3 > 1 ? b : 0) * a.r.nb3 : nullptr;
+    const uint8_t* mbase =
+        a.has_mask ? a.mask.p + (int64_t)(h % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
+                   : nullptr;
+
+    const int len_b = clamp_len(a, b);
+    int kmax = len_b;
+    if (a.causal) {
+        const int last_q = min(q0 + BM, a.Tq) - 1;
+        kmax = min(kmax, a.n_past + last_q + 1);
+    }
+    const float slope = alibi_slope(a, h);
+
+    float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+    for (int k0 = 0; k0 < kmax; k0 += BN) {
+        __syncthreads();
+        load_tile<HD, BN>(sK, kbase, a.k.nb1, a.k.type, a.k.vec16, k0, 0, len_b, a.hd, tid);
+        load_tile<HD, BN>(sV, vbase, a.v.nb1, a.v.type, a.v.vec16, k0, 0, len_b, a.hd, tid);
+        if (RELPOS)
+            load_tile<HD, 128>(sR, rbase, a.r.nb1, a.r.type, a.r.vec16, a.Tq - 1 + k0 - q0 - 63, 0, 2 * a.Tq - 1,
+                               a.hd, tid);
+        __syncthreads();
+
+        float s[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t af[4];
+            ldsm_x4(af, tile_addr<HD>(sQ, warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+            for (int np = 0; np < BN / 16; np++) {
+                uint32_t bf[4];
+                ldsm_x4(bf, tile_addr<HD>(sK, np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+                mma16816(s[2 * np], af, bf[0], bf[1]);
+                mma16816(s[2 * np + 1], af, bf[2], bf[3]);
+            }
+        }
+
+        float* xw = sX + warp * 16 * kXStride;
+        if (RELPOS) {
+            // Band GEMM of this warp: X[i][jj] = Q_v[16w+i] . R[rb0 + jj], jj in [0,80), where
+            // rb0 = (Tq-1) + k0 - (q0+16w+15) is local row 16*(3-w) of the 128-row R tile;
+            // the bias of (row i, key j) is X[i][j + 15 - i].
+            float x[10][4];
+#pragma unroll
+            for (int i = 0; i < 10; i++) x[i][0] = x[i][1] = x[i][2] = x[i][3] = 0.0f;
+            const int rrow0 = 16 * (3 - warp);
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ks++) {
+                uint32_t af[4];
+                ldsm_x4(af, tile_addr<HD>(sQv, warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+                for (int np = 0; np < 5; np++) {
+                    uint32_t bf[4];
+                    ldsm_x4(bf, tile_addr<HD>(sR, rrow0 + np * 16 + (lane & 7) + ((lane >> 4) << 3),
+                                              ks * 2 + ((lane >> 3) & 1)));
+                    mma16816(x[2 * np], af, bf[0], bf[1]);
+                    mma16816(x[2 * np + 1], af, bf[2], bf[3]);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 10; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float val = x[nt][e] * a.relscale;
+                    if (!a.relpos_f32) val = __half2float(__float2half_rn(val));
+                    xw[(g + ((e >> 1) << 3)) * kXStride + nt * 8 + 2 * t + (e & 1)] = val;
+                }
+            __syncwarp();
+        }
+
+        // scale, softcap, bias, mask, bounds; then to the log2 domain
+        float rmax[2] = {ninf, ninf};
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = g + ((e >> 1) << 3);
+                const int j = nt * 8 + 2 * t + (e & 1);
+                const int iq = q0 + warp * 16 + i, ik = k0 + j;
+                float val = s[nt][e] * a.scale;
+                if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
+                if (RELPOS) val += xw[i * kXStride + j + 15 - i];
+                const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + iq);
+                if (mbase && valid && iq < a.Tq)
+                    val += slope * __half2float(*reinterpret_cast<const __half*>(mbase + (int64_t)iq * a.mask.nb1 +
+                                                                                 (int64_t)ik * 2));
+                val = valid ? val * kLog2e : ninf;
+                s[nt][e] = val;
+                rmax[e >> 1] = fmaxf(rmax[e >> 1], val);
+            }
+
+        float alpha[2], muse[2];
+#pragma unroll
+        for (int rI = 0; rI < 2; rI++) {
+            const float mnew = fmaxf(m_run[rI], quad_max(rmax[rI]));
+            muse[rI] = mnew == ninf ? 0.0f : mnew;
+            alpha[rI] = exp2f(m_run[rI] - muse[rI]);
+            m_run[rI] = mnew;
+            l_run[rI] *= alpha[rI];
+        }
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = exp2f(s[nt][e] - muse[e >> 1]);
+                s[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+            o[i][0] *= alpha[0];
+            o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1];
+            o[i][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; kk++) {
+            uint32_t pf[4];
+            pf[0] = pack_half2(s[2 * kk][0], s[2 * kk][1]);
+            pf[1] = pack_half2(s[2 * kk][2], s[2 * kk][3]);
+            pf[2] = pack_half2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pf[3] = pack_half2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < HD / 16; np++) {
+                uint32_t bf[4];
+                ldsm_x4_t(bf, tile_addr<HD>(sV, kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
+                mma16816(o[2 * np], pf, bf[0], bf[1]);
+                mma16816(o[2 * np + 1], pf, bf[2], bf[3]);
+            }
+        }
+    }
+
+    const float l0 = quad_sum(l_run[0]), l1 = quad_sum(l_run[1]);
+    const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+#pragma unroll
+    for (int rI = 0; rI < 2; rI++) {
+        const int iq = q0 + warp * 16 + g + rI * 8;
+        if (iq >= a.Tq) continue;
+        float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * a.hd;
+        const float inv = rI ? inv1 : inv0;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; nt++) {
+            const int c = nt * 8 + 2 * t;
+            if (c < a.hd) out[c] = o[nt][2 * rI] * inv;
+            if (c + 1 < a.hd) out[c + 1] = o[nt][2 * rI + 1] * inv;
+        }
+    }
+}
+
+template <int HD, bool RELPOS>
+int launch_tile_t(const FattnArgs& a, cudaStream_t st) {
+    size_t smem = (size_t)(64 + 64 + 64) * HD * sizeof(__half);
+    if (RELPOS) smem += (size_t)(64 + 128) * HD * sizeof(__half) + 4 * 16 * kXStride * sizeof(float);
+    auto kern = fattn_tile_mma_kernel<HD, RELPOS>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((a.Tq + 63) / 64, a.H, a.B);
+    kern<<<grid, kThreads, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// Split-KV decode kernel
+// ------------------------------------------------------------------------------------------
+constexpr int kDecRows = 16;
+constexpr int kDecBN = 64;
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const FattnArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __half* sQ = reinterpret_cast<__half*>(smem_raw);      // [16][HD]
+    __half* sK = sQ + kDecRows * HD;                        // [64][HD]
+    __half* sV = sK + kDecBN * HD;                          // [64][HD]
+    float* sO = reinterpret_cast<float*>(sK);               // [16][HD] fp32, reused after the key loop
+    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int bk = b / a.bq;
+    const int R = a.Tq * a.gqa;  // <= 16; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
+    const float ninf = -INFINITY;
+
+    // Q rows (tiny): one 8-element chunk per loop step
+    for (int idx = tid; idx < kDecRows * (HD / 8); idx += kThreads) {
+        const int rr = idx / (HD / 8), ch = idx % (HD / 8);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < R) {
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
+                                a.q.type, ch * 8, a.hd, a.q.vec16);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, ch)) * 16) = val;
+    }
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) ldsm_x4(qf[ks], tile_addr<HD>(sQ, lane & 15, ks * 2 + (lane >> 4)));
+
+    const int len_b = clamp_len(a, b);
+    int kmax = len_b;
+    if (a.causal) kmax = min(kmax, a.n_past + a.Tq);
+    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
+    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
+
+    const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
+    const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
+
+    // per-thread row metadata for rows g and g+8
+    int row_iq[2], row_h[2];
+    float row_slope[2];
+    const uint8_t* row_mask[2];
+#pragma unroll
+    for (int rI = 0; rI < 2; rI++) {
+        const int rr = g + rI * 8;
+        row_iq[rI] = rr / a.gqa;
+        row_h[rI] = hk * a.gqa + rr % a.gqa;
+        row_slope[rI] = alibi_slope(a, row_h[rI]);
+        row_mask[rI] = (a.has_mask && rr < R)
+                           ? a.mask.p + (int64_t)row_iq[rI] * a.mask.nb1 +
+                                 (int64_t)(row_h[rI] % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
+                           : nullptr;
+    }
+
+    float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+    for (int tile = tile_lo; tile < tile_hi; tile++) {
+        const int k0 = tile * kDecBN;
+        __syncthreads();
+        load_tile<HD, kDecBN>(sK, kbase, a.k.nb1, a.k.type, a.k.vec16, k0, 0, len_b, a.hd, tid);
+        load_tile<HD, kDecBN>(sV, vbase, a.v.nb1, a.v.type, a.v.vec16, k0, 0, len_b, a.hd, tid);
+        __syncthreads();
+
+        // this warp's 16 keys: k0 + 16*warp ..
+        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t bf[4];
+            ldsm_x4(bf, tile_addr<HD>(sK, warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+            mma16816(s[0], qf[ks], bf[0], bf[1]);
+            mma16816(s[1], qf[ks], bf[2], bf[3]);
+        }
+        float rmax[2] = {ninf, ninf};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int rI = e >> 1;
+                const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
+                float val = s[nt][e] * a.scale;
+                if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
+                const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + row_iq[rI]);
+                if (row_mask[rI] && valid)
+                    val += row_slope[rI] * __half2float(*reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2));
+                val = valid ? val * kLog2e : ninf;
+                s[nt][e] = val;
+                rmax[rI] = fmaxf(rmax[rI], val);
+            }
+        float alpha[2], muse[2];
+#pragma unroll
+        for (int rI = 0; rI < 2; rI++) {
+            const float mnew = fmaxf(m_run[rI], quad_max(rmax[rI]));
+            muse[rI] = mnew == ninf ? 0.0f : mnew;
+            alpha[rI] = exp2f(m_run[rI] - muse[rI]);
+            m_run[rI] = mnew;
+            l_run[rI] *= alpha[rI];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = exp2f(s[nt][e] - muse[e >> 1]);
+                s[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+        uint32_t pf[4];
+        pf[0] = pack_half2(s[0][0], s[0][1]);
+        pf[1] = pack_half2(s[0][2], s[0][3]);
+        pf[2] = pack_half2(s[1][0], s[1][1]);
+        pf[3] = pack_half2(s[1][2], s[1][3]);
+#pragma unroll
+        for (int np = 0; np < HD / 16; np++) {
+            o[2 * np][0] *= alpha[0], o[2 * np][1] *= alpha[0], o[2 * np][2] *= alpha[1], o[2 * np][3] *= alpha[1];
+            o[2 * np + 1][0] *= alpha[0], o[2 * np + 1][1] *= alpha[0], o[2 * np + 1][2] *= alpha[1],
+                o[2 * np + 1][3] *= alpha[1];
+            uint32_t bf[4];
+            ldsm_x4_t(bf, tile_addr<HD>(sV, warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
+            mma16816(o[2 * np], pf, bf[0], bf[1]);
+            mma16816(o[2 * np + 1], pf, bf[2], bf[3]);
+        }
+    }
+
+    // ---- merge the four warps' (m, l, O) in shared memory ----
+    __syncthreads();  // all warps are done with sK/sV
+    const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
+    if (t == 0) {
+        s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
+        s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
+    }
+    for (int idx = tid; idx < kDecRows * HD; idx += kThreads) sO[idx] = 0.0f;
+    __syncthreads();
+    float fac[2];
+#pragma unroll
+    for (int rI = 0; rI < 2; rI++) {
+        const int rr = g + rI * 8;
+        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
+        fac[rI] = (m_run[rI] == ninf) ? 0.0f : exp2f(m_run[rI] - M);
+    }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int rI = e >> 1;
+            if (fac[rI] != 0.0f) atomicAdd(&sO[(g + rI * 8) * HD + nt * 8 + 2 * t + (e & 1)], o[nt][e] * fac[rI]);
+        }
+    if (tid < kDecRows) {
+        const int rr = tid;
+        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
+        float L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) L += (s_m[w][rr] == ninf) ? 0.0f : s_l[w][rr] * exp2f(s_m[w][rr] - M);
+        s_M[rr] = M, s_L[rr] = L;
+    }
+    __syncthreads();
+
+    if (a.n_splits == 1) {
+        for (int idx = tid; idx < R * HD; idx += kThreads) {
+            const int rr = idx / HD, c = idx % HD;
+            if (c >= a.hd) continue;
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            const float L = s_L[rr];
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? sO[idx] / L : 0.0f;
+        }
+    } else {
+        const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
+        float* wo = a.ws_o + unit * kDecRows * HD;
+        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = sO[idx];
+        if (tid < kDecRows) {
+            a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
+            a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
+        }
+    }
+}
+
+// One warp per (batch, kv-head, row): log-sum-exp merge of the split partials.
+template <int HD>
+__global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a) {
+    const int warp_global = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int R = a.Tq * a.gqa;
+    const int total = a.B * a.Hkv * kDecRows;
+    if (warp_global >= total) return;
+    const int rr = warp_global % kDecRows;
+    const int hk = (warp_global / kDecRows) % a.Hkv;
+    const int b = warp_global / (kDecRows * a.Hkv);
+    if (rr >= R) return;
+    const int64_t unit0 = ((int64_t)b * a.Hkv + hk) * a.n_splits;
+    float M = -INFINITY;
+    for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, a.ws_ml[((unit0 + s) * kDecRows + rr) * 2]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    float acc[HD / 32];
+#pragma unroll
+    for (int i = 0; i < HD / 32; i++) acc[i] = 0.0f;
+    float L = 0.0f;
+    for (int s = 0; s < a.n_splits; s++) {
+        const float ms = a.ws_ml[((unit0 + s) * kDecRows + rr) * 2];
+        if (ms == -INFINITY) continue;
+        const float w = exp2f(ms - M);
+        L += w * a.ws_ml[((unit0 + s) * kDecRows + rr) * 2 + 1];
+        const float* po = a.ws_o + ((unit0 + s) * kDecRows + rr) * HD;
+#pragma unroll
+        for (int i = 0; i < HD / 32; i++) acc[i] += w * po[lane + 32 * i];
+    }
+    const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+    float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd;
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+    for (int i = 0; i < HD / 32; i++) {
+        const int c = lane + 32 * i;
+        if (c < a.hd) out[c] = acc[i] * inv;
+    }
+}
+
+template <int HD>
+int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
+    const size_t smem = (size_t)(kDecRows + 2 * kDecBN) * HD * sizeof(__half);
+    auto kern = fattn_decode_split_kernel<HD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(a.n_splits, a.Hkv, a.B);
+    kern<<<grid, kThreads, smem, st>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (a.n_splits > 1) {
+        const int warps = a.B * a.Hkv * kDecRows;
+        fattn_merge_kernel<HD><<<(warps + 3) / 4, kThreads, 0, st>>>(a);
+        e = cudaGetLastError();
+    }
+    return (int)e;
+}
+
+}  // namespace
+
+int launch_tile_mma(const FattnArgs& a, cudaStream_t st) {
+    const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
+    if (a.relpos) {
+        if (hdp == 32) return launch_tile_t<32, true>(a, st);
+        if (hdp == 64) return launch_tile_t<64, true>(a, st);
+        return launch_tile_t<128, true>(a, st);
+    }
+    if (hdp == 32) return launch_tile_t<32, false>(a, st);
+    if (hdp == 64) return launch_tile_t<64, false>(a, st);
+    return launch_tile_t<128, false>(a, st);
+}
+
+int launch_decode_split(const FattnArgs& a, cudaStream_t st) {
+    const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
+    if (hdp == 32) return launch_decode_t<32>(a, st);
+    if (hdp == 64) return launch_decode_t<64>(a, st);
+    return launch_decode_t<128>(a, st);
+}
+
+size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd) {
+    if (n_splits <= 1) return 0;
+    const int hdp = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
+    const size_t units = (size_t)B * Hkv * n_splits;
+    const size_t o = units * kDecRows * hdp * sizeof(float);
+    const size_t ml = units * kDecRows * 2 * sizeof(float);
+    return ((o + 255) / 256) * 256 + ((ml + 255) / 256) * 256;
+}
+
+// Enough CTAs to put about four on every SM, never more splits than 64-key tiles.
+int decode_split_choose(int B, int Hkv, int Lk, int sm_count) {
+    const int tiles = (Lk + kDecBN - 1) / kDecBN;
+    const long units = (long)B * Hkv;
+    long want = (4L * sm_count + units - 1) / units;
+    if (want < 1) want = 1;
+    if (want > tiles) want = tiles;
+    if (want > 64) want = 64;
+    return (int)(want < 1 ? 1 : want);
+}
+
+}  // namespace b200

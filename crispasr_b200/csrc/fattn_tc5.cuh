@@ -1,0 +1,14 @@
+// fattn_tc5.cuh — interface of the TMA + tcgen05 + TMEM prefill kernel (fattn_tc5.cu).
+#pragma once
+#include "fattn_common.cuh"
+
+namespace b200 {
+
+// True when the operands fit the tcgen05 kernel: F16 K/V with 16-byte aligned strides, head_dim 64 or
+// 128, no explicit mask, no softcap/ALiBi (implicit causal mask and kv_len are handled in-kernel).
+bool tc5_supported(const FattnArgs& a);
+
+// Encodes the tensor maps and launches. Returns a B200_* code; on CUDA failure writes the text to errbuf.
+int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen);
+
+}  // namespace b200

@@ -287,9 +287,8 @@ B200_API void orc_quantize_q8_0(const float* x, uint8_t* out, int64_t n) {
         std::memcpy(blk, &dh, 2);
         for (int i = 0; i < 32; i++) {
             const float t = xb[i] * id;
-            // np_roundf: trunc(|t| + 0.5) with the sign restored
-            const float a = std::floor(std::fabs(t) + 0.5f);
-            blk[2 + i] = (uint8_t)(int8_t)(t < 0 ? -a : a);
+            // gguf-py np_roundf: floor(|t|) + floor(2*(|t| - floor(|t|))), sign restored == roundf
+            blk[2 + i] = (uint8_t)(int8_t)std::round(t);
         }
     }
 }

@@ -1,0 +1,181 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every declared symbol, validates operands
+with error codes (never aborts), plans kernels, and the segment scheduler's host logic."""
+import ctypes as C
+import os
+import re
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from crispasr_b200 import abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200_fattn.h")).read()
+    return sorted(set(re.findall(r"B200_API\s+[\w\s\*]+?\b(b200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(b200):
+    names = declared_symbols()
+    assert len(names) >= 18
+    lib = C.CDLL(b200.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/b200_fattn.h but not exported"
+    assert set(names) == set(abi.SYMBOLS), "ctypes mirror and header disagree"
+    assert b"sm_100a" in b200.lib().b200_version()
+
+
+def test_missing_library_fails_loudly(b200, monkeypatch):
+    import crispasr_b200
+    monkeypatch.setattr(crispasr_b200, "_LIB", None)
+    monkeypatch.setattr(crispasr_b200, "LIB_PATH", "/nonexistent/libb200_fattn.so")
+    with pytest.raises(ImportError):
+        crispasr_b200.lib()
+
+
+def _desc(shape, dtype=torch.float16):
+    return torch.zeros(shape, dtype=dtype)
+
+
+def _supports(b200, q, k, v, mask=None, dst=None, **kw):
+    from crispasr_b200.op import _make, _dst_like
+    c = _make(q, k, v, mask, dst if dst is not None else _dst_like(q), dict(scale=1.0, **kw), abi.from_torch)
+    why = C.c_int(0)
+    ok = b200.lib().b200_fattn_supports(*c.args(), C.byref(why))
+    return bool(ok), why.value
+
+
+def test_validator_codes(b200):
+    q = _desc((1, 8, 10, 64), torch.float32)
+    k = _desc((1, 8, 20, 64))
+    assert _supports(b200, q, k, k) == (True, 0)
+    assert _supports(b200, q, k, _desc((1, 8, 20, 64), torch.float32))[1] == abi.E_TYPE      # K/V types differ
+    assert _supports(b200, q, _desc((1, 8, 20, 32)), _desc((1, 8, 20, 32)))[1] == abi.E_SHAPE  # head dims
+    assert _supports(b200, q, _desc((1, 3, 20, 64)), _desc((1, 3, 20, 64)))[1] == abi.E_SHAPE  # 8 % 3
+    assert _supports(b200, q, k, k, _desc((1, 1, 10, 20), torch.float32))[1] == abi.E_TYPE    # mask must be F16
+    assert _supports(b200, q, k, k, _desc((1, 1, 10, 19)))[1] == abi.E_SHAPE                  # mask ne0 != Lk
+    assert _supports(b200, q, k, k, _desc((1, 5, 10, 20)))[1] == abi.E_SHAPE                  # mask heads
+    assert _supports(b200, q, k, k, _desc((1, 8, 10, 20)))[0]                                 # per-head mask ok
+    big = _desc((1, 8, 10, 160), torch.float32)
+    assert _supports(b200, big, _desc((1, 8, 20, 160)), _desc((1, 8, 20, 160)))[1] == abi.E_UNSUPPORTED
+    # dst must be contiguous [hd,H,Tq,B]
+    bad_dst = torch.zeros((1, 10, 8, 128), dtype=torch.float32)[..., :64]
+    assert _supports(b200, q, k, k, dst=bad_dst)[1] == abi.E_STRIDE
+    # Q8_0 rows: nb0 must be one block and hd a multiple of 32
+    kq = torch.zeros((1, 2, 20, 136), dtype=torch.uint8)
+    q128 = _desc((1, 8, 1, 128), torch.float32)
+    assert _supports(b200, q128, kq, kq, kv_type=abi.Q8_0)[0]
+    # relpos needs both operands and Lk == Tq
+    qq = _desc((1, 8, 20, 64), torch.float32)
+    r = _desc((1, 8, 39, 64))
+    assert _supports(b200, qq, k, k, q_v=qq, r=r)[0]
+    assert _supports(b200, q, k, k, q_v=q, r=r)[1] == abi.E_SHAPE
+    assert b200.lib().b200_fattn_supports(None, None, None, None, None, None, None, None) == 0
+    assert b"NULL" in b200.lib().b200_strerror(abi.E_NULL)
+
+
+def test_plan_choices(b200):
+    enc_q = _desc((1, 20, 1500, 64), torch.float32)
+    enc_k = _desc((1, 20, 1500, 64))
+    kern, ns = b200.plan(enc_q, enc_k, enc_k, scale=0.125)
+    assert kern in (abi.KERNEL_PREFILL_TC5, abi.KERNEL_TILE_MMA) and ns == 1
+    # whisper cross-attention decode: 5 beams share the cache -> split-KV with a workspace
+    dq = _desc((1, 20, 5, 64), torch.float32)
+    kern, ns = b200.plan(dq, enc_k, enc_k, scale=0.35)
+    assert kern == abi.KERNEL_DECODE_SPLIT and 1 < ns <= 24
+    assert b200.workspace_bytes(dq, enc_k, enc_k, scale=0.35) >= 20 * ns * 16 * 64 * 4
+    # LLM decode, GQA 4, Q8_0
+    kq = torch.zeros((8, 8, 663, 136), dtype=torch.uint8)
+    kern, _ = b200.plan(_desc((8, 32, 1, 128), torch.float32), kq, kq, scale=0.088, kv_type=abi.Q8_0)
+    assert kern == abi.KERNEL_DECODE_SPLIT
+    # explicit per-head mask or relpos -> general tile kernel unless the tcgen05 kernel takes it
+    r = _desc((1, 20, 2999, 64))
+    kern, _ = b200.plan(enc_q, enc_k, enc_k, scale=0.125, q_v=enc_q, r=r)
+    assert kern in (abi.KERNEL_TILE_MMA, abi.KERNEL_PREFILL_TC5)
+    assert b200.lib().b200_set_kernel_override(abi.KERNEL_TILE_MMA) == 0
+    try:
+        assert b200.plan(dq, enc_k, enc_k, scale=0.35)[0] == abi.KERNEL_TILE_MMA
+    finally:
+        b200.lib().b200_set_kernel_override(abi.KERNEL_NONE)
+    assert b200.lib().b200_set_kernel_override(99) < 0
+
+
+def test_launch_without_gpu_reports_no_device(b200):
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    q = _desc((1, 8, 10, 64), torch.float32)
+    k = _desc((1, 8, 20, 64))
+    with pytest.raises(b200.B200Error) as e:
+        b200.flash_attn_ext_host(q, k, k, scale=1.0)
+    assert e.value.code in (abi.E_NO_DEVICE, abi.E_CUDA)
+
+
+def test_partition_covers_units_exactly(b200):
+    for n, w in [(64, 8), (64, 3), (5, 8), (0, 4), (16, 1)]:
+        seen = []
+        for i in range(w):
+            f, c = b200.SegmentScheduler.partition(n, w, i)
+            seen += list(range(f, f + c))
+        assert seen == list(range(n))
+        sizes = [b200.SegmentScheduler.partition(n, w, i)[1] for i in range(w)]
+        assert max(sizes) - min(sizes) <= 1
+
+
+def test_scheduler_runs_every_unit_once(b200):
+    s = b200.SegmentScheduler(n_host_workers=4)
+    hits = np.zeros(100, np.int32)
+    lock = threading.Lock()
+
+    def unit(dev, u, stream):
+        with lock:
+            hits[u] += 1
+        return 0
+    failed, owners = s.run(100, unit)
+    assert failed == 0 and (hits == 1).all() and all(0 <= o < 4 for o in owners)
+    assert s.run(0, unit) == (0, [])
+    s.close()
+
+
+def test_scheduler_retries_failed_unit_on_another_worker(b200):
+    """Host-side fault injection: unit 7 fails on its first worker (a raised exception) and must be retried
+    elsewhere; unit 11 always fails and is reported, without stopping the other units."""
+    s = b200.SegmentScheduler(n_host_workers=3)
+    tried = {}
+    lock = threading.Lock()
+
+    def unit(dev, u, stream):
+        me = threading.get_ident()
+        with lock:
+            tried.setdefault(u, []).append(me)
+            n = len(tried[u])
+        if u == 7 and n == 1:
+            raise RuntimeError("injected")
+        if u == 11:
+            return 5
+        return 0
+    failed, owners = s.run(20, unit)
+    assert failed == 1 and owners[11] == -1 and owners[7] >= 0
+    assert len(tried[7]) == 2 and tried[7][0] != tried[7][1]
+    assert len(tried[11]) == 2
+    assert all(len(tried[u]) == 1 for u in range(20) if u not in (7, 11))
+    s.close()
+
+
+def test_scheduler_steals_from_slow_worker(b200):
+    import time
+    s = b200.SegmentScheduler(n_host_workers=2)
+    first = {}
+
+    def unit(dev, u, stream):
+        first.setdefault(threading.get_ident(), u)
+        if u < 8:            # worker 0's static range is slow
+            time.sleep(0.01)
+        return 0
+    failed, owners = s.run(16, unit)
+    assert failed == 0
+    assert any(o == 1 for o in owners[:8]), "the idle worker never stole from the busy one"
+    s.close()

@@ -1,0 +1,286 @@
+"""Parity of the CUDA operator (through the C-ABI) against the CPU oracle on seeded inputs.
+Tolerance: max-abs <= 2e-3 and relative L2 <= 1e-3 (fp32 softmax, fp32 accumulation)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from crispasr_b200 import abi
+from tests.util import assert_close, cuda_view, gpu_op, randn_f16
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+KERNELS = {"auto": abi.KERNEL_NONE, "tile": abi.KERNEL_TILE_MMA}
+
+
+@pytest.fixture(params=list(KERNELS))
+def kernel(request, b200):
+    """Runs each case with the automatic kernel choice and again forced onto the general tile kernel."""
+    b200.lib().b200_set_kernel_override(KERNELS[request.param])
+    yield request.param
+    b200.lib().b200_set_kernel_override(abi.KERNEL_NONE)
+
+
+def test_extension_is_loaded_and_device_is_b200(b200):
+    assert torch.cuda.is_available()
+    assert torch.cuda.get_device_capability(0)[0] == 10
+    assert os.path.exists(b200.LIB_PATH)
+
+
+# ---- config 1: Whisper base.en encoder self-attention --------------------------------------------
+def test_cfg1_whisper_base_encoder(b200, orc, kernel):
+    rng = np.random.default_rng(0)
+    T, H, hd = 1500, 8, 64
+    q, k, v = (randn_f16(rng, (1, H, T, hd)) for _ in range(3))
+    ref = orc.flash_attn_ext(q, k, v, scale=0.125)
+    got = gpu_op(b200, q.astype(np.float32), k, v, scale=0.125)   # Q is F32 at the reference call site
+    assert_close(got, ref, "cfg1 contiguous, F32 Q")
+    assert_close(gpu_op(b200, q, k, v, scale=0.125), ref, "cfg1 contiguous, F16 Q")
+
+
+def test_cfg1_whisper_strided_padded_views(b200, orc, kernel):
+    """What src/crispasr.cpp:2813-2821 really issues: token-major K/V views (nb1 = 2*n_state, nb2 = 2*hd)
+    over a zero-cleared buffer padded to 1536 rows, no mask: the 36 zero rows take part in the softmax."""
+    rng = np.random.default_rng(0)
+    T, Tp, H, hd = 1500, 1536, 8, 64
+    kbuf = np.zeros((1, Tp, H, hd), np.float16)
+    vbuf = np.zeros((1, Tp, H, hd), np.float16)
+    kbuf[:, :T], vbuf[:, :T] = randn_f16(rng, (1, T, H, hd)), randn_f16(rng, (1, T, H, hd))
+    qbuf = randn_f16(rng, (1, T, H, hd)).astype(np.float32)
+    qv, kv, vv = (x.transpose(0, 2, 1, 3) for x in (qbuf, kbuf, vbuf))     # (B,H,T,hd) strided
+    ref = orc.flash_attn_ext(qv, kv, vv, scale=0.125)
+    got = gpu_op(b200, cuda_view(qv, qbuf), cuda_view(kv, kbuf), cuda_view(vv, vbuf), scale=0.125)
+    assert_close(got, ref, "cfg1 whisper-strided, Lk 1536 with 36 zero rows")
+
+
+# ---- config 2: Whisper large-v3 decoder step, beam 5 ------------------------------------------------
+@pytest.mark.parametrize("L", [1, 64, 224, 448])
+def test_cfg2_decoder_self_attention_beam_cells(b200, orc, kernel, L):
+    """Layout A of the reference: one pooled cell cache shared by 5 beams, membership only in the F16
+    mask [n_kv, 5] built by the rule of src/crispasr.cpp:3480-3488; Q and K pre-scaled, scale 1.0."""
+    rng = np.random.default_rng(1)
+    H, hd, beams = 20, 64, 5
+    shared = L // 2                      # shared prompt prefix, then private suffixes
+    priv = L - shared
+    n_cells = shared + beams * priv
+    n_kv = min(3584, max(256, -(-n_cells // 256) * 256))
+    cell_pos = np.full(n_kv, 10 ** 6, np.int32)      # unused cells: never visible
+    bits = np.zeros(n_kv, np.uint32)
+    cell_pos[:shared], bits[:shared] = np.arange(shared), (1 << beams) - 1
+    for j in range(beams):
+        sl = slice(shared + j * priv, shared + (j + 1) * priv)
+        cell_pos[sl], bits[sl] = shared + np.arange(priv), 1 << j
+    mask = orc.whisper_beam_mask(cell_pos, bits, tok_seq=np.arange(beams), tok_pos=np.full(beams, L - 1))
+    mask = mask[None, None]                                   # (1,1,5,n_kv)
+    kbuf = randn_f16(rng, (1, n_kv, H, hd), 0.5)
+    vbuf = randn_f16(rng, (1, n_kv, H, hd), 0.5)
+    q = randn_f16(rng, (1, H, beams, hd), 0.5).astype(np.float32)
+    kv, vv = kbuf.transpose(0, 2, 1, 3), vbuf.transpose(0, 2, 1, 3)
+    ref = orc.flash_attn_ext(q, kv, vv, mask, scale=1.0)
+    got = gpu_op(b200, q, cuda_view(kv, kbuf), cuda_view(vv, vbuf), mask, scale=1.0)
+    assert_close(got, ref, f"cfg2 self L={L}")
+
+
+@pytest.mark.parametrize("segments,Lk", [(1, 1500), (1, 1536), (3, 1500)])
+def test_cfg2_decoder_cross_attention(b200, orc, kernel, segments, Lk):
+    rng = np.random.default_rng(1)
+    H, hd, beams = 20, 64, 5
+    kbuf = np.zeros((segments, 1536, H, hd), np.float16)
+    vbuf = np.zeros_like(kbuf)
+    kbuf[:, :1500], vbuf[:, :1500] = randn_f16(rng, (segments, 1500, H, hd), 0.5), randn_f16(rng, (segments, 1500, H, hd), 0.5)
+    q = randn_f16(rng, (segments, H, beams, hd), 0.5).astype(np.float32)
+    kv, vv = kbuf.transpose(0, 2, 1, 3)[:, :, :Lk], vbuf.transpose(0, 2, 1, 3)[:, :, :Lk]
+    scale = 64 ** -0.25
+    ref = orc.flash_attn_ext(q, kv, vv, scale=scale)
+    got = gpu_op(b200, q, cuda_view(kv, kbuf), cuda_view(vv, vbuf), scale=scale)
+    assert_close(got, ref, f"cfg2 cross segments={segments} Lk={Lk}")
+    if kernel == "auto":
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+
+
+# ---- config 3: Whisper large-v3 encoder prefill ---------------------------------------------------------
+def test_cfg3_large_v3_encoder_segments(b200, orc, kernel):
+    rng = np.random.default_rng(2)
+    S, H, T, hd = 2, 20, 1500, 64
+    q, k, v = (randn_f16(rng, (S, H, T, hd)) for _ in range(3))
+    ref = orc.flash_attn_ext(q, k, v, scale=0.125)
+    assert_close(gpu_op(b200, q, k, v, scale=0.125), ref, "cfg3 two segments")
+
+
+# ---- config 4: Voxtral-style LLM decoder, GQA 32/8, hd 128, Q8_0 KV ------------------------------------------
+def _q8_cache(orc, rng, streams, Hkv, rows, hd, max_ctx):
+    x = rng.standard_normal((streams, Hkv, rows, hd)).astype(np.float32)
+    cache = np.zeros((streams, Hkv, max_ctx, hd // 32 * 34), np.uint8)
+    cache[:, :, :rows] = orc.quantize_q8_0(x)
+    return cache
+
+
+def test_cfg4_prefill_causal_q8_0(b200, orc, kernel):
+    rng = np.random.default_rng(3)
+    T, H, Hkv, hd = 407, 32, 8, 128
+    kc, vc = _q8_cache(orc, rng, 1, Hkv, T, hd, 448), _q8_cache(orc, rng, 1, Hkv, T, hd, 448)
+    q = randn_f16(rng, (1, H, T, hd)).astype(np.float32)
+    scale = hd ** -0.5
+    kv, vv = kc[:, :, :T], vc[:, :, :T]
+    mask = orc.causal_mask(T, T, 0)[None, None]
+    ref = orc.flash_attn_ext(q, kv, vv, mask, scale=scale, kv_type=abi.Q8_0)
+    got_m = gpu_op(b200, q, cuda_view(kv, kc), cuda_view(vv, vc), mask, scale=scale, kv_type=abi.Q8_0)
+    assert_close(got_m, ref, "cfg4 prefill, explicit F16 causal mask")
+    got_i = gpu_op(b200, q, cuda_view(kv, kc), cuda_view(vv, vc), scale=scale, kv_type=abi.Q8_0, causal=True, n_past=0)
+    assert_close(got_i, ref, "cfg4 prefill, implicit causal")
+
+
+@pytest.mark.parametrize("lens", [[408] * 8, [408, 450, 511, 512, 513, 600, 663, 1]])
+def test_cfg4_decode_ragged_streams(b200, orc, kernel, lens):
+    rng = np.random.default_rng(3)
+    S, H, Hkv, hd, max_ctx = 8, 32, 8, 128, 672
+    kc, vc = _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx), _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx)
+    q = randn_f16(rng, (S, H, 1, hd)).astype(np.float32)
+    scale = hd ** -0.5
+    Lk = max(lens)
+    kv, vv = kc[:, :, :Lk], vc[:, :, :Lk]
+    ref = orc.flash_attn_ext(q, kv, vv, scale=scale, kv_type=abi.Q8_0, kv_len=lens)
+    got = gpu_op(b200, q, cuda_view(kv, kc), cuda_view(vv, vc), scale=scale, kv_type=abi.Q8_0, kv_len=lens)
+    assert_close(got, ref, f"cfg4 decode lens={lens}")
+    if kernel == "auto":
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+
+
+def test_cfg4_decode_f16_cache_gqa(b200, orc, kernel):
+    rng = np.random.default_rng(33)
+    S, H, Hkv, hd, Lk = 4, 32, 8, 128, 535
+    k, v = randn_f16(rng, (S, Hkv, Lk, hd)), randn_f16(rng, (S, Hkv, Lk, hd))
+    q = randn_f16(rng, (S, H, 1, hd)).astype(np.float32)
+    ref = orc.flash_attn_ext(q, k, v, scale=hd ** -0.5)
+    assert_close(gpu_op(b200, q, k, v, scale=hd ** -0.5), ref, "decode F16 GQA")
+
+
+# ---- config 5: FastConformer relative-position attention ---------------------------------------------------------
+def _relpos_case(orc, rng, T, H=8, hd=128, d_model=1024):
+    q = rng.standard_normal((1, H, T, hd)).astype(np.float32)
+    u = (rng.standard_normal((H, 1, hd)) * 0.02).astype(np.float32)
+    vb = (rng.standard_normal((H, 1, hd)) * 0.02).astype(np.float32)
+    q_u = (q + u).astype(np.float16).astype(np.float32)
+    q_v = (q + vb).astype(np.float16).astype(np.float32)
+    k, v = randn_f16(rng, (1, H, T, hd)).astype(np.float32), randn_f16(rng, (1, H, T, hd)).astype(np.float32)
+    pe = orc.make_pos_enc(d_model, T)                                        # (2T-1, d)
+    w = (rng.standard_normal((d_model, H * hd)) / 32.0).astype(np.float32)   # attn_pos_w, sigma 1/32
+    r = (pe @ w).reshape(2 * T - 1, H, hd).transpose(1, 0, 2)[None]
+    r = np.ascontiguousarray(r).astype(np.float16)
+    return q_u, q_v, k, v, r
+
+
+@pytest.mark.parametrize("T", [64, 200, 611])
+def test_cfg5_fused_relpos_bias(b200, orc, kernel, T):
+    """Fused bias == the reference's materialised F16 mask path (src/core/fastconformer.h:880-933)."""
+    rng = np.random.default_rng(4)
+    q_u, q_v, k, v, r = _relpos_case(orc, rng, T)
+    scale = 128 ** -0.5
+    mask = orc.relpos_mask(q_v, r, scale)                       # (1,H,T,T) F16: what the reference feeds the op
+    ref = orc.flash_attn_ext(q_u, k, v, mask, scale=scale)
+    got_fused = gpu_op(b200, q_u, k, v, scale=scale, q_v=q_v, r=r)
+    assert_close(got_fused, ref, f"cfg5 fused T={T}")
+    got_mask = gpu_op(b200, q_u, k, v, mask, scale=scale)       # per-head mask form of the plain op
+    assert_close(got_mask, ref, f"cfg5 per-head mask T={T}")
+
+
+def test_cfg5_relpos_with_padding_mask(b200, orc, kernel):
+    """Bucketed padding (src/canary_ctc.cpp:370-382): pad keys carry -inf on top of the bias."""
+    rng = np.random.default_rng(44)
+    T, valid = 160, 131
+    q_u, q_v, k, v, r = _relpos_case(orc, rng, T)
+    scale = 128 ** -0.5
+    pad = np.zeros((1, 1, T, T), np.float16)
+    pad[..., valid:] = -np.inf
+    ref = orc.flash_attn_ext(q_u, k, v, pad, scale=scale, q_v=q_v, r=r)
+    got = gpu_op(b200, q_u, k, v, pad, scale=scale, q_v=q_v, r=r)
+    assert_close(got[:, :valid], ref[:, :valid], "cfg5 fused + padding mask")
+    got2 = gpu_op(b200, q_u, k, v, scale=scale, q_v=q_v, r=r, kv_len=[valid])
+    assert_close(got2[:, :valid], ref[:, :valid], "cfg5 fused + kv_len")
+
+
+# ---- golden fixtures and edge cases ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["enc64", "gqa128_causal", "perhead_mask", "decode1", "beams5"])
+def test_golden_sdpa_fixtures(b200, kernel, name):
+    g = np.load(os.path.join(G, "sdpa.npz"))
+    mask = g[name + "_mask"] if name + "_mask" in g else None
+    got = gpu_op(b200, g[name + "_q"], g[name + "_k"], g[name + "_v"], mask, scale=float(g[name + "_scale"]))
+    assert_close(got, g[name + "_out"], name)
+
+
+def test_golden_cross_attn_kat(b200, kernel):
+    """tests/test-core-cross-attn.cpp numbers through the GPU op (hd 4, F32 K/V, unscaled)."""
+    g = np.load(os.path.join(G, "crossattn.npz"))
+    Q = (g["q_proj"] @ g["dec"]).astype(np.float32).reshape(1, 2, 1, 4)
+    got = gpu_op(b200, Q, g["cK"][None], g["cV"][None], scale=1.0)
+    # Q, K, V are rounded to F16 on the way to the tensor cores: 1e-3 instead of the test's 1e-4
+    assert np.abs(got.reshape(-1) - g["head_out"]).max() < 1e-3
+
+
+@pytest.mark.parametrize("Tq,Lk,hd,H,Hkv", [(1, 1, 64, 4, 4), (3, 65, 64, 2, 1), (17, 63, 128, 4, 2), (64, 64, 32, 2, 2),
+                                           (129, 257, 64, 3, 3), (5, 1000, 128, 8, 8), (100, 7, 128, 2, 2)])
+def test_ragged_shapes(b200, orc, kernel, Tq, Lk, hd, H, Hkv):
+    rng = np.random.default_rng(Tq * 1000 + Lk)
+    q, k, v = randn_f16(rng, (2, H, Tq, hd)), randn_f16(rng, (2, Hkv, Lk, hd)), randn_f16(rng, (2, Hkv, Lk, hd))
+    ref = orc.flash_attn_ext(q, k, v, scale=hd ** -0.5)
+    assert_close(gpu_op(b200, q, k, v, scale=hd ** -0.5), ref, f"Tq={Tq} Lk={Lk} hd={hd}")
+
+
+def test_f32_kv_softcap_alibi(b200, orc, kernel):
+    rng = np.random.default_rng(8)
+    q = randn_f16(rng, (1, 6, 70, 64)).astype(np.float32)
+    k = randn_f16(rng, (1, 6, 90, 64)).astype(np.float32)
+    v = randn_f16(rng, (1, 6, 90, 64)).astype(np.float32)
+    m = (rng.standard_normal((1, 1, 70, 90))).astype(np.float16)
+    ref = orc.flash_attn_ext(q, k, v, m, scale=0.3, max_bias=8.0, softcap=5.0)
+    assert_close(gpu_op(b200, q, k, v, m, scale=0.3, max_bias=8.0, softcap=5.0), ref, "F32 KV + softcap + ALiBi")
+
+
+def test_fully_masked_rows_and_empty_cache(b200, orc, kernel):
+    rng = np.random.default_rng(6)
+    q, k, v = randn_f16(rng, (2, 4, 9, 64)), randn_f16(rng, (2, 4, 80, 64)), randn_f16(rng, (2, 4, 80, 64))
+    m = np.zeros((1, 1, 9, 80), np.float16)
+    m[0, 0, 4, :] = -np.inf
+    ref = orc.flash_attn_ext(q, k, v, m, scale=0.125)
+    got = gpu_op(b200, q, k, v, m, scale=0.125)
+    assert np.all(got[:, 4] == 0)
+    assert_close(got, ref, "fully masked row")
+    got = gpu_op(b200, q, k, v, scale=0.125, kv_len=[0, 80])
+    assert np.all(got[0] == 0)
+    assert_close(got, orc.flash_attn_ext(q, k, v, scale=0.125, kv_len=[0, 80]), "kv_len 0")
+
+
+def test_host_buffer_entry_point(b200, orc):
+    rng = np.random.default_rng(12)
+    q = torch.from_numpy(randn_f16(rng, (2, 8, 5, 64)).astype(np.float32)).pin_memory()
+    k = torch.from_numpy(randn_f16(rng, (2, 8, 300, 64))).pin_memory()
+    v = torch.from_numpy(randn_f16(rng, (2, 8, 300, 64))).pin_memory()
+    out = b200.flash_attn_ext_host(q, k, v, scale=0.125, kv_len=torch.tensor([300, 123], dtype=torch.int32))
+    ref = orc.flash_attn_ext(q.numpy(), k.numpy(), v.numpy(), scale=0.125, kv_len=[300, 123])
+    assert_close(out.numpy(), ref, "host entry point")
+    b200.lib().b200_host_arena_release()
+
+
+def test_full_size_properties_cfg5(b200, orc):
+    """BASELINE size (T = 7500, 8 heads, hd 128): sampled query rows against the oracle, plus the
+    size-independent property that softmax weights sum to one (V = ones gives ones)."""
+    rng = np.random.default_rng(4)
+    T = 7500
+    q_u, q_v, k, v, r = _relpos_case(orc, rng, T)
+    scale = 128 ** -0.5
+    got = gpu_op(b200, q_u, k, v, scale=scale, q_v=q_v, r=r)
+    rows = np.array([0, 1, 63, 64, 3749, 7437, 7499])
+    # the oracle on a row subset: rel-shift index (T-1)+k-q needs the true q, so check via the materialised
+    # mask rows of those queries
+    mask_rows = np.empty((1, 8, len(rows), T), np.float16)
+    rf = r.astype(np.float32)
+    for i, qi in enumerate(rows):
+        band = rf[0, :, T - 1 - qi: 2 * T - 1 - qi]                     # r[T-1+k-q] for k = 0..T-1
+        mask_rows[0, :, i] = (np.einsum("hc,hkc->hk", q_v[0, :, qi], band) * np.float32(scale)).astype(np.float16)
+    ref = orc.flash_attn_ext(q_u[:, :, rows], k, v, mask_rows, scale=scale)
+    assert_close(got[:, rows], ref, "cfg5 full size, sampled rows", max_abs=2e-3, rel_l2=2e-3)
+    ones = np.ones_like(v)
+    got1 = gpu_op(b200, q_u, k, ones, scale=scale, q_v=q_v, r=r)
+    assert np.abs(got1 - 1.0).max() < 2e-3
