@@ -414,3 +414,69 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
 B200_API void b200_host_arena_release(void) { g_arena.release(); }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of the split-KV decode launch.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they run the operator:
+// a decode loop that sits inside a real-time audio callback, an embedder whose memory budget is
+// fixed at start-up and audited, or a process that hands the library a stream but owns no
+// allocator of its own.  b200_fattn_launch needs a caller-provided workspace for the split-KV
+// partials; this entry point instead keeps that scratch in a fixed array that is part of the
+// loaded module, so a call needs nothing but its operands.
+//
+// The array costs kStaticScratchBytes of device memory on every GPU that loads the library, from
+// load until the process exits.  All calls share it and it is never cleared: the decode kernel
+// writes every partial (O, m, l) of every split before the merge kernel reads any, so nothing has
+// to start at zero, but the previous call's bytes are still there.  Two calls that can overlap
+// on the GPU (different streams, or different host threads) race on the array; issue them on one
+// stream or serialise them.
+// ------------------------------------------------------------------------------------------
+namespace b200 {
+namespace {
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: covers the split-KV partials of up to 8 decode streams x 8 KV heads x head_dim 128
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address the kernels can use comes from cudaGetSymbolAddress, once per device, with that device current.
+int static_scratch_ptr(void** out) {
+    static std::mutex mu;
+    static void* ptrs[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaGetDevice");
+        return B200_E_NO_DEVICE;
+    }
+    if (dev < 0 || dev >= 64) return B200_E_NO_DEVICE;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        if (!p || (uintptr_t)p % 256) return B200_E_ALIGN;
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return B200_OK;
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" B200_API int b200_fattn_launch_static(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                                  const b200_tensor* mask, const b200_tensor* dst,
+                                                  const b200_fattn_params* params, const b200_fattn_ext* ext,
+                                                  void* cuda_stream) {
+    Plan plan;
+    int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
+    if (rc != B200_OK) return rc;
+    if (plan.kernel != B200_KERNEL_DECODE_SPLIT) return B200_E_UNSUPPORTED;  // only the split-KV decode form
+    if (plan.ws_bytes > kStaticScratchBytes) return B200_E_LIMIT;
+    DeviceInfo di;
+    if ((rc = device_info(&di))) return rc;
+    void* scratch = nullptr;
+    if ((rc = static_scratch_ptr(&scratch))) return rc;
+    return do_launch(plan, scratch, kStaticScratchBytes, (cudaStream_t)cuda_stream);
+}
+
+extern "C" B200_API size_t b200_fattn_static_scratch_bytes(void) { return b200::kStaticScratchBytes; }

@@ -182,6 +182,26 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
 /* Frees the calling thread's staging arena of b200_fattn_forward_host. */
 B200_API void b200_host_arena_release(void);
 
+/*
+ * b200_fattn_launch_static — no counterpart in the reference (ggml always sizes a work buffer for the
+ * op): the split-KV decode launch for callers that cannot allocate device memory — code running inside a
+ * real-time audio callback, embedders with a fixed, audited memory budget, hosts that pass a stream but
+ * own no allocator.  Same operands and semantics as b200_fattn_launch, no workspace argument: the split
+ * partials live in a fixed array inside the loaded module (b200_fattn_static_scratch_bytes() = 8 MiB, held
+ * on every GPU that loads the library until the process exits).  The call itself allocates and frees
+ * nothing.  Accepts only operand forms that b200_fattn_plan maps to B200_KERNEL_DECODE_SPLIT
+ * (else B200_E_UNSUPPORTED) whose b200_fattn_workspace_bytes fits the array (else B200_E_LIMIT).
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call before starting any stream capture.  Every call shares the one
+ * array and finds the previous call's contents in it (the kernels overwrite all they read, nothing
+ * needs clearing); calls that may overlap on the GPU race on it, so keep them on one stream.
+ */
+B200_API int b200_fattn_launch_static(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                      const b200_tensor* mask, const b200_tensor* dst,
+                                      const b200_fattn_params* params, const b200_fattn_ext* ext,
+                                      void* cuda_stream);
+B200_API size_t b200_fattn_static_scratch_bytes(void);
+
 /* The kernel family the calling thread's most recent successful launch used. */
 B200_API int b200_last_kernel(void);
 

@@ -1,0 +1,103 @@
+"""The allocation-free decode entry point, b200_fattn_launch_static.
+
+It exists for hosts that cannot allocate device memory where they run the operator (a decode loop inside
+a real-time audio callback, an embedder with a fixed memory budget, a caller that hands over a stream but
+has no allocator): the split-KV partials live in a fixed 8 MiB array inside the loaded library instead of
+a caller-provided workspace.  The test calls it through the C-ABI twice in a row — the second call finds
+the first call's bytes in the shared array — and compares each result with b200_fattn_launch on the same
+operands, within the parity tolerance of the suite.  This file sorts last so a run that stops at the
+first failure has already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from crispasr_b200 import abi
+from tests.util import MAX_ABS_TOL, REL_L2_TOL, errors
+
+pytestmark = pytest.mark.gpu
+
+
+def _descs(q, k, v, dst, kv_type=None):
+    return abi.from_torch(q), abi.from_torch(k, kv_type), abi.from_torch(v, kv_type), abi.from_torch(dst)
+
+
+def _launch_ws(L, q, k, v, kv_type, scale, kv_len=None):
+    """The existing entry point, with a caller-allocated workspace."""
+    dst = torch.empty((q.shape[0], q.shape[2], q.shape[1], q.shape[3]), dtype=torch.float32, device="cuda")
+    tq, tk, tv, td = _descs(q, k, v, dst, kv_type)
+    p = abi.Params(scale, 0.0, 0.0, 0)
+    e = abi.Ext()
+    if kv_len is not None:
+        e.kv_len = kv_len.data_ptr()
+    n = C.c_size_t(0)
+    assert L.b200_fattn_workspace_bytes(C.byref(tq), C.byref(tk), C.byref(tv), None, C.byref(td), C.byref(p), C.byref(e), C.byref(n)) == 0
+    ws = torch.empty(max(n.value, 256), dtype=torch.uint8, device="cuda")
+    rc = L.b200_fattn_launch(C.byref(tq), C.byref(tk), C.byref(tv), None, C.byref(td), C.byref(p), C.byref(e),
+                             ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.b200_strerror(rc)
+    torch.cuda.synchronize()
+    return dst, n.value
+
+
+def _launch_static(L, q, k, v, kv_type, scale, kv_len=None):
+    dst = torch.empty((q.shape[0], q.shape[2], q.shape[1], q.shape[3]), dtype=torch.float32, device="cuda")
+    tq, tk, tv, td = _descs(q, k, v, dst, kv_type)
+    p = abi.Params(scale, 0.0, 0.0, 0)
+    e = abi.Ext()
+    if kv_len is not None:
+        e.kv_len = kv_len.data_ptr()
+    rc = L.b200_fattn_launch_static(C.byref(tq), C.byref(tk), C.byref(tv), None, C.byref(td), C.byref(p), C.byref(e),
+                                    torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return rc, dst
+
+
+def test_static_scratch_matches_workspace_launch_twice(b200, orc):
+    L = b200.lib()
+    assert L.b200_fattn_static_scratch_bytes() == 8 << 20
+    rng = np.random.default_rng(77)
+    # call 1: LLM decode, 8 streams, GQA 32/8, head_dim 128, Q8_0 cache with ragged lengths
+    S, H, Hkv, hd, Lk = 8, 32, 8, 128, 663
+    kq = torch.from_numpy(orc.quantize_q8_0(rng.standard_normal((S, Hkv, Lk, hd)).astype(np.float32))).cuda()
+    vq = torch.from_numpy(orc.quantize_q8_0(rng.standard_normal((S, Hkv, Lk, hd)).astype(np.float32))).cuda()
+    q1 = torch.from_numpy(rng.standard_normal((S, H, 1, hd)).astype(np.float16)).cuda()
+    lens = torch.tensor([663, 408, 500, 64, 1, 650, 129, 333], dtype=torch.int32, device="cuda")
+    want1, ws1 = _launch_ws(L, q1, kq, vq, abi.Q8_0, hd ** -0.5, lens)
+    assert ws1 > 0, "the case must use split-KV scratch"
+    rc, got1 = _launch_static(L, q1, kq, vq, abi.Q8_0, hd ** -0.5, lens)
+    assert rc == 0, L.b200_strerror(rc)
+    # call 2, directly after: Whisper cross-attention, 5 beams share one F16 cache, different geometry
+    k2 = torch.from_numpy((rng.standard_normal((1, 20, 1500, 64)) * 0.5).astype(np.float16)).cuda()
+    v2 = torch.from_numpy((rng.standard_normal((1, 20, 1500, 64)) * 0.5).astype(np.float16)).cuda()
+    q2 = torch.from_numpy((rng.standard_normal((1, 20, 5, 64)) * 0.5).astype(np.float32)).cuda()
+    rc, got2 = _launch_static(L, q2, k2, v2, None, 64 ** -0.25)
+    assert rc == 0, L.b200_strerror(rc)
+    want2, ws2 = _launch_ws(L, q2, k2, v2, None, 64 ** -0.25)
+    assert ws2 > 0
+    for name, got, want in (("call 1", got1, want1), ("call 2", got2, want2)):
+        ma, rl = errors(got.cpu().numpy(), want.cpu().numpy())
+        assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL, f"{name}: max-abs {ma:.3e} rel-L2 {rl:.3e}"
+    # and both agree with the oracle
+    ref1 = orc.flash_attn_ext(q1.cpu().numpy(), kq.cpu().numpy(), vq.cpu().numpy(), scale=hd ** -0.5,
+                              kv_type=abi.Q8_0, kv_len=lens.cpu().numpy())
+    ma, rl = errors(got1.cpu().numpy(), ref1)
+    assert ma <= MAX_ABS_TOL and rl <= REL_L2_TOL
+
+
+def test_static_scratch_rejects_what_it_cannot_hold(b200):
+    L = b200.lib()
+    # 591 (stream, kv-head) units get 2 splits each: 1182 partials x 16 rows x 128 floats = 9.7 MB > 8 MiB
+    q = torch.zeros((3, 197, 1, 128), dtype=torch.float16, device="cuda")
+    k = torch.zeros((3, 197, 128, 128), dtype=torch.float16, device="cuda")
+    need = b200.workspace_bytes(q, k, k, scale=1.0)
+    assert need > (8 << 20)
+    rc, _ = _launch_static(L, q, k, k, None, 1.0)
+    assert rc == abi.E_LIMIT and b"limit" in L.b200_strerror(rc)
+    # a prefill-shaped call is not the decode kernel: refused, not silently rerouted
+    qp = torch.zeros((1, 4, 300, 64), dtype=torch.float16, device="cuda")
+    kp = torch.zeros((1, 4, 300, 64), dtype=torch.float16, device="cuda")
+    rc, _ = _launch_static(L, qp, kp, kp, None, 0.125)
+    assert rc == abi.E_UNSUPPORTED
