@@ -287,6 +287,13 @@ B200_API const char* b200_strerror(int code) {
 B200_API const char* b200_last_cuda_error(void) { return g_cuda_err; }
 B200_API int b200_last_kernel(void) { return g_last_kernel; }
 
+B200_API int b200_device_status(void) {
+    int st = 0;
+    const int e = tc5_read_status(&st);
+    if (e != 0) return cuda_fail((cudaError_t)e, "cudaMemcpyFromSymbol(status)");
+    return st ? B200_E_DEVICE_WAIT : B200_OK;
+}
+
 B200_API int b200_set_kernel_override(int kernel) {
     if (kernel < B200_KERNEL_NONE || kernel > B200_KERNEL_PREFILL_TC5) return B200_E_SHAPE;
     g_override = kernel;

@@ -1,5 +1,532 @@
+// fattn_tc5.cu — prefill attention on the Blackwell tensor path: TMA-staged K/V tiles, tcgen05.mma
+// with accumulators in tensor memory (TMEM), fp32 online softmax by one thread per query row.
+//
+// One CTA = one 128-row query tile of one (head, batch entry); 192 threads:
+//   warps 0-3  softmax / correction / epilogue: thread r owns query row r (TMEM lane r)
+//   warp  4    TMA producer (one lane): K and V tiles of 128 keys, 128-byte swizzled
+//   warp  5    TMEM allocator and the single tcgen05.mma issuing thread
+// TMEM (256 columns per CTA, so two CTAs share an SM and fill each other's softmax bubbles):
+//   cols [0,128)       S = Q.K^T tile, fp32            (128 lanes x 128 keys)
+//   cols [0,64)        P = exp2(S - m), f16x2 packed    (aliases S once the row has been read)
+//   cols [128,128+HD)  O accumulator, fp32
+// Shared memory: Q tile (written once by the softmax warps, converted to f16, swizzled by hand so
+// both F32 and F16 Q with any strides work), NSTG K tiles and NSTG V tiles (TMA, SWIZZLE_128B).
+// Per KV tile: S = Q.K^T (SS MMA, both operands K-major) -> softmax threads read S, write P to TMEM
+// -> O += P.V (TS MMA: A = P from TMEM, B = V from shared memory, MN-major).
+// The rescale of O by exp2(m_old - m_new) is lazy: it only happens when a row's maximum grew by
+// more than 2^8, so P stays within f16 range and the common case touches O only in the MMA.
+//
+// Every mbarrier wait is bounded: when a wait runs out the CTA raises a flag, all roles leave their
+// loops, in-flight copies are drained (bounded), TMEM is released and a device status word is set.
+#include <cuda.h>
+
+#include <cstdio>
+#include <mutex>
+
 #include "fattn_tc5.cuh"
+
 namespace b200 {
-bool tc5_supported(const FattnArgs&) { return false; }
-int launch_prefill_tc5(const FattnArgs&, cudaStream_t, char*, size_t) { return B200_E_UNSUPPORTED; }
+
+__device__ int g_tc5_status = 0;  // 0 ok, 1 = a bounded wait ran out in some CTA
+
+namespace {
+
+constexpr int kTile = 128;              // query rows per CTA and keys per step
+constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 f16
+constexpr int kThreadsTc5 = 192;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 256) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    atomicExch(&g_tc5_status, 1);
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1 (sm_100).
+//   K-major operand : rows of 128 bytes, 8-row groups 1024 bytes apart  -> LBO = 16 B (unused), SBO = 1024 B
+//   MN-major operand: 64-element chunks `lbo` bytes apart, 8-k groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;   // version
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor for kind::f16: F16 A/B, F32 accumulate, M = 128.
+__host__ __device__ constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Eight Q elements [c0, c0+8) of one row as packed f16 (F32 rows are rounded to nearest even).
+__device__ __forceinline__ uint4 q_chunk(const uint8_t* rowp, int type, int c0, bool vec16) {
+    uint4 out;
+    if (type == B200_TYPE_F16) {
+        if (vec16) return __ldg(reinterpret_cast<const uint4*>(rowp + 2 * c0));
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(rowp + 2 * c0);
+        out.x = h[0] | ((uint32_t)h[1] << 16), out.y = h[2] | ((uint32_t)h[3] << 16);
+        out.z = h[4] | ((uint32_t)h[5] << 16), out.w = h[6] | ((uint32_t)h[7] << 16);
+        return out;
+    }
+    float f[8];
+    if (vec16) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(rowp + 4 * c0));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(rowp + 4 * c0 + 16));
+        f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] = *reinterpret_cast<const float*>(rowp + 4 * (c0 + i));
+    }
+    out.x = pack_half2(f[0], f[1]), out.y = pack_half2(f[2], f[3]);
+    out.z = pack_half2(f[4], f[5]), out.w = pack_half2(f[6], f[7]);
+    return out;
+}
+
+struct Tc5Smem {
+    // offsets from the 1024-byte aligned base of dynamic shared memory
+    template <int HD, int NSTG>
+    static constexpr int tile_bytes() { return kPanelBytes * (HD / 64); }
+};
+
+template <int HD, int NSTG>
+__global__ void __launch_bounds__(kThreadsTc5, 2)
+fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV) {
+    constexpr int PANELS = HD / 64;
+    constexpr int TILE_BYTES = kPanelBytes * PANELS;
+    constexpr uint32_t IDESC_S = idesc_f16(kTile, false);
+    constexpr uint32_t IDESC_PV = idesc_f16(HD, true);
+
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+    const uint32_t sQ = smem_base;
+    const uint32_t sK = sQ + TILE_BYTES;
+    const uint32_t sV = sK + NSTG * TILE_BYTES;
+    const uint32_t sBar = sV + NSTG * TILE_BYTES;  // 8-byte slots
+    const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8 * NSTG, bar_v_full = sBar + 16 * NSTG,
+                   bar_v_empty = sBar + 24 * NSTG, bar_s_full = sBar + 32 * NSTG, bar_p_ready = bar_s_full + 8,
+                   bar_o_done = bar_s_full + 16;
+    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 24;
+    volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * kTile, h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / a.gqa, bk = b / a.bq;
+
+    int len_b = a.Lk;
+    if (a.kv_len) {
+        const int v = a.kv_len[b];
+        len_b = v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
+    }
+    int kmax = len_b;
+    if (a.causal) kmax = min(kmax, a.n_past + min(q0 + kTile, a.Tq));
+    const int n_tiles = kmax > 0 ? (kmax + kTile - 1) / kTile : 0;
+
+    if (n_tiles == 0) {  // nothing to attend to: zeros
+        if (tid < kTile && q0 + tid < a.Tq) {
+            float4* out = reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + q0 + tid) * a.H + h) * HD);
+#pragma unroll
+            for (int i = 0; i < HD / 4; i++) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
+
+    // ---- set-up ----
+    if (tid == 4 * 32) {
+        for (int i = 0; i < NSTG; i++) {
+            mbar_init(bar_k_full + 8 * i, 1);
+            mbar_init(bar_k_empty + 8 * i, 1);
+            mbar_init(bar_v_full + 8 * i, 1);
+            mbar_init(bar_v_empty + 8 * i, 1);
+        }
+        mbar_init(bar_s_full, 1);
+        mbar_init(bar_p_ready, kTile);
+        mbar_init(bar_o_done, 1);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem_base))),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp < 4) {
+        // Q tile -> shared memory, f16, 128-byte swizzle: row r, 16-byte chunk c of panel p lives at
+        // p*16384 + r*128 + ((c ^ (r & 7)) * 16). Thread r writes row r.
+        const int r = tid;
+        const int iq = q0 + r;
+        const uint8_t* rowp = a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3;
+        uint8_t* dst_row = smem_gen + r * 128;
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) {
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (iq < a.Tq) val = q_chunk(rowp, a.q.type, c * 8, a.q.vec16 != 0);
+            *reinterpret_cast<uint4*>(dst_row + (c >> 3) * kPanelBytes + (((c & 7) ^ (r & 7)) << 4)) = val;
+        }
+        fence_proxy_async();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem_base;
+    const uint32_t tmem_S = tmem_base;            // cols [0,128)
+    const uint32_t tmem_P = tmem_base;            // cols [0,64), f16x2
+    const uint32_t tmem_O = tmem_base + kTile;    // cols [128,128+HD)
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            bool ok = true;
+            int issued_k = 0, issued_v = 0;
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int slot = j % NSTG, use = j / NSTG;
+                const int k0 = j * kTile;
+                if (use > 0) ok = mbar_wait(bar_k_empty + 8 * slot, (use - 1) & 1, s_abort);
+                if (!ok) break;
+                mbar_arrive_expect_tx(bar_k_full + 8 * slot, TILE_BYTES);
+#pragma unroll
+                for (int p = 0; p < PANELS; p++)
+                    tma_load_4d(sK + slot * TILE_BYTES + p * kPanelBytes, &tmK, bar_k_full + 8 * slot, p * 64, k0, hk, bk);
+                issued_k = j + 1;
+                if (use > 0) ok = mbar_wait(bar_v_empty + 8 * slot, (use - 1) & 1, s_abort);
+                if (!ok) break;
+                mbar_arrive_expect_tx(bar_v_full + 8 * slot, TILE_BYTES);
+#pragma unroll
+                for (int p = 0; p < PANELS; p++)
+                    tma_load_4d(sV + slot * TILE_BYTES + p * kPanelBytes, &tmV, bar_v_full + 8 * slot, p * 64, k0, hk, bk);
+                issued_v = j + 1;
+            }
+            if (!ok) {
+                // drain: wait (bounded) for the copies this thread still has in flight
+                for (int j = max(0, issued_k - NSTG); j < issued_k; j++)
+                    for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_k_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
+                for (int j = max(0, issued_v - NSTG); j < issued_v; j++)
+                    for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_v_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int slot = j % NSTG, use = j / NSTG;
+                ok = mbar_wait(bar_k_full + 8 * slot, use & 1, s_abort);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+                    mma_ss(tmem_S, smem_desc(sQ + off, 16, 1024), smem_desc(sK + slot * TILE_BYTES + off, 16, 1024),
+                           IDESC_S, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_s_full);
+                tc_commit(bar_k_empty + 8 * slot);
+                ok = mbar_wait(bar_p_ready, j & 1, s_abort);
+                if (!ok) break;
+                ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kTile / 16; ks++)
+                    mma_ts(tmem_O, tmem_P + ks * 8, smem_desc(sV + slot * TILE_BYTES + ks * 2048, kPanelBytes, 1024),
+                           IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(bar_v_empty + 8 * slot);
+                if (j == n_tiles - 1) tc_commit(bar_o_done);
+            }
+            if (!ok) {
+                // make sure no MMA of this CTA is still running before TMEM is released
+                tc_commit(bar_o_done);
+                for (uint32_t it = 0; it < 65536 && !mbar_try_wait(bar_o_done, 0); ++it) __nanosleep(256);
+            }
+        }
+    } else {
+        // ================= softmax / correction / epilogue =================
+        const int r = tid;
+        const int iq = q0 + r;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = a.scale * kLog2e;
+        int kend = len_b;
+        if (a.causal) kend = min(kend, a.n_past + iq + 1);
+        float m_ref = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; j++) {
+            ok = mbar_wait(bar_s_full, j & 1, s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const int n_valid = kend - j * kTile;  // columns >= n_valid are masked
+            // pass 1: row maximum (two 64-column halves; S is read again in pass 2 to keep registers low)
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                uint32_t sreg[2][32];
+                tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int q2 = 0; q2 < 2; q2++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        float sv = __uint_as_float(sreg[q2][i]);
+                        if (hh * 64 + q2 * 32 + i >= n_valid) sv = -INFINITY;
+                        mx[i & 3] = fmaxf(mx[i & 3], sv);
+                    }
+            }
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;  // c > 0
+            // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
+            const bool grow = m_tile > m_ref + kRescaleThreshold;  // also true for -inf -> finite
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_ref, m_tile);
+                if (j > 0) {
+                    const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
+                    l_run *= alpha;
+#pragma unroll
+                    for (int q4 = 0; q4 < HD / 32; q4++) {
+                        uint32_t oreg[32];
+                        tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                        tmem_st32(tmem_O + lane_base + q4 * 32, oreg);
+                    }
+                }
+                m_ref = m_new;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            // pass 2: P = exp2(S*c - m), packed f16x2, written over the columns of S already consumed
+            float lsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                uint32_t sreg[2][32];
+                uint32_t preg[32];
+                tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int q2 = 0; q2 < 2; q2++)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int col = hh * 64 + q2 * 32 + i;
+                        float p0 = ex2(fmaf(__uint_as_float(sreg[q2][i]), c, -m_use));
+                        float p1 = ex2(fmaf(__uint_as_float(sreg[q2][i + 1]), c, -m_use));
+                        if (col >= n_valid) p0 = 0.0f;
+                        if (col + 1 >= n_valid) p1 = 0.0f;
+                        lsum[(i >> 1) & 3] += p0 + p1;
+                        preg[q2 * 16 + (i >> 1)] = pack_half2(p0, p1);
+                    }
+                tmem_st32(tmem_P + lane_base + hh * 32, preg);
+            }
+            l_run += (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p_ready);
+        }
+        if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * HD;
+#pragma unroll
+            for (int q4 = 0; q4 < HD / 32; q4++) {
+                uint32_t oreg[32];
+                tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                tmem_wait_ld();
+                if (iq < a.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(out + q4 * 32 + i) =
+                            make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
+                                        __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
+                }
+            }
+        }
+    }
+
+    // ---- teardown ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static std::once_flag once;
+    static EncodeTiledFn fn = nullptr;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// K/V as a rank-4 F16 tensor [hd, Lk, Hkv, Bk] with the caller's byte strides; box = 64 x 128 x 1 x 1.
+bool encode_kv_map(CUtensorMap* m, const View& v, int hd, int Lk, int Hkv, int Bk) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)Lk, (cuuint64_t)Hkv, (cuuint64_t)Bk};
+    const cuuint64_t strides[3] = {(cuuint64_t)v.nb1, (cuuint64_t)v.nb2, (cuuint64_t)v.nb3};
+    const cuuint32_t box[4] = {64, (cuuint32_t)kTile, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<uint8_t*>(v.p), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD, int NSTG>
+int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+    CUtensorMap tmK, tmV;
+    if (!encode_kv_map(&tmK, a.k, a.hd, a.Lk, a.Hkv, a.B / a.bq) || !encode_kv_map(&tmV, a.v, a.hd, a.Lk, a.Hkv, a.B / a.bq)) {
+        snprintf(errbuf, errlen, "cuTensorMapEncodeTiled failed for K/V");
+        return B200_E_CUDA;
+    }
+    constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
+    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 24 + 16;
+    auto kern = fattn_prefill_tc5_kernel<HD, NSTG>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+        dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
+        kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        snprintf(errbuf, errlen, "tcgen05 prefill launch: %s", cudaGetErrorString(e));
+        return B200_E_CUDA;
+    }
+    return B200_OK;
+}
+
+}  // namespace
+
+bool tc5_supported(const FattnArgs& a) {
+    if (a.hd != 64 && a.hd != 128) return false;
+    if (a.k.type != B200_TYPE_F16 || a.v.type != B200_TYPE_F16) return false;
+    if (!a.k.vec16 || !a.v.vec16) return false;
+    if (a.has_mask || a.relpos || a.softcap != 0.0f || a.n2 != 0) return false;
+    if (!(a.scale > 0.0f)) return false;
+    const int64_t lim = (int64_t)1 << 40;
+    if (a.k.nb1 <= 0 || a.k.nb2 <= 0 || a.k.nb3 <= 0 || a.v.nb1 <= 0 || a.v.nb2 <= 0 || a.v.nb3 <= 0) return false;
+    if (a.k.nb1 >= lim || a.k.nb2 >= lim || a.k.nb3 >= lim || a.v.nb1 >= lim || a.v.nb2 >= lim || a.v.nb3 >= lim) return false;
+    return true;
+}
+
+int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+    if (a.hd == 64) return launch_t<64, 2>(a, st, errbuf, errlen);
+    return launch_t<128, 1>(a, st, errbuf, errlen);
+}
+
+int tc5_read_status(int* status) {
+    int v = 0;
+    const cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc5_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    *status = v;
+    return 0;
+}
+
+}  // namespace b200

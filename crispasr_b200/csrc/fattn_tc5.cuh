@@ -11,4 +11,7 @@ bool tc5_supported(const FattnArgs& a);
 // Encodes the tensor maps and launches. Returns a B200_* code; on CUDA failure writes the text to errbuf.
 int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen);
 
+// Reads the device status word set when a bounded device-side wait ran out (0 = never). Returns a cudaError_t value.
+int tc5_read_status(int* status);
+
 }  // namespace b200

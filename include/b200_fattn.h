@@ -202,6 +202,15 @@ B200_API int b200_fattn_launch_static(const b200_tensor* q, const b200_tensor* k
                                       void* cuda_stream);
 B200_API size_t b200_fattn_static_scratch_bytes(void);
 
+/*
+ * b200_device_status — every wait inside the kernels (on an mbarrier that a TMA copy or a tensor-core
+ * commit completes) is bounded; a CTA whose wait runs out stops, releases its tensor memory and sets a
+ * status word on the device.  This reads that word on the current device: B200_OK, or
+ * B200_E_DEVICE_WAIT if any launch since load hit the limit (its output is then undefined).  Call it
+ * after synchronising the stream(s) of interest.  No reference counterpart (ggml aborts instead).
+ */
+B200_API int b200_device_status(void);
+
 /* The kernel family the calling thread's most recent successful launch used. */
 B200_API int b200_last_kernel(void);
 

@@ -107,6 +107,9 @@ def test_cfg3_large_v3_encoder_segments(b200, orc, kernel):
     q, k, v = (randn_f16(rng, (S, H, T, hd)) for _ in range(3))
     ref = orc.flash_attn_ext(q, k, v, scale=0.125)
     assert_close(gpu_op(b200, q, k, v, scale=0.125), ref, "cfg3 two segments")
+    if kernel == "auto":
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5, "the encoder prefill must run on the tcgen05 kernel"
+        assert b200.lib().b200_device_status() == 0
 
 
 # ---- config 4: Voxtral-style LLM decoder, GQA 32/8, hd 128, Q8_0 KV ------------------------------------------
