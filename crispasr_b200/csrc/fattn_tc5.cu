@@ -29,6 +29,13 @@ namespace b200 {
 
 __device__ int g_tc5_status = 0;  // 0 ok, 1 = a bounded wait ran out in some CTA
 
+#ifdef B200_TC5_TRACE
+__device__ long long g_tc5_trace[3][64][8];
+#define TC5_TRACE(role, j, k) do { if (blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == 0 && (j) < 64) g_tc5_trace[role][j][k] = clock64(); } while (0)
+#else
+#define TC5_TRACE(role, j, k) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kTile = 128;              // query rows per CTA and keys per step
@@ -36,7 +43,7 @@ constexpr int kPanelBytes = 128 * 128;  // 128 rows x 64 f16
 constexpr int kThreadsTc5 = 192;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: P <= 256 stays well inside f16 range
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -175,6 +182,53 @@ __device__ __forceinline__ uint4 q_chunk(const uint8_t* rowp, int type, int c0, 
     return out;
 }
 
+// {hi, lo} -> packed f16x2 with lo in the low half
+__device__ __forceinline__ uint32_t cvt_f16x2(float lo, float hi) {
+    uint32_t y;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
+    return y;
+}
+// Maximum of 64 score columns held in two 32-register chunks; columns >= n_valid (tile-relative) are skipped.
+__device__ __forceinline__ float row_max64(const uint32_t (&sreg)[2][32], int col0, int n_valid) {
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++)
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            const float sv = (col0 + q2 * 32 + i < n_valid) ? __uint_as_float(sreg[q2][i]) : -INFINITY;
+            mx[i & 3] = fmaxf(mx[i & 3], sv);
+        }
+    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
+// 64 score columns -> 32 packed f16x2 probabilities exp2(s*c - m); updates the running raw maximum and the
+// row sum (f16x2 partial sums of four pairs, widened to fp32).
+template <bool MASKED>
+__device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_t (&preg)[32], float c, float m_use,
+                                          int col0, int n_valid, float& mx_io, float& lsum_io) {
+    float mx[8];
+    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx[i] = -INFINITY;
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float s0 = __uint_as_float(sreg[q2][i]), s1 = __uint_as_float(sreg[q2][i + 1]);
+            if (MASKED) {
+                if (col0 + q2 * 32 + i >= n_valid) s0 = -INFINITY;
+                if (col0 + q2 * 32 + i + 1 >= n_valid) s1 = -INFINITY;
+            }
+            mx[(i >> 1) & 7] = fmaxf(mx[(i >> 1) & 7], fmaxf(s0, s1));
+            const float p0 = ex2(fmaf(s0, c, -m_use));
+            const float p1 = ex2(fmaf(s1, c, -m_use));
+            ls[(i >> 1) & 3] += p0 + p1;
+            preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
+        }
+    mx_io = fmaxf(mx_io, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))));
+    lsum_io += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+}
+
 struct Tc5Smem {
     // offsets from the 1024-byte aligned base of dynamic shared memory
     template <int HD, int NSTG>
@@ -227,6 +281,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     }
 
     // ---- set-up ----
+    if (tid == 0) TC5_TRACE(2, 60, 0);
     if (tid == 4 * 32) {
         for (int i = 0; i < NSTG; i++) {
             mbar_init(bar_k_full + 8 * i, 1);
@@ -241,6 +296,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+        // the first NSTG tiles need no empty-slot wait: start their copies before the CTA-wide set-up barrier
+        for (int j = 0; j < NSTG && j < n_tiles; j++) {
+            mbar_arrive_expect_tx(bar_k_full + 8 * j, TILE_BYTES);
+#pragma unroll
+            for (int p = 0; p < PANELS; p++)
+                tma_load_4d(sK + j * TILE_BYTES + p * kPanelBytes, &tmK, bar_k_full + 8 * j, p * 64, j * kTile, hk, bk);
+            mbar_arrive_expect_tx(bar_v_full + 8 * j, TILE_BYTES);
+#pragma unroll
+            for (int p = 0; p < PANELS; p++)
+                tma_load_4d(sV + j * TILE_BYTES + p * kPanelBytes, &tmV, bar_v_full + 8 * j, p * 64, j * kTile, hk, bk);
+        }
     }
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem_base))),
@@ -267,6 +333,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem_base;
+    if (tid == 0) TC5_TRACE(2, 60, 1);
     const uint32_t tmem_S = tmem_base;            // cols [0,128)
     const uint32_t tmem_P = tmem_base;            // cols [0,64), f16x2
     const uint32_t tmem_O = tmem_base + kTile;    // cols [128,128+HD)
@@ -275,19 +342,21 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         // ================= TMA producer =================
         if (lane == 0) {
             bool ok = true;
-            int issued_k = 0, issued_v = 0;
-            for (int j = 0; j < n_tiles && ok; j++) {
+            int issued_k = min(NSTG, n_tiles), issued_v = min(NSTG, n_tiles);
+            for (int j = NSTG; j < n_tiles && ok; j++) {
                 const int slot = j % NSTG, use = j / NSTG;
                 const int k0 = j * kTile;
-                if (use > 0) ok = mbar_wait(bar_k_empty + 8 * slot, (use - 1) & 1, s_abort);
+                ok = mbar_wait(bar_k_empty + 8 * slot, (use - 1) & 1, s_abort);
                 if (!ok) break;
+                TC5_TRACE(2, j, 0);
                 mbar_arrive_expect_tx(bar_k_full + 8 * slot, TILE_BYTES);
 #pragma unroll
                 for (int p = 0; p < PANELS; p++)
                     tma_load_4d(sK + slot * TILE_BYTES + p * kPanelBytes, &tmK, bar_k_full + 8 * slot, p * 64, k0, hk, bk);
                 issued_k = j + 1;
-                if (use > 0) ok = mbar_wait(bar_v_empty + 8 * slot, (use - 1) & 1, s_abort);
+                ok = mbar_wait(bar_v_empty + 8 * slot, (use - 1) & 1, s_abort);
                 if (!ok) break;
+                TC5_TRACE(2, j, 1);
                 mbar_arrive_expect_tx(bar_v_full + 8 * slot, TILE_BYTES);
 #pragma unroll
                 for (int p = 0; p < PANELS; p++)
@@ -304,32 +373,54 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         }
     } else if (warp == 5) {
         // ================= MMA issuer =================
+        // Order: S[0]; then per tile j: (barriers of tile j+1 are awaited while the softmax of tile j runs)
+        // wait P[j] -> PV[j] -> S[j+1], back to back, so the softmax threads of the next tile wake as early
+        // as the tensor pipe allows.  S[j+1] overwrites the columns P[j] lives in; tcgen05.mma executes in
+        // issue order, so PV[j] has consumed P[j] before S[j+1] writes.
         if (lane == 0) {
-            bool ok = true;
-            for (int j = 0; j < n_tiles && ok; j++) {
-                const int slot = j % NSTG, use = j / NSTG;
-                ok = mbar_wait(bar_k_full + 8 * slot, use & 1, s_abort);
-                if (!ok) break;
+            bool ok = mbar_wait(bar_k_full, 0, s_abort);
+            if (ok) {
+                TC5_TRACE(1, 0, 0);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-                    mma_ss(tmem_S, smem_desc(sQ + off, 16, 1024), smem_desc(sK + slot * TILE_BYTES + off, 16, 1024),
-                           IDESC_S, ks > 0 ? 1u : 0u);
+                    mma_ss(tmem_S, smem_desc(sQ + off, 16, 1024), smem_desc(sK + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(bar_s_full);
-                tc_commit(bar_k_empty + 8 * slot);
+                tc_commit(bar_k_empty);
+                TC5_TRACE(1, 0, 1);
+            }
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int slot = j % NSTG, use = j / NSTG;
+                const int nslot = (j + 1) % NSTG, nuse = (j + 1) / NSTG;
+                const bool more = j + 1 < n_tiles;
+                ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
+                if (ok && more) ok = mbar_wait(bar_k_full + 8 * nslot, nuse & 1, s_abort);
+                if (!ok) break;
+                TC5_TRACE(1, j, 2);
                 ok = mbar_wait(bar_p_ready, j & 1, s_abort);
                 if (!ok) break;
-                ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
-                if (!ok) break;
+                TC5_TRACE(1, j, 3);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kTile / 16; ks++)
                     mma_ts(tmem_O, tmem_P + ks * 8, smem_desc(sV + slot * TILE_BYTES + ks * 2048, kPanelBytes, 1024),
                            IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(bar_v_empty + 8 * slot);
-                if (j == n_tiles - 1) tc_commit(bar_o_done);
+                if (more) {
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ks++) {
+                        const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+                        mma_ss(tmem_S, smem_desc(sQ + off, 16, 1024), smem_desc(sK + nslot * TILE_BYTES + off, 16, 1024),
+                               IDESC_S, ks > 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar_s_full);
+                    tc_commit(bar_k_empty + 8 * nslot);
+                } else {
+                    tc_commit(bar_o_done);
+                }
+                TC5_TRACE(1, j, 4);
             }
             if (!ok) {
                 // make sure no MMA of this CTA is still running before TMEM is released
@@ -350,33 +441,51 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         for (int j = 0; j < n_tiles; j++) {
             ok = mbar_wait(bar_s_full, j & 1, s_abort);
             if (!ok) break;
+            if (tid == 0) TC5_TRACE(0, j, 0);
             tc_fence_after();
-            const int n_valid = kend - j * kTile;  // columns >= n_valid are masked
-            // pass 1: row maximum (two 64-column halves; S is read again in pass 2 to keep registers low)
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            const int n_valid = kend - j * kTile;  // columns >= n_valid of this row are masked
+            const bool full_tile = __all_sync(0xffffffffu, n_valid >= kTile);
+            if (j == 0) {
+                // first tile: the reference maximum is the tile maximum (max-only pass over S)
+                float mx = -INFINITY;
 #pragma unroll
-            for (int hh = 0; hh < 2; hh++) {
-                uint32_t sreg[2][32];
-                tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
-                tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
-                tmem_wait_ld();
-#pragma unroll
-                for (int q2 = 0; q2 < 2; q2++)
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        float sv = __uint_as_float(sreg[q2][i]);
-                        if (hh * 64 + q2 * 32 + i >= n_valid) sv = -INFINITY;
-                        mx[i & 3] = fmaxf(mx[i & 3], sv);
-                    }
+                for (int hh = 0; hh < 2; hh++) {
+                    uint32_t sreg[2][32];
+                    tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                    tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                    tmem_wait_ld();
+                    mx = fmaxf(mx, row_max64(sreg, hh * 64, full_tile ? 2 * kTile : n_valid));
+                }
+                m_ref = mx * c;  // c > 0
             }
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c;  // c > 0
-            // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
-            const bool grow = m_tile > m_ref + kRescaleThreshold;  // also true for -inf -> finite
-            if (__any_sync(0xffffffffu, grow)) {
+            uint32_t preg[2][32];
+            float lsum = 0.0f;
+            for (int attempt = 0; attempt < 2; attempt++) {
+                // P = exp2(S*c - m_ref), rounded to f16x2; the tile maximum is tracked in the same pass and
+                // only checked afterwards (lazy rescale).
+                const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+                float mx = -INFINITY;
+                lsum = 0.0f;
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    uint32_t sreg[2][32];
+                    tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                    tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                    tmem_wait_ld();
+                    if (tid == 0) TC5_TRACE(0, j, 3 + 2 * hh);
+                    if (full_tile) softmax64<false>(sreg, preg[hh], c, m_use, 0, 0, mx, lsum);
+                    else softmax64<true>(sreg, preg[hh], c, m_use, hh * 64, n_valid, mx, lsum);
+                    if (tid == 0) TC5_TRACE(0, j, 4 + 2 * hh);
+                }
+                if (tid == 0 && attempt == 1) TC5_TRACE(0, j, 7);
+                const float m_tile = mx * c;
+                const bool grow = m_tile > m_ref + kRescaleThreshold;
+                if (!__any_sync(0xffffffffu, grow)) break;
+                // some row of this warp outgrew its reference maximum: rescale O and l, then redo P
                 const float m_new = fmaxf(m_ref, m_tile);
+                const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
+                l_run *= alpha;
                 if (j > 0) {
-                    const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
-                    l_run *= alpha;
 #pragma unroll
                     for (int q4 = 0; q4 < HD / 32; q4++) {
                         uint32_t oreg[32];
@@ -389,36 +498,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 }
                 m_ref = m_new;
             }
-            const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-            // pass 2: P = exp2(S*c - m), packed f16x2, written over the columns of S already consumed
-            float lsum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int hh = 0; hh < 2; hh++) {
-                uint32_t sreg[2][32];
-                uint32_t preg[32];
-                tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
-                tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
-                tmem_wait_ld();
-#pragma unroll
-                for (int q2 = 0; q2 < 2; q2++)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int col = hh * 64 + q2 * 32 + i;
-                        float p0 = ex2(fmaf(__uint_as_float(sreg[q2][i]), c, -m_use));
-                        float p1 = ex2(fmaf(__uint_as_float(sreg[q2][i + 1]), c, -m_use));
-                        if (col >= n_valid) p0 = 0.0f;
-                        if (col + 1 >= n_valid) p1 = 0.0f;
-                        lsum[(i >> 1) & 3] += p0 + p1;
-                        preg[q2 * 16 + (i >> 1)] = pack_half2(p0, p1);
-                    }
-                tmem_st32(tmem_P + lane_base + hh * 32, preg);
-            }
-            l_run += (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
+            l_run += lsum;
+            if (tid == 0) TC5_TRACE(0, j, 1);
+            tmem_st32(tmem_P + lane_base, preg[0]);
+            tmem_st32(tmem_P + lane_base + 32, preg[1]);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_p_ready);
+            if (tid == 0) TC5_TRACE(0, j, 2);
         }
         if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
+        if (tid == 0) TC5_TRACE(2, 60, 2);
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
@@ -440,6 +530,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     }
 
     // ---- teardown ----
+    if (tid == 0) TC5_TRACE(2, 60, 3);
     tc_fence_before();
     __syncthreads();
     if (warp == 5) {
@@ -520,6 +611,12 @@ int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t
     if (a.hd == 64) return launch_t<64, 2>(a, st, errbuf, errlen);
     return launch_t<128, 1>(a, st, errbuf, errlen);
 }
+
+#ifdef B200_TC5_TRACE
+extern "C" __attribute__((visibility("default"))) int b200_dbg_trace(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tc5_trace, sizeof(long long) * 3 * 64 * 8);
+}
+#endif
 
 int tc5_read_status(int* status) {
     int v = 0;
