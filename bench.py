@@ -191,7 +191,7 @@ def run_reference(args, w, rank, world):
 def config_of(args, w, units):
     return {"workload": args.workload, "layers": w["layers"], f"{w['unit_name']}_per_gpu": units, "heads": w["H"],
             "kv_heads": w["Hkv"], "head_dim": w["hd"], "q_len": w["Tq"], "kv_len": w["Lk"], "kv_type": w["kv"],
-            "q_type": "f16", "sharding": "units across GPUs, no collective",
+            "q_type": "f16", "sharding": "units across GPUs, no collective", "launch": "python loop" if args.no_graph else "cuda graph of one step",
             "l2": "inputs of one launch exceed L2" if w["kind"] == "prefill" else "L2 flushed between steps"}
 
 
@@ -206,6 +206,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernel", default="auto", choices=["auto", "tile"])
+    ap.add_argument("--no-graph", action="store_true", help="launch each layer from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -243,6 +244,15 @@ def main():
         t = t.repeat((rep,) + (1,) * (t.dim() - 1))[:units].contiguous()
         return t
     q, k, v = up(q_np), up(k_np), up(v_np)
+    if w["kind"] == "decode":
+        # K/V live in cache slabs as the allocator lays them out: head-major rows, the row count per head
+        # rounded up to 32 so every head starts 16-byte aligned; the op sees a view of the first Lk rows.
+        ctx_rows = -(-w["Lk"] // 32) * 32
+        def slab(t):
+            buf = torch.zeros(t.shape[:2] + (ctx_rows, t.shape[3]), dtype=t.dtype, device=dev)
+            buf[:, :, : w["Lk"]] = t
+            return buf[:, :, : w["Lk"]]
+        k, v = slab(k), slab(v)
     kw = dict(scale=scale_of(w))
     if w["kv"] == "q8_0":
         kw["kv_type"] = abi.Q8_0
@@ -264,8 +274,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    step()                      # first call outside any capture (function attributes, tensor maps, lazy init)
+    torch.cuda.synchronize()
+    run_step = step
+    if not args.no_graph:
+        # the layer loop is launch-bound from Python for the small decode shapes: capture one step
+        # (all layers) into a CUDA graph and replay it, as a runtime would
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run_step = graph.replay
     for _ in range(max(args.warmup, 0)):
-        step()
+        run_step()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -276,7 +296,7 @@ def main():
         if flush is not None:
             flush.fill_(s & 0xFF)        # evict L2 between steps (outside the event pair)
         ev[s][0].record()
-        step()
+        run_step()
         ev[s][1].record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -293,7 +313,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         e2e_units = min(units, 16 if w["kind"] == "prefill" else units)
-        hq, hk, hv = (x[:e2e_units].cpu().pin_memory() for x in (q, k, v))
+        hq, hk, hv = (x[:e2e_units].contiguous().cpu().pin_memory() for x in (q, k, v))
         hkw = dict(kw)
         if w["kind"] == "relpos":
             hkw["q_v"], hkw["r"] = kw["q_v"][:e2e_units].cpu().pin_memory(), kw["r"].cpu().pin_memory()

@@ -53,6 +53,20 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Raises a kernel's dynamic shared memory limit once per (kernel instantiation, device): the attribute call is
+// kept out of the steady-state launch path (and out of stream captures after the first launch).
+// `done` is a static flag array owned by the calling launcher instantiation (one per kernel instantiation).
+template <typename Kern>
+inline cudaError_t set_smem_once(Kern kern, size_t smem, bool (&done)[64]) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+    return e;
+}
+
 // Launchers implemented per kernel family; each returns a cudaError_t-compatible int (0 = ok).
 int launch_tile_mma(const FattnArgs& a, cudaStream_t st);
 int launch_decode_split(const FattnArgs& a, cudaStream_t st);

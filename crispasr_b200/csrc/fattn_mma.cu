@@ -315,7 +315,8 @@ int launch_tile_t(const FattnArgs& a, cudaStream_t st) {
     size_t smem = (size_t)(64 + 64 + 64) * HD * sizeof(__half);
     if (RELPOS) smem += (size_t)(64 + 128) * HD * sizeof(__half) + 4 * 16 * kXStride * sizeof(float);
     auto kern = fattn_tile_mma_kernel<HD, RELPOS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(kern, smem, smem_set);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((a.Tq + 63) / 64, a.H, a.B);
     kern<<<grid, kThreads, smem, st>>>(a);
@@ -328,13 +329,98 @@ int launch_tile_t(const FattnArgs& a, cudaStream_t st) {
 constexpr int kDecRows = 16;
 constexpr int kDecBN = 64;
 
+// How a decode CTA brings K/V tiles into shared memory.
+enum DecodeMode {
+    kDecSync = 0,    // element loads + conversion (F32 K/V, unaligned or gapped layouts)
+    kDecAsyncF16 = 1,  // cp.async 16-byte copies of F16 rows into a multi-stage ring
+    kDecAsyncQ8 = 2    // cp.async of the raw Q8_0 byte range of a tile, then a shared-to-shared dequantise
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;  // src-size 0 zero-fills the 16 destination bytes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// cp.async copy of rows [row0, row0+64) x HD halves into a swizzled fp16 tile; rows >= row_hi are zero-filled.
 template <int HD>
+__device__ __forceinline__ void issue_tile_f16(__half* sm, const uint8_t* base, int64_t nb1, int row0, int row_hi, int tid) {
+    constexpr int CPR = HD / 8;
+#pragma unroll
+    for (int it = 0; it < kDecBN * CPR / kThreads; it++) {
+        const int idx = tid + it * kThreads;
+        const int row = idx / CPR, ch = idx % CPR;
+        const int grow = row0 + row;
+        const bool valid = grow < row_hi;
+        cp_async16(tile_addr<HD>(sm, row, ch), base + (valid ? (int64_t)grow * nb1 + ch * 16 : 0), valid);
+    }
+}
+
+// cp.async copy of the contiguous raw byte range of Q8_0 rows [row0, row0+64): 64 * (HD/32*34) bytes.
+template <int HD>
+__device__ __forceinline__ void issue_tile_q8raw(uint8_t* sm, const uint8_t* base, int row0, int row_hi, int tid) {
+    constexpr int RB = HD / 32 * 34;
+    constexpr int CHUNKS = kDecBN * RB / 16;
+    const int64_t byte0 = (int64_t)row0 * RB;
+    const int64_t byte_hi = (int64_t)row_hi * RB;  // bytes at or beyond this belong to rows that are not read
+    for (int idx = tid; idx < CHUNKS; idx += kThreads) {
+        const int64_t off = byte0 + (int64_t)idx * 16;
+        const bool valid = off < byte_hi;  // a chunk straddling row_hi is still inside the allocation (rows < Lk)
+        cp_async16(smem_u32(sm) + idx * 16, base + (valid ? off : 0), valid);
+    }
+}
+
+// Raw Q8_0 tile (64 rows of HD/32 blocks) in shared memory -> swizzled fp16 tile. x = fp16(d * q): the product of
+// an 11-bit and a 7-bit significand is exact before the single rounding, i.e. equal to fp32(d)*q rounded to fp16.
+template <int HD>
+__device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, int rows_valid, int tid) {
+    constexpr int NBLK = HD / 32, RB = NBLK * 34;
+    for (int idx = tid; idx < kDecBN * NBLK; idx += kThreads) {
+        const int row = idx / NBLK, blk = idx % NBLK;
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(raw + row * RB + blk * 34);
+        if (row >= rows_valid) {  // rows past the valid length read as zeros whatever the copy brought in
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++)
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * (HD / 8) + swz<HD>(row, blk * 4 + c4)) * 16) =
+                    make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
+        const __half d = *reinterpret_cast<const __half*>(src);
+        const __half2 d2 = __half2half2(d);
+        const __half2 bias = __float2half2_rn(1152.0f);
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {  // four 16-byte output chunks of 8 halves
+            uint32_t out[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t w = src[1 + c4 * 4 + i] ^ 0x8080u;  // two int8 -> biased uint8
+                // halves 0x64xx = 1024 + xx; minus 1152 gives the signed value exactly
+                const uint32_t h2 = 0x64006400u | (w & 0xFFu) | ((w & 0xFF00u) << 8);
+                const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&h2), bias), d2);
+                out[i] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * (HD / 8) + swz<HD>(row, blk * 4 + c4)) * 16) =
+                make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+}
+
+template <int HD, int MODE>
 __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const FattnArgs a) {
+    constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
+    constexpr int RAW_BYTES = kDecBN * (HD / 32 * 34);    // one raw Q8_0 K or V tile
+    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 3);
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    __half* sQ = reinterpret_cast<__half*>(smem_raw);      // [16][HD]
-    __half* sK = sQ + kDecRows * HD;                        // [64][HD]
-    __half* sV = sK + kDecBN * HD;                          // [64][HD]
-    float* sO = reinterpret_cast<float*>(sK);               // [16][HD] fp32, reused after the key loop
+    __half* sQ = reinterpret_cast<__half*>(smem_raw);              // [16][HD]
+    // fp16 tiles: NS stages (async F16) or one pair (sync, Q8)
+    __half* sKV = sQ + kDecRows * HD;
+    constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
+    uint8_t* sRaw = reinterpret_cast<uint8_t*>(sKV + F16_STAGES * 2 * TILE_HALVES);  // Q8: NS stages of raw K|V
+    float* sO = reinterpret_cast<float*>(sKV);                      // [16][HD] fp32, reused after the key loop
     __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -342,6 +428,33 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
     const int bk = b / a.bq;
     const int R = a.Tq * a.gqa;  // <= 16; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
     const float ninf = -INFINITY;
+
+    const int len_b = clamp_len(a, b);
+    int kmax = len_b;
+    if (a.causal) kmax = min(kmax, a.n_past + a.Tq);
+    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
+    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
+    const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
+    const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
+
+    auto issue = [&](int tile) {
+        if (tile < tile_hi) {
+            const int stage = (tile - tile_lo) % NS;
+            if (MODE == kDecAsyncF16) {
+                issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid);
+                issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid);
+            } else if (MODE == kDecAsyncQ8) {
+                issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES, kbase, tile * kDecBN, len_b, tid);
+                issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, vbase, tile * kDecBN, len_b, tid);
+            }
+        }
+        cp_async_commit();
+    };
+    if (MODE != kDecSync) {
+#pragma unroll
+        for (int s0 = 0; s0 < NS - 1; s0++) issue(tile_lo + s0);
+    }
 
     // Q rows (tiny): one 8-element chunk per loop step
     for (int idx = tid; idx < kDecRows * (HD / 8); idx += kThreads) {
@@ -359,29 +472,19 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ks++) ldsm_x4(qf[ks], tile_addr<HD>(sQ, lane & 15, ks * 2 + (lane >> 4)));
 
-    const int len_b = clamp_len(a, b);
-    int kmax = len_b;
-    if (a.causal) kmax = min(kmax, a.n_past + a.Tq);
-    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
-    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
-    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
-
-    const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
-    const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
-
     // per-thread row metadata for rows g and g+8
-    int row_iq[2], row_h[2];
+    int row_iq[2];
     float row_slope[2];
     const uint8_t* row_mask[2];
 #pragma unroll
     for (int rI = 0; rI < 2; rI++) {
         const int rr = g + rI * 8;
         row_iq[rI] = rr / a.gqa;
-        row_h[rI] = hk * a.gqa + rr % a.gqa;
-        row_slope[rI] = alibi_slope(a, row_h[rI]);
+        const int hq = hk * a.gqa + rr % a.gqa;
+        row_slope[rI] = alibi_slope(a, hq);
         row_mask[rI] = (a.has_mask && rr < R)
-                           ? a.mask.p + (int64_t)row_iq[rI] * a.mask.nb1 +
-                                 (int64_t)(row_h[rI] % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
+                           ? a.mask.p + (int64_t)row_iq[rI] * a.mask.nb1 + (int64_t)(hq % a.mask_ne2) * a.mask.nb2 +
+                                 (int64_t)(b % a.mask_ne3) * a.mask.nb3
                            : nullptr;
     }
 
@@ -392,10 +495,29 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
 
     for (int tile = tile_lo; tile < tile_hi; tile++) {
         const int k0 = tile * kDecBN;
-        __syncthreads();
-        load_tile<HD, kDecBN>(sK, kbase, a.k.nb1, a.k.type, a.k.vec16, k0, 0, len_b, a.hd, tid);
-        load_tile<HD, kDecBN>(sV, vbase, a.v.nb1, a.v.type, a.v.vec16, k0, 0, len_b, a.hd, tid);
-        __syncthreads();
+        const __half *sK, *sV;
+        if (MODE == kDecSync) {
+            __syncthreads();
+            load_tile<HD, kDecBN>(sKV, kbase, a.k.nb1, a.k.type, a.k.vec16, k0, 0, len_b, a.hd, tid);
+            load_tile<HD, kDecBN>(sKV + TILE_HALVES, vbase, a.v.nb1, a.v.type, a.v.vec16, k0, 0, len_b, a.hd, tid);
+            __syncthreads();
+            sK = sKV, sV = sKV + TILE_HALVES;
+        } else if (MODE == kDecAsyncF16) {
+            cp_async_wait<NS - 2>();
+            __syncthreads();             // tile `tile` has landed for every thread; stage of tile-1 is free
+            issue(tile + NS - 1);
+            const int stage = (tile - tile_lo) % NS;
+            sK = sKV + stage * 2 * TILE_HALVES, sV = sK + TILE_HALVES;
+        } else {
+            cp_async_wait<NS - 2>();
+            __syncthreads();             // raw tile landed; everybody is done with the previous fp16 tiles
+            const int stage = (tile - tile_lo) % NS;
+            dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES, sKV, len_b - k0, tid);
+            dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, sKV + TILE_HALVES, len_b - k0, tid);
+            __syncthreads();
+            issue(tile + NS - 1);        // overwrites the raw stage of tile-1, which was dequantised an iteration ago
+            sK = sKV, sV = sKV + TILE_HALVES;
+        }
 
         // this warp's 16 keys: k0 + 16*warp ..
         float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
@@ -455,9 +577,10 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
             mma16816(o[2 * np + 1], pf, bf[2], bf[3]);
         }
     }
+    if (MODE != kDecSync) cp_async_wait<0>();
 
     // ---- merge the four warps' (m, l, O) in shared memory ----
-    __syncthreads();  // all warps are done with sK/sV
+    __syncthreads();  // all warps are done with the K/V tiles
     const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
     if (t == 0) {
         s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
@@ -548,11 +671,15 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
     }
 }
 
-template <int HD>
-int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
-    const size_t smem = (size_t)(kDecRows + 2 * kDecBN) * HD * sizeof(__half);
-    auto kern = fattn_decode_split_kernel<HD>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int HD, int MODE>
+int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
+    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 3);
+    constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
+    size_t smem = (size_t)(kDecRows + F16_STAGES * 2 * kDecBN) * HD * sizeof(__half);
+    if (MODE == kDecAsyncQ8) smem += (size_t)NS * 2 * kDecBN * (HD / 32 * 34);
+    auto kern = fattn_decode_split_kernel<HD, MODE>;
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(kern, smem, smem_set);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(a.n_splits, a.Hkv, a.B);
     kern<<<grid, kThreads, smem, st>>>(a);
@@ -564,6 +691,34 @@ int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
         e = cudaGetLastError();
     }
     return (int)e;
+}
+
+// Which staging mode the operands allow.
+int decode_mode(const FattnArgs& a, int hdp) {
+    if (a.hd != hdp) return kDecSync;  // zero-padded head dims take the element path
+    if (a.k.type == B200_TYPE_F16 && a.k.vec16 && a.v.vec16) return kDecAsyncF16;
+    if (a.k.type == B200_TYPE_Q8_0) {
+        const int64_t rb = a.hd / 32 * 34;
+        const bool contiguous_rows = a.k.nb1 == rb && a.v.nb1 == rb;
+        const bool aligned = ((uintptr_t)a.k.p % 16 == 0) && ((uintptr_t)a.v.p % 16 == 0) && a.k.nb2 % 16 == 0 &&
+                             a.k.nb3 % 16 == 0 && a.v.nb2 % 16 == 0 && a.v.nb3 % 16 == 0;
+        // the last 16-byte chunk of a tile may reach past row Lk-1 by < 16 bytes only if rows*rb is not a
+        // multiple of 16; chunks are issued per tile of 64 rows (64*rb is a multiple of 16) and chunks that
+        // start at or beyond row kv_len are zero-filled, so reads stay inside rows [0, Lk) when Lk*rb % 16 == 0
+        // or the head slab continues behind row Lk-1 (nb2 > Lk*rb).
+        const bool tail_ok = ((int64_t)a.Lk * rb) % 16 == 0 || a.k.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16;
+        if (contiguous_rows && aligned && tail_ok && a.v.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16) return kDecAsyncQ8;
+    }
+    return kDecSync;
+}
+
+template <int HD>
+int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
+    switch (decode_mode(a, HD)) {
+        case kDecAsyncF16: return launch_decode_m<HD, kDecAsyncF16>(a, st);
+        case kDecAsyncQ8: return launch_decode_m<HD, kDecAsyncQ8>(a, st);
+        default: return launch_decode_m<HD, kDecSync>(a, st);
+    }
 }
 
 }  // namespace

@@ -580,7 +580,8 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
     const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 24 + 16;
     auto kern = fattn_prefill_tc5_kernel<HD, NSTG>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(kern, smem, smem_set);
     if (e == cudaSuccess) {
         dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
         kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
