@@ -539,6 +539,368 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     }
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Relative-position variant (FastConformer, head_dim 128): logits = scale*Q_u.K^T + f16(scale * relshift(Q_v.R^T)).
+//
+// Per 128x128 tile the bias needs X = Q_v[128 x hd] . R_band[256 x hd]^T with R_band = R rows
+// [rb, rb+256), rb = (Tq-1) + k0 - q0 - 127; the bias of (row i, key j) is X[i][j - i + 127] (the rel-shift).
+// X is one more accumulator in TMEM (256 columns; S 128, O 128 -> all 512 columns, one CTA per SM).
+// A tcgen05.ld reads the same columns for every lane, so the per-row shift cannot be done in the load:
+// each softmax thread loads the 96 columns its warp can need for half a tile, rounds scale*x to f16 (the
+// reference's rounding point), parks them in its own row of a shared-memory buffer and reads 64 of them
+// back from its row-dependent offset.  Only the thread itself touches its row: no barrier is involved.
+// Consecutive KV tiles share half of the band, so R arrives in 128-row half-blocks through a 2-slot ring
+// (half-block m = rows rb_0 + 128m ..; tile j uses half-blocks j and j+1).
+// MMA order: X[0] S[0] | per tile j: X[j+1] as soon as the softmax threads have drained X[j]; then, once
+// P[j] is in TMEM, PV[j] and S[j+1].
+// ------------------------------------------------------------------------------------------------------
+constexpr int kBncStride = 208;  // bytes per bounce row: 96 halves + 16 bytes of padding (conflict-free 16-byte stores)
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_b32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreadsTc5, 1)
+fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
+                                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmR) {
+    constexpr int HD = 128;
+    constexpr int TILE_BYTES = 2 * kPanelBytes;  // 128 rows x 128 halves
+    constexpr uint32_t IDESC_S = idesc_f16(kTile, false);   // also used for each 128-column half of X
+    constexpr uint32_t IDESC_PV = idesc_f16(HD, true);
+
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+    const uint32_t sQ = smem_base, sQv = sQ + TILE_BYTES, sK = sQv + TILE_BYTES, sV = sK + TILE_BYTES,
+                   sR = sV + TILE_BYTES, sBnc = sR + 2 * TILE_BYTES, sBar = sBnc + kTile * kBncStride;
+    const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8, bar_v_full = sBar + 16, bar_v_empty = sBar + 24,
+                   bar_r_full = sBar + 32 /* [2] */, bar_r_empty = sBar + 48 /* [2] */, bar_s_full = sBar + 64,
+                   bar_x_full = sBar + 72, bar_x_free = sBar + 80, bar_p_ready = sBar + 88, bar_o_done = sBar + 96;
+    uint8_t* misc = smem_gen + 6 * TILE_BYTES + kTile * kBncStride + 104;
+    volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * kTile, h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / a.gqa, bk = b / a.bq;
+    const int rb3 = a.r_ne3 > 1 ? b : 0;
+
+    int len_b = a.Lk;
+    if (a.kv_len) {
+        const int v = a.kv_len[b];
+        len_b = v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
+    }
+    const int n_tiles = len_b > 0 ? (len_b + kTile - 1) / kTile : 0;
+    if (n_tiles == 0) {
+        if (tid < kTile && q0 + tid < a.Tq) {
+            float4* out = reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + q0 + tid) * a.H + h) * HD);
+#pragma unroll
+            for (int i = 0; i < HD / 4; i++) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
+    const int rb0 = a.Tq - 1 - q0 - 127;  // first R row of half-block 0 (may be negative: TMA zero-fills)
+
+    // half-block m of R -> ring slot m % 2 (two 64-column panels of 128 rows)
+    auto load_r = [&](int m) {
+        const int slot = m & 1;
+        mbar_arrive_expect_tx(bar_r_full + 8 * slot, TILE_BYTES);
+        tma_load_4d(sR + slot * TILE_BYTES, &tmR, bar_r_full + 8 * slot, 0, rb0 + kTile * m, h, rb3);
+        tma_load_4d(sR + slot * TILE_BYTES + kPanelBytes, &tmR, bar_r_full + 8 * slot, 64, rb0 + kTile * m, h, rb3);
+    };
+    auto load_kv = [&](int j, bool is_v) {
+        const uint32_t bar = is_v ? bar_v_full : bar_k_full;
+        const uint32_t dst = is_v ? sV : sK;
+        mbar_arrive_expect_tx(bar, TILE_BYTES);
+        tma_load_4d(dst, is_v ? &tmV : &tmK, bar, 0, j * kTile, hk, bk);
+        tma_load_4d(dst + kPanelBytes, is_v ? &tmV : &tmK, bar, 64, j * kTile, hk, bk);
+    };
+
+    // ---- set-up ----
+    if (tid == 4 * 32) {
+        for (int i = 0; i < 13; i++) {
+            const uint32_t bar = sBar + 8 * i;
+            mbar_init(bar, (bar == bar_x_free || bar == bar_p_ready) ? kTile : 1);
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmR)) : "memory");
+        load_r(0);
+        load_r(1);
+        load_kv(0, false);
+        load_kv(0, true);
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem_base))),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp < 4) {
+        const int r = tid;
+        const int iq = q0 + r;
+#pragma unroll
+        for (int which = 0; which < 2; which++) {
+            const View& qv = which ? a.qv : a.q;
+            const uint8_t* rowp = qv.p + (int64_t)iq * qv.nb1 + (int64_t)h * qv.nb2 + (int64_t)b * qv.nb3;
+            uint8_t* dst_row = smem_gen + which * TILE_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < HD / 8; c++) {
+                uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                if (iq < a.Tq) val = q_chunk(rowp, qv.type, c * 8, qv.vec16 != 0);
+                *reinterpret_cast<uint4*>(dst_row + (c >> 3) * kPanelBytes + (((c & 7) ^ (r & 7)) << 4)) = val;
+            }
+        }
+        fence_proxy_async();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem_base;
+    const uint32_t tmem_S = tmem_base, tmem_P = tmem_base, tmem_O = tmem_base + 128, tmem_X = tmem_base + 256;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            bool ok = true;
+            for (int j = 1; j < n_tiles && ok; j++) {
+                // half-block j+1 goes into the slot half-block j-1 leaves once X[j-1] has been computed
+                ok = mbar_wait(bar_r_empty + 8 * ((j + 1) & 1), (((j - 1) >> 1)) & 1, s_abort);
+                if (!ok) break;
+                load_r(j + 1);
+                ok = mbar_wait(bar_k_empty, (j - 1) & 1, s_abort);
+                if (!ok) break;
+                load_kv(j, false);
+                ok = mbar_wait(bar_v_empty, (j - 1) & 1, s_abort);
+                if (!ok) break;
+                load_kv(j, true);
+            }
+            if (!ok) {  // drain: bounded wait for copies still in flight
+                for (uint32_t it = 0; it < 65536; ++it) __nanosleep(64);
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            auto issue_x = [&](int j) {  // X[j] from half-blocks j (columns 0..127) and j+1 (columns 128..255)
+#pragma unroll
+                for (int hb = 0; hb < 2; hb++) {
+                    const uint32_t rslot = sR + ((j + hb) & 1) * TILE_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ks++) {
+                        const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+                        mma_ss(tmem_X + hb * 128, smem_desc(sQv + off, 16, 1024), smem_desc(rslot + off, 16, 1024), IDESC_S,
+                               ks > 0 ? 1u : 0u);
+                    }
+                }
+                tc_commit(bar_x_full);
+                tc_commit(bar_r_empty + 8 * (j & 1));
+            };
+            auto issue_s = [&]() {
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+                    mma_ss(tmem_S, smem_desc(sQ + off, 16, 1024), smem_desc(sK + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_s_full);
+                tc_commit(bar_k_empty);
+            };
+            bool ok = mbar_wait(bar_r_full, 0, s_abort) && mbar_wait(bar_r_full + 8, 0, s_abort) &&
+                      mbar_wait(bar_k_full, 0, s_abort);
+            if (ok) {
+                tc_fence_after();
+                issue_x(0);
+                issue_s();
+            }
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const bool more = j + 1 < n_tiles;
+                if (more) {
+                    // X[j+1] needs half-block j+2 (slot j%2, its (j+2)/2-th use) and the X columns drained
+                    ok = mbar_wait(bar_r_full + 8 * (j & 1), ((j + 2) >> 1) & 1, s_abort) &&
+                         mbar_wait(bar_x_free, j & 1, s_abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_x(j + 1);
+                }
+                ok = mbar_wait(bar_v_full, j & 1, s_abort);
+                if (ok && more) ok = mbar_wait(bar_k_full, (j + 1) & 1, s_abort);
+                if (ok) ok = mbar_wait(bar_p_ready, j & 1, s_abort);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kTile / 16; ks++)
+                    mma_ts(tmem_O, tmem_P + ks * 8, smem_desc(sV + ks * 2048, kPanelBytes, 1024), IDESC_PV,
+                           (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(bar_v_empty);
+                if (more) issue_s();
+                else tc_commit(bar_o_done);
+            }
+            if (!ok) {
+                tc_commit(bar_o_done);
+                for (uint32_t it = 0; it < 65536 && !mbar_try_wait(bar_o_done, 0); ++it) __nanosleep(256);
+            }
+        }
+    } else {
+        // ================= softmax / bias / epilogue =================
+        const int r = tid;
+        const int iq = q0 + r;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = a.scale * kLog2e;
+        const float bscale = a.relscale;
+        const int shift = 31 - lane;                        // band offset of this row inside the warp's columns
+        const uint32_t bnc_row = sBnc + r * kBncStride;
+        const uint32_t bnc_rd = bnc_row + (shift >> 1) * 4;
+        const uint32_t fs = (shift & 1) * 16;
+        const uint32_t x_col0 = 96 - 32 * warp;             // first X column any row of this warp can need
+        float m_ref = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; j++) {
+            // ---- phase A: bias of this row, 2 x 64 columns, as packed f16 (the reference's rounding point) ----
+            ok = mbar_wait(bar_x_full, j & 1, s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t breg[2][32];
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
+#pragma unroll
+                for (int q3 = 0; q3 < 3; q3++) {
+                    uint32_t xr[32];
+                    tmem_ld32(tmem_X + lane_base + x_col0 + cc * 64 + q3 * 32, xr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            float v0 = __uint_as_float(xr[i + 2 * u]) * bscale, v1 = __uint_as_float(xr[i + 2 * u + 1]) * bscale;
+                            w[u] = cvt_f16x2(v0, v1);
+                        }
+                        st_shared_v4(bnc_row + q3 * 64 + i * 2, w[0], w[1], w[2], w[3]);
+                    }
+                }
+                uint32_t prev = ld_shared_b32(bnc_rd);
+#pragma unroll
+                for (int p2 = 0; p2 < 32; p2++) {
+                    const uint32_t next = ld_shared_b32(bnc_rd + 4 * (p2 + 1));
+                    breg[cc][p2] = __funnelshift_r(prev, next, fs);
+                    prev = next;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_x_free);
+
+            // ---- phase B: softmax with the bias added in the log2 domain ----
+            ok = mbar_wait(bar_s_full, j & 1, s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const int n_valid = len_b - j * kTile;
+            // pass 1: row maximum of t = S*c + bias*log2(e) over the tile (S is read again in pass 2; keeping t
+            // or a deferred P in registers next to the 64 bias registers would spill)
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+                uint32_t sreg[32];
+                tmem_ld32(tmem_S + lane_base + q4 * 32, sreg);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int col = q4 * 32 + i;
+                    const __half2 bh = *reinterpret_cast<const __half2*>(&breg[q4 >> 1][(q4 & 1) * 16 + (i >> 1)]);
+                    float t0 = fmaf(__low2float(bh), kLog2e, __uint_as_float(sreg[i]) * c);
+                    float t1 = fmaf(__high2float(bh), kLog2e, __uint_as_float(sreg[i + 1]) * c);
+                    if (col >= n_valid) t0 = -INFINITY;
+                    if (col + 1 >= n_valid) t1 = -INFINITY;
+                    mx[(i >> 1) & 3] = fmaxf(mx[(i >> 1) & 3], fmaxf(t0, t1));
+                }
+            }
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // lazy rescale: O and l are only touched when a row outgrew its reference maximum by 2^8
+            const bool grow = m_tile > m_ref + kRescaleThreshold;  // also true for -inf -> finite
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_ref, m_tile);
+                const float alpha = (m_ref == -INFINITY) ? 0.0f : ex2(m_ref - m_new);
+                l_run *= alpha;
+                if (j > 0) {
+#pragma unroll
+                    for (int q4 = 0; q4 < HD / 32; q4++) {
+                        uint32_t oreg[32];
+                        tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                        tmem_st32(tmem_O + lane_base + q4 * 32, oreg);
+                    }
+                }
+                m_ref = m_new;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            // pass 2: P = exp2(t - m_ref), stored over the S columns already consumed
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                uint32_t preg[32];
+#pragma unroll
+                for (int q2 = 0; q2 < 2; q2++) {
+                    uint32_t sreg[32];
+                    tmem_ld32(tmem_S + lane_base + hh * 64 + q2 * 32, sreg);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int col = hh * 64 + q2 * 32 + i;
+                        const __half2 bh = *reinterpret_cast<const __half2*>(&breg[hh][q2 * 16 + (i >> 1)]);
+                        const float t0 = fmaf(__low2float(bh), kLog2e, __uint_as_float(sreg[i]) * c);
+                        const float t1 = fmaf(__high2float(bh), kLog2e, __uint_as_float(sreg[i + 1]) * c);
+                        float p0 = ex2(t0 - m_use), p1 = ex2(t1 - m_use);
+                        if (col >= n_valid) p0 = 0.0f;
+                        if (col + 1 >= n_valid) p1 = 0.0f;
+                        ls[(i >> 1) & 3] += p0 + p1;
+                        preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
+                    }
+                }
+                tmem_st32(tmem_P + lane_base + hh * 32, preg);
+            }
+            l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p_ready);
+        }
+        if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * HD;
+#pragma unroll
+            for (int q4 = 0; q4 < HD / 32; q4++) {
+                uint32_t oreg[32];
+                tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                tmem_wait_ld();
+                if (iq < a.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(out + q4 * 32 + i) =
+                            make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
+                                        __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+
 // ---- host side ----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -568,6 +930,43 @@ bool encode_kv_map(CUtensorMap* m, const View& v, int hd, int Lk, int Hkv, int B
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<uint8_t*>(v.p), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// R as a rank-4 F16 tensor [hd, 2T-1, H, 1|B]; box = 64 columns x 128 rows.
+bool encode_r_map(CUtensorMap* m, const FattnArgs& a) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const int64_t nb3 = a.r_ne3 > 1 ? a.r.nb3 : a.r.nb2 * a.H;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.hd, (cuuint64_t)(2 * a.Tq - 1), (cuuint64_t)a.H, (cuuint64_t)a.r_ne3};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.r.nb1, (cuuint64_t)a.r.nb2, (cuuint64_t)nb3};
+    const cuuint32_t box[4] = {64, (cuuint32_t)kTile, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<uint8_t*>(a.r.p), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_relpos(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+    CUtensorMap tmK, tmV, tmR;
+    if (!encode_kv_map(&tmK, a.k, a.hd, a.Lk, a.Hkv, a.B / a.bq) || !encode_kv_map(&tmV, a.v, a.hd, a.Lk, a.Hkv, a.B / a.bq) ||
+        !encode_r_map(&tmR, a)) {
+        snprintf(errbuf, errlen, "cuTensorMapEncodeTiled failed for K/V/R");
+        return B200_E_CUDA;
+    }
+    const size_t smem = 1024 + (size_t)6 * 2 * kPanelBytes + (size_t)kTile * kBncStride + 104 + 16;
+    auto kern = fattn_prefill_tc5_relpos_kernel;
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(kern, smem, smem_set);
+    if (e == cudaSuccess) {
+        dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
+        kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV, tmR);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        snprintf(errbuf, errlen, "tcgen05 rel-pos prefill launch: %s", cudaGetErrorString(e));
+        return B200_E_CUDA;
+    }
+    return B200_OK;
 }
 
 template <int HD, int NSTG>
@@ -600,8 +999,13 @@ bool tc5_supported(const FattnArgs& a) {
     if (a.hd != 64 && a.hd != 128) return false;
     if (a.k.type != B200_TYPE_F16 || a.v.type != B200_TYPE_F16) return false;
     if (!a.k.vec16 || !a.v.vec16) return false;
-    if (a.has_mask || a.relpos || a.softcap != 0.0f || a.n2 != 0) return false;
+    if (a.has_mask || a.softcap != 0.0f || a.n2 != 0) return false;
     if (!(a.scale > 0.0f)) return false;
+    if (a.relpos) {
+        // fused bias: head_dim 128, F16 R with TMA-legal strides, no causal mask, bias rounded to F16
+        if (a.hd != 128 || a.causal || a.relpos_f32) return false;
+        if (a.r.type != B200_TYPE_F16 || !a.r.vec16 || a.r.nb1 <= 0 || a.r.nb2 <= 0) return false;
+    }
     const int64_t lim = (int64_t)1 << 40;
     if (a.k.nb1 <= 0 || a.k.nb2 <= 0 || a.k.nb3 <= 0 || a.v.nb1 <= 0 || a.v.nb2 <= 0 || a.v.nb3 <= 0) return false;
     if (a.k.nb1 >= lim || a.k.nb2 >= lim || a.k.nb3 >= lim || a.v.nb1 >= lim || a.v.nb2 >= lim || a.v.nb3 >= lim) return false;
@@ -609,6 +1013,7 @@ bool tc5_supported(const FattnArgs& a) {
 }
 
 int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+    if (a.relpos) return launch_relpos(a, st, errbuf, errlen);
     if (a.hd == 64) return launch_t<64, 2>(a, st, errbuf, errlen);
     return launch_t<128, 1>(a, st, errbuf, errlen);
 }
