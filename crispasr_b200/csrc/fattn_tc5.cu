@@ -554,7 +554,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
 // MMA order: X[0] S[0] | per tile j: X[j+1] as soon as the softmax threads have drained X[j]; then, once
 // P[j] is in TMEM, PV[j] and S[j+1].
 // ------------------------------------------------------------------------------------------------------
-constexpr int kBncStride = 208;  // bytes per bounce row: 96 halves + 16 bytes of padding (conflict-free 16-byte stores)
+constexpr int kBncStride = 256;  // bytes per bounce row: a ring of 64 fp32 words
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -726,13 +726,16 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                     ok = mbar_wait(bar_r_full + 8 * (j & 1), ((j + 2) >> 1) & 1, s_abort) &&
                          mbar_wait(bar_x_free, j & 1, s_abort);
                     if (!ok) break;
+                    TC5_TRACE(1, j, 0);
                     tc_fence_after();
                     issue_x(j + 1);
+                    TC5_TRACE(1, j, 1);
                 }
                 ok = mbar_wait(bar_v_full, j & 1, s_abort);
                 if (ok && more) ok = mbar_wait(bar_k_full, (j + 1) & 1, s_abort);
                 if (ok) ok = mbar_wait(bar_p_ready, j & 1, s_abort);
                 if (!ok) break;
+                TC5_TRACE(1, j, 2);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kTile / 16; ks++)
@@ -741,6 +744,7 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 tc_commit(bar_v_empty);
                 if (more) issue_s();
                 else tc_commit(bar_o_done);
+                TC5_TRACE(1, j, 3);
             }
             if (!ok) {
                 tc_commit(bar_o_done);
@@ -752,75 +756,114 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         const int r = tid;
         const int iq = q0 + r;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        const float c = a.scale * kLog2e;
-        const float bscale = a.relscale;
+        const float bscale = a.relscale;   // == a.scale: the tcgen05 path is not taken with a softcap
         const int shift = 31 - lane;                        // band offset of this row inside the warp's columns
+        // Bounce ring of this row: 64 fp32 words, rotated by 4*lane words so that the 16-byte stores (same logical
+        // chunk in every lane) and the 4-byte loads (logical word c - lane) are both bank-conflict free.
         const uint32_t bnc_row = sBnc + r * kBncStride;
-        const uint32_t bnc_rd = bnc_row + (shift >> 1) * 4;
-        const uint32_t fs = (shift & 1) * 16;
+        const uint32_t rot = 4u * lane;
         const uint32_t x_col0 = 96 - 32 * warp;             // first X column any row of this warp can need
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
-            // ---- phase A: bias of this row, 2 x 64 columns, as packed f16 (the reference's rounding point) ----
+            // ---- phase A: the 128 bias values of this row, fp32 registers holding f16-rounded numbers ----
             ok = mbar_wait(bar_x_full, j & 1, s_abort);
             if (!ok) break;
+            if (tid == 0) TC5_TRACE(0, j, 0);
             tc_fence_after();
-            uint32_t breg[2][32];
+            // TMEM loads are slow while the tensor pipe is running (the accumulator traffic of the MMAs has priority),
+            // so they are issued in two deep batches per phase and overlapped with the arithmetic of the previous batch.
+            float u[4][32];
+            auto bounce_chunk = [&](const uint32_t (&xr)[32], int k) {
+                // scale, then round to 11 significant bits (the f16 the reference casts its mask to) with Veltkamp's
+                // splitting: three fp32 operations instead of two format conversions; store chunk k in the ring
 #pragma unroll
-            for (int cc = 0; cc < 2; cc++) {
+                for (int i = 0; i < 32; i += 4) {
+                    uint32_t w[4];
 #pragma unroll
-                for (int q3 = 0; q3 < 3; q3++) {
-                    uint32_t xr[32];
-                    tmem_ld32(tmem_X + lane_base + x_col0 + cc * 64 + q3 * 32, xr);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            float v0 = __uint_as_float(xr[i + 2 * u]) * bscale, v1 = __uint_as_float(xr[i + 2 * u + 1]) * bscale;
-                            w[u] = cvt_f16x2(v0, v1);
-                        }
-                        st_shared_v4(bnc_row + q3 * 64 + i * 2, w[0], w[1], w[2], w[3]);
+                    for (int e = 0; e < 4; e++) {
+                        const float v = __fmul_rn(__uint_as_float(xr[i + e]), bscale);   // _rn: never contracted
+                        const float g = __fmul_rn(v, 8193.0f);
+                        w[e] = __float_as_uint(__fsub_rn(g, __fsub_rn(g, v)));
                     }
+                    st_shared_v4(bnc_row + ((((k & 1) * 32 + i) * 4 + rot * 4) & 255), w[0], w[1], w[2], w[3]);
                 }
-                uint32_t prev = ld_shared_b32(bnc_rd);
+            };
+            auto read_quarter = [&](int qq) {  // tile columns [32qq, 32qq+32): ring words shift .. shift+31 of chunks qq, qq+1
 #pragma unroll
-                for (int p2 = 0; p2 < 32; p2++) {
-                    const uint32_t next = ld_shared_b32(bnc_rd + 4 * (p2 + 1));
-                    breg[cc][p2] = __funnelshift_r(prev, next, fs);
-                    prev = next;
+                for (int t2 = 0; t2 < 32; t2++)
+                    u[qq][t2] = __uint_as_float(ld_shared_b32(bnc_row + (((qq * 32 + shift + t2) * 4 + rot * 4) & 255)));
+            };
+            {
+                uint32_t xa[3][32], xb[2][32];
+#ifdef B200_TC5_TRACE
+                long long c0 = clock64();
+#endif
+#pragma unroll
+                for (int k = 0; k < 3; k++) tmem_ld32(tmem_X + lane_base + x_col0 + k * 32, xa[k]);
+#ifdef B200_TC5_TRACE
+                long long c1 = clock64();
+#endif
+                tmem_wait_ld();
+#ifdef B200_TC5_TRACE
+                long long c2 = clock64();
+#endif
+#pragma unroll
+                for (int k = 0; k < 2; k++) tmem_ld32(tmem_X + lane_base + x_col0 + (3 + k) * 32, xb[k]);
+#ifdef B200_TC5_TRACE
+                long long c3 = clock64();
+#endif
+                bounce_chunk(xa[0], 0);
+#ifdef B200_TC5_TRACE
+                long long c4 = clock64();
+#endif
+                bounce_chunk(xa[1], 1);
+                read_quarter(0);
+#ifdef B200_TC5_TRACE
+                long long c5 = clock64();
+                if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == 0 && j < 64) {
+                    g_tc5_trace[2][j][2] = c1 - c0; g_tc5_trace[2][j][3] = c2 - c1; g_tc5_trace[2][j][4] = c3 - c2;
+                    g_tc5_trace[2][j][5] = c4 - c3; g_tc5_trace[2][j][6] = c5 - c4;
                 }
+#endif
+                bounce_chunk(xa[2], 2);
+                read_quarter(1);
+                tmem_wait_ld();
+                bounce_chunk(xb[0], 3);
+                read_quarter(2);
+                bounce_chunk(xb[1], 4);
+                read_quarter(3);
             }
             tc_fence_before();
             mbar_arrive(bar_x_free);
+            if (tid == 0) TC5_TRACE(0, j, 1);
 
-            // ---- phase B: softmax with the bias added in the log2 domain ----
+            // ---- phase B: u = S*scale + bias (natural units), row maximum ----
             ok = mbar_wait(bar_s_full, j & 1, s_abort);
             if (!ok) break;
+            if (tid == 0) TC5_TRACE(0, j, 2);
             tc_fence_after();
             const int n_valid = len_b - j * kTile;
-            // pass 1: row maximum of t = S*c + bias*log2(e) over the tile (S is read again in pass 2; keeping t
-            // or a deferred P in registers next to the 64 bias registers would spill)
+            const bool full_tile = n_valid >= kTile;   // uniform over the CTA: only the last tile is partial
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) {
-                uint32_t sreg[32];
-                tmem_ld32(tmem_S + lane_base + q4 * 32, sreg);
+            for (int hh = 0; hh < 2; hh++) {
+                uint32_t sreg[2][32];
+                tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int col = q4 * 32 + i;
-                    const __half2 bh = *reinterpret_cast<const __half2*>(&breg[q4 >> 1][(q4 & 1) * 16 + (i >> 1)]);
-                    float t0 = fmaf(__low2float(bh), kLog2e, __uint_as_float(sreg[i]) * c);
-                    float t1 = fmaf(__high2float(bh), kLog2e, __uint_as_float(sreg[i + 1]) * c);
-                    if (col >= n_valid) t0 = -INFINITY;
-                    if (col + 1 >= n_valid) t1 = -INFINITY;
-                    mx[(i >> 1) & 3] = fmaxf(mx[(i >> 1) & 3], fmaxf(t0, t1));
-                }
+                for (int q2 = 0; q2 < 2; q2++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        float uv = fmaf(__uint_as_float(sreg[q2][i]), bscale, u[hh * 2 + q2][i]);
+                        if (!full_tile && hh * 64 + q2 * 32 + i >= n_valid) uv = -INFINITY;
+                        u[hh * 2 + q2][i] = uv;
+                        mx[i & 3] = fmaxf(mx[i & 3], uv);
+                    }
             }
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            if (tid == 0) TC5_TRACE(0, j, 3);
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * kLog2e;
             // lazy rescale: O and l are only touched when a row outgrew its reference maximum by 2^8
             const bool grow = m_tile > m_ref + kRescaleThreshold;  // also true for -inf -> finite
             if (__any_sync(0xffffffffu, grow)) {
@@ -841,35 +884,27 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 m_ref = m_new;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-            // pass 2: P = exp2(t - m_ref), stored over the S columns already consumed
+            // P = exp2(u*log2(e) - m_ref) from registers; masked columns hold -inf and give 0
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int hh = 0; hh < 2; hh++) {
                 uint32_t preg[32];
 #pragma unroll
-                for (int q2 = 0; q2 < 2; q2++) {
-                    uint32_t sreg[32];
-                    tmem_ld32(tmem_S + lane_base + hh * 64 + q2 * 32, sreg);
-                    tmem_wait_ld();
+                for (int q2 = 0; q2 < 2; q2++)
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const int col = hh * 64 + q2 * 32 + i;
-                        const __half2 bh = *reinterpret_cast<const __half2*>(&breg[hh][q2 * 16 + (i >> 1)]);
-                        const float t0 = fmaf(__low2float(bh), kLog2e, __uint_as_float(sreg[i]) * c);
-                        const float t1 = fmaf(__high2float(bh), kLog2e, __uint_as_float(sreg[i + 1]) * c);
-                        float p0 = ex2(t0 - m_use), p1 = ex2(t1 - m_use);
-                        if (col >= n_valid) p0 = 0.0f;
-                        if (col + 1 >= n_valid) p1 = 0.0f;
+                        const float p0 = ex2(fmaf(u[hh * 2 + q2][i], kLog2e, -m_use));
+                        const float p1 = ex2(fmaf(u[hh * 2 + q2][i + 1], kLog2e, -m_use));
                         ls[(i >> 1) & 3] += p0 + p1;
                         preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
                     }
-                }
                 tmem_st32(tmem_P + lane_base + hh * 32, preg);
             }
             l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_p_ready);
+            if (tid == 0) TC5_TRACE(0, j, 4);
         }
         if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
         if (ok) {
