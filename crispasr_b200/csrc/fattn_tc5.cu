@@ -229,6 +229,40 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
     lsum_io += (ls[0] + ls[1]) + (ls[2] + ls[3]);
 }
 
+// One query row (HD elements) -> f16, written into the 128-byte swizzled operand tile: row r, 16-byte chunk c of
+// panel p at p*16384 + r*128 + ((c ^ (r & 7)) * 16).  The type is tested once and all loads of the row are issued
+// before the first store, so the row costs one memory round trip instead of HD/8.
+template <int HD>
+__device__ __forceinline__ void load_q_row(uint8_t* tile, int r, const uint8_t* rowp, int type, bool vec16, bool valid) {
+    uint4 v[HD / 8];
+    if (!valid) {
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) v[c] = make_uint4(0u, 0u, 0u, 0u);
+    } else if (type == B200_TYPE_F16 && vec16) {
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) v[c] = __ldg(reinterpret_cast<const uint4*>(rowp) + c);
+    } else if (type == B200_TYPE_F32 && vec16) {
+#pragma unroll
+        for (int c0 = 0; c0 < HD / 8; c0 += 4) {  // 4 chunks = 8 float4 in flight
+            float4 f[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = __ldg(reinterpret_cast<const float4*>(rowp) + c0 * 2 + i);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                v[c0 + i].x = pack_half2(f[2 * i].x, f[2 * i].y), v[c0 + i].y = pack_half2(f[2 * i].z, f[2 * i].w);
+                v[c0 + i].z = pack_half2(f[2 * i + 1].x, f[2 * i + 1].y), v[c0 + i].w = pack_half2(f[2 * i + 1].z, f[2 * i + 1].w);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < HD / 8; c++) v[c] = q_chunk(rowp, type, c * 8, false);
+    }
+    uint8_t* dst_row = tile + r * 128;
+#pragma unroll
+    for (int c = 0; c < HD / 8; c++)
+        *reinterpret_cast<uint4*>(dst_row + (c >> 3) * kPanelBytes + (((c & 7) ^ (r & 7)) << 4)) = v[c];
+}
+
 struct Tc5Smem {
     // offsets from the 1024-byte aligned base of dynamic shared memory
     template <int HD, int NSTG>
@@ -253,8 +287,10 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t sBar = sV + NSTG * TILE_BYTES;  // 8-byte slots
     const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8 * NSTG, bar_v_full = sBar + 16 * NSTG,
                    bar_v_empty = sBar + 24 * NSTG, bar_s_full = sBar + 32 * NSTG, bar_p_ready = bar_s_full + 8,
-                   bar_o_done = bar_s_full + 16;
-    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 24;
+                   bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24;
+    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 32;
+    // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
+    constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
     volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
 
@@ -292,6 +328,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         mbar_init(bar_s_full, 1);
         mbar_init(bar_p_ready, kTile);
         mbar_init(bar_o_done, 1);
+        mbar_init(bar_pv_done, 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
@@ -313,29 +350,25 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                      "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (lane == 0) TC5_TRACE(2, 61, 0);
     }
     if (warp < 4) {
-        // Q tile -> shared memory, f16, 128-byte swizzle: row r, 16-byte chunk c of panel p lives at
-        // p*16384 + r*128 + ((c ^ (r & 7)) * 16). Thread r writes row r.
+        // Q tile -> shared memory (thread r writes row r)
         const int r = tid;
         const int iq = q0 + r;
-        const uint8_t* rowp = a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3;
-        uint8_t* dst_row = smem_gen + r * 128;
-#pragma unroll
-        for (int c = 0; c < HD / 8; c++) {
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (iq < a.Tq) val = q_chunk(rowp, a.q.type, c * 8, a.q.vec16 != 0);
-            *reinterpret_cast<uint4*>(dst_row + (c >> 3) * kPanelBytes + (((c & 7) ^ (r & 7)) << 4)) = val;
-        }
+        load_q_row<HD>(smem_gen, r, a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.type,
+                       a.q.vec16 != 0, iq < a.Tq);
         fence_proxy_async();
+        if (tid == 0) TC5_TRACE(2, 61, 1);
     }
+    if (tid == 4 * 32) TC5_TRACE(2, 61, 2);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem_base;
     if (tid == 0) TC5_TRACE(2, 60, 1);
     const uint32_t tmem_S = tmem_base;            // cols [0,128)
-    const uint32_t tmem_P = tmem_base;            // cols [0,64), f16x2
+    const uint32_t tmem_P = SEP_P ? tmem_base + kTile + HD : tmem_base;  // f16x2: cols [192,256) (hd 64) or aliasing S [0,64)
     const uint32_t tmem_O = tmem_base + kTile;    // cols [128,128+HD)
 
     if (warp == 4) {
@@ -403,12 +436,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 if (!ok) break;
                 TC5_TRACE(1, j, 3);
                 tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < kTile / 16; ks++)
-                    mma_ts(tmem_O, tmem_P + ks * 8, smem_desc(sV + slot * TILE_BYTES + ks * 2048, kPanelBytes, 1024),
-                           IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit(bar_v_empty + 8 * slot);
-                if (more) {
+                auto issue_next_s = [&]() {
 #pragma unroll
                     for (int ks = 0; ks < HD / 16; ks++) {
                         const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
@@ -417,9 +445,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     }
                     tc_commit(bar_s_full);
                     tc_commit(bar_k_empty + 8 * nslot);
-                } else {
-                    tc_commit(bar_o_done);
-                }
+                };
+                // with P in its own columns the next S goes first: the softmax threads wake after 4 MMAs, not 12
+                if (SEP_P && more) issue_next_s();
+#pragma unroll
+                for (int ks = 0; ks < kTile / 16; ks++)
+                    mma_ts(tmem_O, tmem_P + ks * 8, smem_desc(sV + slot * TILE_BYTES + ks * 2048, kPanelBytes, 1024),
+                           IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(bar_v_empty + 8 * slot);
+                if (SEP_P) tc_commit(bar_pv_done);
+                if (!SEP_P && more) issue_next_s();
+                if (!more) tc_commit(bar_o_done);
                 TC5_TRACE(1, j, 4);
             }
             if (!ok) {
@@ -460,6 +496,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             }
             uint32_t preg[2][32];
             float lsum = 0.0f;
+            bool pv_waited = false;
             for (int attempt = 0; attempt < 2; attempt++) {
                 // P = exp2(S*c - m_ref), rounded to f16x2; the tile maximum is tracked in the same pass and
                 // only checked afterwards (lazy rescale).
@@ -482,6 +519,12 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 const bool grow = m_tile > m_ref + kRescaleThreshold;
                 if (!__any_sync(0xffffffffu, grow)) break;
                 // some row of this warp outgrew its reference maximum: rescale O and l, then redo P
+                if (SEP_P && j > 0 && !pv_waited) {  // O must be at rest: P.V of the previous tile has completed
+                    ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                    pv_waited = true;
+                }
                 const float m_new = fmaxf(m_ref, m_tile);
                 const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
                 l_run *= alpha;
@@ -498,7 +541,13 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 }
                 m_ref = m_new;
             }
+            if (!ok) break;
             l_run += lsum;
+            if (SEP_P && j > 0 && !pv_waited) {  // P[j-1] must have been consumed before P[j] overwrites it
+                ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
+                if (!ok) break;
+                tc_fence_after();
+            }
             if (tid == 0) TC5_TRACE(0, j, 1);
             tmem_st32(tmem_P + lane_base, preg[0]);
             tmem_st32(tmem_P + lane_base + 32, preg[1]);
@@ -646,18 +695,10 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     if (warp < 4) {
         const int r = tid;
         const int iq = q0 + r;
-#pragma unroll
-        for (int which = 0; which < 2; which++) {
-            const View& qv = which ? a.qv : a.q;
-            const uint8_t* rowp = qv.p + (int64_t)iq * qv.nb1 + (int64_t)h * qv.nb2 + (int64_t)b * qv.nb3;
-            uint8_t* dst_row = smem_gen + which * TILE_BYTES + r * 128;
-#pragma unroll
-            for (int c = 0; c < HD / 8; c++) {
-                uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                if (iq < a.Tq) val = q_chunk(rowp, qv.type, c * 8, qv.vec16 != 0);
-                *reinterpret_cast<uint4*>(dst_row + (c >> 3) * kPanelBytes + (((c & 7) ^ (r & 7)) << 4)) = val;
-            }
-        }
+        load_q_row<HD>(smem_gen, r, a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.type,
+                       a.q.vec16 != 0, iq < a.Tq);
+        load_q_row<HD>(smem_gen + TILE_BYTES, r, a.qv.p + (int64_t)iq * a.qv.nb1 + (int64_t)h * a.qv.nb2 + (int64_t)b * a.qv.nb3,
+                       a.qv.type, a.qv.vec16 != 0, iq < a.Tq);
         fence_proxy_async();
     }
     tc_fence_before();
@@ -1012,7 +1053,7 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
         return B200_E_CUDA;
     }
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
-    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 24 + 16;
+    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 32 + 16;
     auto kern = fattn_prefill_tc5_kernel<HD, NSTG>;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem_once(kern, smem, smem_set);
