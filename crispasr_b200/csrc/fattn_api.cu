@@ -237,12 +237,13 @@ struct Arena {
     uint8_t* base = nullptr;
     size_t cap = 0;
     int device = -1;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr, stream2 = nullptr;
     ~Arena() { release(); }
     void release() {
         if (base) cudaFree(base);
         if (stream) cudaStreamDestroy(stream);
-        base = nullptr, cap = 0, stream = nullptr, device = -1;
+        if (stream2) cudaStreamDestroy(stream2);
+        base = nullptr, cap = 0, stream = nullptr, stream2 = nullptr, device = -1;
     }
 };
 thread_local Arena g_arena;
@@ -368,7 +369,7 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     const size_t kvlen_off = (ext && ext->kv_len) ? bump((size_t)q->ne[3] * 4) : 0;
     const size_t dst_bytes = (size_t)dst->ne[0] * dst->ne[1] * dst->ne[2] * dst->ne[3] * 4;
     const size_t dst_off = bump(dst_bytes);
-    const size_t ws_off = bump(plan.ws_bytes);
+    const size_t ws_off = bump(2 * ((plan.ws_bytes + 255) / 256 * 256));  // one per stream in flight
 
     Arena& ar = g_arena;
     cudaError_t e;
@@ -384,37 +385,96 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
         if ((e = cudaMalloc((void**)&ar.base, total)) != cudaSuccess) return cuda_fail(e, "cudaMalloc(arena)");
         ar.cap = total;
     }
+    if (!ar.stream2 && (e = cudaStreamCreateWithFlags(&ar.stream2, cudaStreamNonBlocking)) != cudaSuccess)
+        return cuda_fail(e, "cudaStreamCreate");
+
+    // Batch entries are independent, so the call is pipelined over chunks of the batch dimension on two
+    // streams: the H2D copy of chunk i+1 overlaps the kernel and the D2H copy of chunk i (separate copy
+    // engines).  Chunking needs the batch dimension outermost in every batched operand; otherwise one chunk.
+    const int64_t B = q->ne[3];
+    auto batch_outermost = [](const b200_tensor* t) {
+        b200_tensor one = *t;
+        one.ne[3] = 1;
+        return t->ne[3] == 1 || t->nb[3] >= span_bytes(&one);
+    };
+    bool chunkable = B >= 2 && k->ne[3] == B;
+    for (int i = 0; i < 6 && chunkable; i++)
+        if (in[i] && in[i]->ne[3] != 1 && (in[i]->ne[3] != B || !batch_outermost(in[i]))) chunkable = false;
+    const int n_chunks = chunkable ? (int)(B < 4 ? B : 4) : 1;
+    const size_t ws_each = (plan.ws_bytes + 255) / 256 * 256;  // chunk plans never need more than the full plan
+    cudaStream_t streams[2] = {ar.stream, ar.stream2};
+
+    // operands without a batch dimension (ne[3] == 1) are copied once, ahead of everything, on stream 0
     b200_tensor dt[6];
+    cudaEvent_t shared_ready = nullptr;
     for (int i = 0; i < 6; i++) {
         if (!in[i]) continue;
         dt[i] = *in[i];
         dt[i].data = ar.base + off[i];
-        if ((e = cudaMemcpyAsync(dt[i].data, in[i]->data, span_bytes(in[i]), cudaMemcpyHostToDevice, ar.stream)) !=
-            cudaSuccess)
-            return cuda_fail(e, "cudaMemcpyAsync(H2D)");
-    }
-    b200_fattn_ext dext;
-    memset(&dext, 0, sizeof(dext));
-    if (ext) {
-        dext = *ext;
-        dext.q_v = ext->q_v ? &dt[4] : nullptr;
-        dext.r = ext->r ? &dt[5] : nullptr;
-        if (ext->kv_len) {
-            if ((e = cudaMemcpyAsync(ar.base + kvlen_off, ext->kv_len, (size_t)q->ne[3] * 4, cudaMemcpyHostToDevice,
-                                     ar.stream)) != cudaSuccess)
-                return cuda_fail(e, "cudaMemcpyAsync(kv_len)");
-            dext.kv_len = (const int32_t*)(ar.base + kvlen_off);
+        if (n_chunks == 1 || in[i]->ne[3] == 1) {
+            if ((e = cudaMemcpyAsync(dt[i].data, in[i]->data, span_bytes(in[i]), cudaMemcpyHostToDevice, streams[0])) !=
+                cudaSuccess)
+                return cuda_fail(e, "cudaMemcpyAsync(H2D)");
         }
     }
-    b200_tensor ddst = *dst;
-    ddst.data = ar.base + dst_off;
-    rc = make_plan(&dt[0], &dt[1], &dt[2], mask ? &dt[3] : nullptr, &ddst, params, ext ? &dext : nullptr, false, &plan);
-    if (rc != B200_OK) return rc;
-    rc = do_launch(plan, plan.ws_bytes ? ar.base + ws_off : nullptr, plan.ws_bytes, ar.stream);
-    if (rc != B200_OK) return rc;
-    if ((e = cudaMemcpyAsync(dst->data, ddst.data, dst_bytes, cudaMemcpyDeviceToHost, ar.stream)) != cudaSuccess)
-        return cuda_fail(e, "cudaMemcpyAsync(D2H)");
-    if ((e = cudaStreamSynchronize(ar.stream)) != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    if (ext && ext->kv_len &&
+        (e = cudaMemcpyAsync(ar.base + kvlen_off, ext->kv_len, (size_t)B * 4, cudaMemcpyHostToDevice, streams[0])) !=
+            cudaSuccess)
+        return cuda_fail(e, "cudaMemcpyAsync(kv_len)");
+    if (n_chunks > 1) {
+        if ((e = cudaEventCreateWithFlags(&shared_ready, cudaEventDisableTiming)) != cudaSuccess)
+            return cuda_fail(e, "cudaEventCreate");
+        cudaEventRecord(shared_ready, streams[0]);
+        cudaStreamWaitEvent(streams[1], shared_ready, 0);
+    }
+
+    int rc_chunks = B200_OK;
+    for (int c = 0; c < n_chunks && rc_chunks == B200_OK; c++) {
+        const int64_t b0 = B * c / n_chunks, b1 = B * (c + 1) / n_chunks, nb = b1 - b0;
+        cudaStream_t st = streams[c & 1];
+        b200_tensor ct[6];
+        for (int i = 0; i < 6; i++) {
+            if (!in[i]) continue;
+            ct[i] = dt[i];
+            if (n_chunks > 1 && in[i]->ne[3] != 1) {
+                ct[i].data = (uint8_t*)dt[i].data + (size_t)b0 * in[i]->nb[3];
+                ct[i].ne[3] = nb;
+                b200_tensor hview = *in[i];
+                hview.ne[3] = nb;
+                if ((e = cudaMemcpyAsync(ct[i].data, (const uint8_t*)in[i]->data + (size_t)b0 * in[i]->nb[3], span_bytes(&hview),
+                                         cudaMemcpyHostToDevice, st)) != cudaSuccess)
+                    return cuda_fail(e, "cudaMemcpyAsync(H2D chunk)");
+            }
+        }
+        b200_fattn_ext dext;
+        memset(&dext, 0, sizeof(dext));
+        if (ext) {
+            dext = *ext;
+            dext.q_v = ext->q_v ? &ct[4] : nullptr;
+            dext.r = ext->r ? &ct[5] : nullptr;
+            dext.kv_len = ext->kv_len ? (const int32_t*)(ar.base + kvlen_off) + b0 : nullptr;
+        }
+        b200_tensor cdst = *dst;
+        cdst.ne[3] = nb;
+        cdst.data = ar.base + dst_off + (size_t)b0 * dst->nb[3];
+        Plan cplan;
+        rc_chunks = make_plan(&ct[0], &ct[1], &ct[2], mask ? &ct[3] : nullptr, &cdst, params, ext ? &dext : nullptr, false, &cplan);
+        if (rc_chunks != B200_OK) break;
+        if (cplan.ws_bytes > ws_each) {
+            rc_chunks = B200_E_WORKSPACE;
+            break;
+        }
+        rc_chunks = do_launch(cplan, cplan.ws_bytes ? ar.base + ws_off + (size_t)(c & 1) * ws_each : nullptr, cplan.ws_bytes, st);
+        if (rc_chunks != B200_OK) break;
+        if ((e = cudaMemcpyAsync((uint8_t*)dst->data + (size_t)b0 * dst->nb[3], cdst.data, (size_t)nb * dst->nb[3],
+                                 cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+            return cuda_fail(e, "cudaMemcpyAsync(D2H)");
+    }
+    cudaError_t e0 = cudaStreamSynchronize(streams[0]), e1 = cudaStreamSynchronize(streams[1]);
+    if (shared_ready) cudaEventDestroy(shared_ready);
+    if (rc_chunks != B200_OK) return rc_chunks;
+    if (e0 != cudaSuccess) return cuda_fail(e0, "cudaStreamSynchronize");
+    if (e1 != cudaSuccess) return cuda_fail(e1, "cudaStreamSynchronize");
     return B200_OK;
 }
 

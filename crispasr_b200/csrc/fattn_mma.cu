@@ -389,23 +389,34 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
                     make_uint4(0u, 0u, 0u, 0u);
             continue;
         }
-        const __half d = *reinterpret_cast<const __half*>(src);
-        const __half2 d2 = __half2half2(d);
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(src));
         const __half2 bias = __float2half2_rn(1152.0f);
+        // The 32 quants start 2 bytes into the block. Read aligned 32-bit words and realign with a funnel shift:
+        // block offset = 0 mod 4 -> word 0 holds {d, q0, q1} and the quants straddle words (shift 16);
+        // block offset = 2 mod 4 -> the quants start on the next word boundary (shift 0).
+        const uint32_t o = (uint32_t)(row * RB + blk * 34);
+        const uint32_t sh = (o >> 1) & 1u;
+        const uint32_t* W = reinterpret_cast<const uint32_t*>(raw + (o & ~3u) + 4u * sh);
+        uint32_t w[9];
 #pragma unroll
-        for (int c4 = 0; c4 < 4; c4++) {  // four 16-byte output chunks of 8 halves
-            uint32_t out[4];
+        for (int i = 0; i < 8; i++) w[i] = W[i];
+        w[8] = sh ? 0u : W[8];
+        const uint32_t fs = 16u * (1u - sh);
+        uint32_t out[16];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t w = src[1 + c4 * 4 + i] ^ 0x8080u;  // two int8 -> biased uint8
-                // halves 0x64xx = 1024 + xx; minus 1152 gives the signed value exactly
-                const uint32_t h2 = 0x64006400u | (w & 0xFFu) | ((w & 0xFF00u) << 8);
-                const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&h2), bias), d2);
-                out[i] = *reinterpret_cast<const uint32_t*>(&v);
-            }
-            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * (HD / 8) + swz<HD>(row, blk * 4 + c4)) * 16) =
-                make_uint4(out[0], out[1], out[2], out[3]);
+        for (int kk = 0; kk < 8; kk++) {
+            const uint32_t win = __funnelshift_r(w[kk], w[kk + 1], fs) ^ 0x80808080u;  // four int8 -> biased uint8
+            // halves 0x64xx = 1024 + xx; minus 1152 gives the signed value exactly; times d rounds once
+            const uint32_t h01 = __byte_perm(win, 0x64646464u, 0x4140), h23 = __byte_perm(win, 0x64646464u, 0x4342);
+            const __half2 v01 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&h01), bias), d2);
+            const __half2 v23 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&h23), bias), d2);
+            out[2 * kk] = *reinterpret_cast<const uint32_t*>(&v01);
+            out[2 * kk + 1] = *reinterpret_cast<const uint32_t*>(&v23);
         }
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * (HD / 8) + swz<HD>(row, blk * 4 + c4)) * 16) =
+                make_uint4(out[4 * c4], out[4 * c4 + 1], out[4 * c4 + 2], out[4 * c4 + 3]);
     }
 }
 

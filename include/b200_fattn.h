@@ -174,7 +174,10 @@ B200_API int b200_fattn_launch(const b200_tensor* q, const b200_tensor* k, const
  * round trip of src/voxtral.cpp:1196-1223 in one call.  All `data` pointers
  * (and ext->kv_len) are host pointers; operands are staged through a per-thread
  * device arena that grows on demand, copied in, computed and copied back, and
- * the call returns after the result is in `dst->data`.
+ * the call returns after the result is in `dst->data`.  Batch entries (ne[3]) are
+ * independent, so the call is pipelined over up to four chunks of the batch on two
+ * streams: the upload of one chunk overlaps the kernel and the download of the
+ * previous one.  Pinned host buffers are needed for that overlap to happen.
  */
 B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
                                      const b200_tensor* mask, const b200_tensor* dst,
