@@ -102,7 +102,26 @@ struct Plan {
     FattnArgs args;
     int kernel;
     size_t ws_bytes;
+    bool cast_kv;      // K/V are first converted to contiguous F16 in the workspace (prefill on the tcgen05 kernel)
+    size_t cast_each;  // bytes of one converted tensor, rounded up to 256
 };
+
+// The operand block as the tcgen05 kernel would see it after K/V have been converted to contiguous F16.
+FattnArgs with_f16_kv(const FattnArgs& a, const void* kbuf, const void* vbuf) {
+    FattnArgs c = a;
+    const int Bk = a.B / a.bq;
+    (void)Bk;
+    for (int which = 0; which < 2; which++) {
+        View& v = which ? c.v : c.k;
+        v.p = (const uint8_t*)(which ? vbuf : kbuf);
+        v.type = B200_TYPE_F16;
+        v.nb1 = (int64_t)a.hd * 2;
+        v.nb2 = v.nb1 * a.Lk;
+        v.nb3 = v.nb2 * a.Hkv;
+        v.vec16 = 1;
+    }
+    return c;
+}
 
 // Validates the operands against the op contract and fills the kernel argument block.
 // `need_device` = false keeps the call free of CUDA (supports / plan on a CPU-only host assume 148 SMs).
@@ -197,9 +216,21 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     if (g_override == B200_KERNEL_TILE_MMA) kernel = B200_KERNEL_TILE_MMA;
     if (g_override == B200_KERNEL_DECODE_SPLIT && decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
     if (g_override == B200_KERNEL_PREFILL_TC5 && tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
+    plan->cast_kv = false;
+    plan->cast_each = 0;
+    if (kernel == B200_KERNEL_TILE_MMA && g_override != B200_KERNEL_TILE_MMA && !decode_ok && (a.hd == 64 || a.hd == 128) &&
+        !tc5_ok) {
+        // F32 / Q8_0 / unaligned K/V: a conversion pre-pass into the workspace puts the call on the tcgen05 kernel
+        const FattnArgs c = with_f16_kv(a, (const void*)256, (const void*)256);
+        if (tc5_supported(c)) {
+            kernel = B200_KERNEL_PREFILL_TC5;
+            plan->cast_kv = true;
+            plan->cast_each = ((size_t)a.hd * 2 * a.Lk * a.Hkv * (a.B / a.bq) + 255) / 256 * 256;
+        }
+    }
     plan->kernel = kernel;
     a.n_splits = 1;
-    plan->ws_bytes = 0;
+    plan->ws_bytes = plan->cast_kv ? 2 * plan->cast_each : 0;
     if (kernel == B200_KERNEL_DECODE_SPLIT) {
         a.n_splits = decode_split_choose(a.B, a.Hkv, a.Lk, sm_count);
         plan->ws_bytes = decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
@@ -209,6 +240,20 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
 
 int do_launch(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st) {
     FattnArgs& a = plan.args;
+    if (plan.cast_kv) {
+        if (!workspace || ws_bytes < plan.ws_bytes || (uintptr_t)workspace % 256) return B200_E_WORKSPACE;
+        void* kbuf = workspace;
+        void* vbuf = (uint8_t*)workspace + plan.cast_each;
+        const int Bk = a.B / a.bq;
+        int ce = launch_kv_to_f16(a.k, kbuf, a.hd, a.Lk, a.Hkv, Bk, st);
+        if (ce == 0) ce = launch_kv_to_f16(a.v, vbuf, a.hd, a.Lk, a.Hkv, Bk, st);
+        if (ce != 0) return cuda_fail((cudaError_t)ce, "K/V conversion launch");
+        const FattnArgs c = with_f16_kv(a, kbuf, vbuf);
+        const int rc = launch_prefill_tc5(c, st, g_cuda_err, sizeof(g_cuda_err));
+        if (rc != B200_OK) return rc;
+        g_last_kernel = plan.kernel;
+        return B200_OK;
+    }
     if (plan.ws_bytes) {
         if (!workspace || ws_bytes < plan.ws_bytes || (uintptr_t)workspace % 256) return B200_E_WORKSPACE;
         const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);

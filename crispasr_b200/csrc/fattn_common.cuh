@@ -70,6 +70,8 @@ inline cudaError_t set_smem_once(Kern kern, size_t smem, bool (&done)[64]) {
 // Launchers implemented per kernel family; each returns a cudaError_t-compatible int (0 = ok).
 int launch_tile_mma(const FattnArgs& a, cudaStream_t st);
 int launch_decode_split(const FattnArgs& a, cudaStream_t st);
+// Converts K or V (F32 / Q8_0 / unaligned F16, any strides) to contiguous F16 [hd, Lk, Hkv, Bk] at `dst`.
+int launch_kv_to_f16(const View& src, void* dst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st);
 size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd);
 int decode_split_choose(int B, int Hkv, int Lk, int sm_count);
 

@@ -732,7 +732,29 @@ int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
     }
 }
 
+// K or V of any supported type / stride -> contiguous F16 [hd, Lk, Hkv, Bk] (the operand form of the tcgen05 kernels).
+__global__ void kv_to_f16_kernel(const View src, uint8_t* dst, int hd, int Lk, int Hkv, int Bk) {
+    const int cpr = hd / 8;
+    const int64_t total = (int64_t)Bk * Hkv * Lk * cpr;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int ch = (int)(i % cpr);
+        const int64_t row = i / cpr;  // ((b*Hkv + h)*Lk + k)
+        const int k = (int)(row % Lk);
+        const int h = (int)((row / Lk) % Hkv);
+        const int b = (int)(row / ((int64_t)Lk * Hkv));
+        const uint8_t* rowp = src.p + (int64_t)k * src.nb1 + (int64_t)h * src.nb2 + (int64_t)b * src.nb3;
+        *reinterpret_cast<uint4*>(dst + (row * cpr + ch) * 16) = load8_as_half(rowp, src.type, ch * 8, hd, src.vec16 != 0);
+    }
+}
+
 }  // namespace
+
+int launch_kv_to_f16(const View& src, void* dst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st) {
+    const int64_t total = (int64_t)Bk * Hkv * Lk * (hd / 8);
+    const int blocks = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
+    kv_to_f16_kernel<<<blocks, 256, 0, st>>>(src, (uint8_t*)dst, hd, Lk, Hkv, Bk);
+    return (int)cudaGetLastError();
+}
 
 int launch_tile_mma(const FattnArgs& a, cudaStream_t st) {
     const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);

@@ -229,6 +229,37 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
     lsum_io += (ls[0] + ls[1]) + (ls[2] + ls[3]);
 }
 
+// Explicit F16 mask: turns 64 raw scores into log2-domain logits t = s*c + mask*log2(e) in place (mask -inf stays
+// -inf).  `mptr` points at the mask value of the first of the 64 columns, `avail` is how many mask columns exist
+// from there to the end of the mask row (loads never go past it).  Eight 16-byte loads are in flight at once.
+__device__ __forceinline__ void apply_mask64(uint32_t (&sreg)[2][32], const uint8_t* mptr, int avail, float c) {
+    uint4 mv[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        if (q * 8 + 8 <= avail) {
+            mv[q] = __ldg(reinterpret_cast<const uint4*>(mptr + q * 16));
+        } else {
+            uint16_t hv[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                hv[i] = (q * 8 + i < avail) ? __ldg(reinterpret_cast<const uint16_t*>(mptr + (q * 8 + i) * 2)) : (uint16_t)0;
+            mv[q] = make_uint4(hv[0] | ((uint32_t)hv[1] << 16), hv[2] | ((uint32_t)hv[3] << 16), hv[4] | ((uint32_t)hv[5] << 16),
+                               hv[6] | ((uint32_t)hv[7] << 16));
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const uint32_t w[4] = {mv[q].x, mv[q].y, mv[q].z, mv[q].w};
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float2 m2 = __half22float2(*reinterpret_cast<const __half2*>(&w[u]));
+            const int i = q * 8 + 2 * u;
+            sreg[i >> 5][i & 31] = __float_as_uint(fmaf(__uint_as_float(sreg[i >> 5][i & 31]), c, m2.x * kLog2e));
+            sreg[i >> 5][(i + 1) & 31] = __float_as_uint(fmaf(__uint_as_float(sreg[i >> 5][(i + 1) & 31]), c, m2.y * kLog2e));
+        }
+    }
+}
+
 // One query row (HD elements) -> f16, written into the 128-byte swizzled operand tile: row r, 16-byte chunk c of
 // panel p at p*16384 + r*128 + ((c ^ (r & 7)) * 16).  The type is tested once and all loads of the row are issued
 // before the first store, so the row costs one memory round trip instead of HD/8.
@@ -269,7 +300,7 @@ struct Tc5Smem {
     static constexpr int tile_bytes() { return kPanelBytes * (HD / 64); }
 };
 
-template <int HD, int NSTG>
+template <int HD, int NSTG, bool HASMASK>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV) {
@@ -474,6 +505,11 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         if (a.causal) kend = min(kend, a.n_past + iq + 1);
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
+        // explicit mask row of this query ([Lk, Tq, 1|H, 1|B] F16, 16-byte aligned strides); rows past Tq reuse row 0
+        const uint8_t* mrow = HASMASK ? a.mask.p + (int64_t)(iq < a.Tq ? iq : 0) * a.mask.nb1 +
+                                            (int64_t)(h % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
+                                      : nullptr;
+        const float c_exp = HASMASK ? 1.0f : c;   // with a mask the scores are moved to the log2 domain by apply_mask64
         for (int j = 0; j < n_tiles; j++) {
             ok = mbar_wait(bar_s_full, j & 1, s_abort);
             if (!ok) break;
@@ -490,9 +526,10 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
                     tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
                     tmem_wait_ld();
+                    if (HASMASK) apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
                     mx = fmaxf(mx, row_max64(sreg, hh * 64, full_tile ? 2 * kTile : n_valid));
                 }
-                m_ref = mx * c;  // c > 0
+                m_ref = mx * c_exp;  // c > 0
             }
             uint32_t preg[2][32];
             float lsum = 0.0f;
@@ -510,12 +547,13 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
                     tmem_wait_ld();
                     if (tid == 0) TC5_TRACE(0, j, 3 + 2 * hh);
-                    if (full_tile) softmax64<false>(sreg, preg[hh], c, m_use, 0, 0, mx, lsum);
-                    else softmax64<true>(sreg, preg[hh], c, m_use, hh * 64, n_valid, mx, lsum);
+                    if (HASMASK) apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
+                    if (full_tile) softmax64<false>(sreg, preg[hh], c_exp, m_use, 0, 0, mx, lsum);
+                    else softmax64<true>(sreg, preg[hh], c_exp, m_use, hh * 64, n_valid, mx, lsum);
                     if (tid == 0) TC5_TRACE(0, j, 4 + 2 * hh);
                 }
                 if (tid == 0 && attempt == 1) TC5_TRACE(0, j, 7);
-                const float m_tile = mx * c;
+                const float m_tile = mx * c_exp;
                 const bool grow = m_tile > m_ref + kRescaleThreshold;
                 if (!__any_sync(0xffffffffu, grow)) break;
                 // some row of this warp outgrew its reference maximum: rescale O and l, then redo P
@@ -1054,13 +1092,24 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     }
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
     const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 32 + 16;
-    auto kern = fattn_prefill_tc5_kernel<HD, NSTG>;
-    static bool smem_set[64] = {false};
-    cudaError_t e = set_smem_once(kern, smem, smem_set);
-    if (e == cudaSuccess) {
-        dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
-        kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
-        e = cudaGetLastError();
+    cudaError_t e;
+    dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
+    if (a.has_mask) {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
+            e = cudaGetLastError();
+        }
+    } else {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
+            e = cudaGetLastError();
+        }
     }
     if (e != cudaSuccess) {
         snprintf(errbuf, errlen, "tcgen05 prefill launch: %s", cudaGetErrorString(e));
@@ -1075,8 +1124,9 @@ bool tc5_supported(const FattnArgs& a) {
     if (a.hd != 64 && a.hd != 128) return false;
     if (a.k.type != B200_TYPE_F16 || a.v.type != B200_TYPE_F16) return false;
     if (!a.k.vec16 || !a.v.vec16) return false;
-    if (a.has_mask || a.softcap != 0.0f || a.n2 != 0) return false;
+    if (a.softcap != 0.0f || a.n2 != 0) return false;
     if (!(a.scale > 0.0f)) return false;
+    if (a.has_mask && (a.relpos || !a.mask.vec16)) return false;  // explicit masks: plain kernel, 16-byte aligned rows
     if (a.relpos) {
         // fused bias: head_dim 128, F16 R with TMA-legal strides, no causal mask, bias rounded to F16
         if (a.hd != 128 || a.causal || a.relpos_f32) return false;

@@ -112,6 +112,39 @@ def test_cfg3_large_v3_encoder_segments(b200, orc, kernel):
         assert b200.lib().b200_device_status() == 0
 
 
+def test_voxtral_audio_encoder_f32_kv(b200, orc, kernel):
+    """core_attn::encoder_self_attn (src/core/attention.h:517-580): contiguous F32 Q/K/V, Whisper large dims, no pad,
+    no mask.  K/V are converted to F16 by a pre-pass into the workspace and the call runs on the tcgen05 kernel."""
+    rng = np.random.default_rng(22)
+    H, T, hd = 20, 1500, 64
+    q, k, v = (randn_f16(rng, (1, H, T, hd)).astype(np.float32) for _ in range(3))
+    ref = orc.flash_attn_ext(q, k, v, scale=0.125)
+    assert_close(gpu_op(b200, q, k, v, scale=0.125), ref, "voxtral encoder, F32 K/V")
+    if kernel == "auto":
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5
+        assert b200.workspace_bytes(torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v), scale=0.125) >= 2 * H * T * hd * 2
+
+
+@pytest.mark.parametrize("hd,per_head", [(64, False), (128, True)])
+def test_explicit_mask_prefill(b200, orc, kernel, hd, per_head):
+    """Explicit F16 masks with 16-byte aligned rows (LLM causal prefill mask of src/voxtral.cpp:1187-1194 plus random
+    additive bias and -inf holes, shared or per head) on the tcgen05 kernel."""
+    rng = np.random.default_rng(hd)
+    B, H, Hkv, Tq, Lk = 2, 4, 2, 300, 520
+    q, k, v = randn_f16(rng, (B, H, Tq, hd)), randn_f16(rng, (B, Hkv, Lk, hd)), randn_f16(rng, (B, Hkv, Lk, hd))
+    m = (rng.standard_normal((1, H if per_head else 1, Tq, Lk)) * 0.5).astype(np.float16)
+    m[rng.random(m.shape) < 0.3] = -np.inf
+    m[..., 0] = 0
+    m = m + orc.causal_mask(Lk, Tq, Lk - Tq)[None, None]
+    m[0, 0, 17, :] = -np.inf                      # one fully masked row
+    ref = orc.flash_attn_ext(q, k, v, m, scale=hd ** -0.5)
+    got = gpu_op(b200, q, k, v, m, scale=hd ** -0.5)
+    assert np.all(got[:, 17, 0] == 0)
+    assert_close(got, ref, f"explicit mask hd={hd} per_head={per_head}")
+    if kernel == "auto":
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5
+
+
 # ---- config 4: Voxtral-style LLM decoder, GQA 32/8, hd 128, Q8_0 KV ------------------------------------------
 def _q8_cache(orc, rng, streams, Hkv, rows, hd, max_ctx):
     x = rng.standard_normal((streams, Hkv, rows, hd)).astype(np.float32)
