@@ -37,6 +37,13 @@ WORKLOADS = {
                                           kv="f16", seed=1, unit_name="segment-steps"),
     "voxtral_decode_q8_0": dict(kind="decode", layers=30, units=8, H=32, Hkv=8, Tq=1, Lk=535, hd=128, kv="q8_0",
                                 seed=3, unit_name="stream-steps"),
+    # config 2, self-attention half: 5 beams of one segment over the pooled cell cache (448 private cells each,
+    # padded to 2304), beam membership only in the F16 mask [n_kv, 5]
+    "whisper_large_v3_decode_self": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=2304, hd=64,
+                                         kv="f16", seed=1, unit_name="segment-steps", beam_cells=448),
+    # config 4, prefill half: 375 audio + 32 text tokens, causal, GQA 32/8 over a Q8_0 cache, 8 streams
+    "voxtral_prefill_q8_0": dict(kind="prefill", layers=30, units=8, H=32, Hkv=8, Tq=407, Lk=407, hd=128, kv="q8_0",
+                                 seed=3, unit_name="streams", causal=True),
     "parakeet_relpos_encoder": dict(kind="relpos", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128,
                                     kv="f16", seed=4, unit_name="utterances"),
 }
@@ -121,9 +128,13 @@ def scale_of(w):
 def algorithmic_work(w, units):
     """Per launch (one layer over `units` units): FLOPs for tensor-bound forms, bytes for HBM-bound ones."""
     if w["kind"] in ("prefill", "relpos"):
-        return dict(bound="tensor", amount=4.0 * w["Tq"] * w["Lk"] * w["hd"] * w["H"] * units, unit="TFLOP/s", div=1e12)
+        flops = 4.0 * w["Tq"] * w["Lk"] * w["hd"] * w["H"] * units
+        if w.get("causal"):
+            flops = 2.0 * w["Tq"] * (w["Lk"] + 1) * w["hd"] * w["H"] * units   # lower triangle only
+        return dict(bound="tensor", amount=flops, unit="TFLOP/s", div=1e12)
     row = w["hd"] * 2 if w["kv"] == "f16" else w["hd"] // 32 * 34
-    kv_bytes = 2.0 * w["Lk"] * w["Hkv"] * row * units
+    rows = w["Tq"] * w["beam_cells"] if "beam_cells" in w else w["Lk"]    # valid cells only
+    kv_bytes = 2.0 * rows * w["Hkv"] * row * units
     qo_bytes = units * w["H"] * w["Tq"] * w["hd"] * (2 + 4)
     return dict(bound="hbm", amount=kv_bytes + qo_bytes, unit="GB/s", div=1e9)
 
@@ -135,6 +146,8 @@ def oracle_kwargs(w, extra):
         kw["kv_type"] = abi.Q8_0
     if w["kind"] == "relpos":
         kw.update(q_v=extra["q_v"], r=extra["r"])
+    if w.get("causal"):
+        kw.update(causal=True, n_past=0)
     return kw
 
 
@@ -258,16 +271,30 @@ def main():
         kw["kv_type"] = abi.Q8_0
     if w["kind"] == "relpos":
         kw["q_v"], kw["r"] = up(extra["q_v"]), torch.from_numpy(extra["r"]).to(dev)
+    if w.get("causal"):
+        kw["causal"], kw["n_past"] = True, 0
+    mask = None
+    if "beam_cells" in w:
+        from oracle import oracle as orc_mask
+        L, beams = w["beam_cells"], w["Tq"]
+        cell_pos = np.full(w["Lk"], 10 ** 6, np.int32)
+        bits = np.zeros(w["Lk"], np.uint32)
+        for jb in range(beams):
+            cell_pos[jb * L:(jb + 1) * L], bits[jb * L:(jb + 1) * L] = np.arange(L), 1 << jb
+        m = orc_mask.whisper_beam_mask(cell_pos, bits, tok_seq=np.arange(beams), tok_pos=np.full(beams, L - 1))
+        mask = torch.from_numpy(m[None, None]).to(dev)
     out = torch.empty((units, w["Tq"], w["H"], w["hd"]), dtype=torch.float32, device=dev)
-    ws_bytes = b200.workspace_bytes(q, k, v, **kw)
+    ws_bytes = b200.workspace_bytes(q, k, v, mask, **kw)
     ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    kernel_id, n_splits = b200.plan(q, k, v, **kw)
+    kernel_id, n_splits = b200.plan(q, k, v, mask, **kw)
     launches_per_layer = 1 + (1 if (kernel_id == abi.KERNEL_DECODE_SPLIT and n_splits > 1) else 0)
+    if kernel_id == abi.KERNEL_PREFILL_TC5 and ws_bytes:
+        launches_per_layer += 2   # K and V conversion pre-pass
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if w["kind"] != "prefill" else None
 
     def step():
         for _ in range(w["layers"]):
-            b200.flash_attn_ext(q, k, v, out=out, workspace=ws, **kw)
+            b200.flash_attn_ext(q, k, v, mask, out=out, workspace=ws, **kw)
 
     def barrier():
         if world > 1:
@@ -317,11 +344,12 @@ def main():
         hkw = dict(kw)
         if w["kind"] == "relpos":
             hkw["q_v"], hkw["r"] = kw["q_v"][:e2e_units].cpu().pin_memory(), kw["r"].cpu().pin_memory()
+        hmask = mask.cpu().pin_memory() if mask is not None else None
         hout = torch.empty((e2e_units, w["Tq"], w["H"], w["hd"]), dtype=torch.float32).pin_memory()
         e2e_layers = w["layers"]
         def e2e_step():
             for _ in range(e2e_layers):
-                b200.flash_attn_ext_host(hq, hk, hv, out=hout, **hkw)
+                b200.flash_attn_ext_host(hq, hk, hv, hmask, out=hout, **hkw)
         e2e_step()
         barrier()
         n_e2e = max(1, min(args.steps, 3))

@@ -89,6 +89,7 @@ SYMBOLS = {
     "b200_kv_bytes": (C.c_size_t, [C.c_void_p]),
     "b200_kv_view": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, TP, TP]),
     "b200_kv_append": (C.c_int, [C.c_void_p, C.c_int, TP, TP, C.c_void_p, C.c_int32, C.c_void_p]),
+    "b200_kv_copy_stream": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "b200_sched_create": (C.c_int, [C.POINTER(C.c_int), C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "b200_sched_destroy": (None, [C.c_void_p]),
     "b200_sched_run": (C.c_int, [C.c_void_p, C.c_int, UNIT_FN, C.c_void_p, C.POINTER(C.c_int)]),

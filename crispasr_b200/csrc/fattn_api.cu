@@ -103,8 +103,26 @@ struct Plan {
     int kernel;
     size_t ws_bytes;
     bool cast_kv;      // K/V are first converted to contiguous F16 in the workspace (prefill on the tcgen05 kernel)
-    size_t cast_each;  // bytes of one converted tensor, rounded up to 256
+    bool cast_r;       // the same for the rel-pos table R
+    size_t cast_each;  // bytes of one converted K or V tensor, rounded up to 256
+    size_t cast_r_bytes;
 };
+
+bool kv_is_tma_ready(const FattnArgs& a) {
+    return a.k.type == B200_TYPE_F16 && a.v.type == B200_TYPE_F16 && a.k.vec16 && a.v.vec16;
+}
+bool r_is_tma_ready(const FattnArgs& a) { return !a.relpos || (a.r.type == B200_TYPE_F16 && a.r.vec16); }
+
+FattnArgs with_f16_r(const FattnArgs& a, const void* rbuf) {
+    FattnArgs c = a;
+    c.r.p = (const uint8_t*)rbuf;
+    c.r.type = B200_TYPE_F16;
+    c.r.nb1 = (int64_t)a.hd * 2;
+    c.r.nb2 = c.r.nb1 * (2 * a.Tq - 1);
+    c.r.nb3 = c.r.nb2 * a.H;
+    c.r.vec16 = 1;
+    return c;
+}
 
 // The operand block as the tcgen05 kernel would see it after K/V have been converted to contiguous F16.
 FattnArgs with_f16_kv(const FattnArgs& a, const void* kbuf, const void* vbuf) {
@@ -216,21 +234,24 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     if (g_override == B200_KERNEL_TILE_MMA) kernel = B200_KERNEL_TILE_MMA;
     if (g_override == B200_KERNEL_DECODE_SPLIT && decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
     if (g_override == B200_KERNEL_PREFILL_TC5 && tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
-    plan->cast_kv = false;
-    plan->cast_each = 0;
+    plan->cast_kv = plan->cast_r = false;
+    plan->cast_each = plan->cast_r_bytes = 0;
     if (kernel == B200_KERNEL_TILE_MMA && g_override != B200_KERNEL_TILE_MMA && !decode_ok && (a.hd == 64 || a.hd == 128) &&
         !tc5_ok) {
         // F32 / Q8_0 / unaligned K/V: a conversion pre-pass into the workspace puts the call on the tcgen05 kernel
-        const FattnArgs c = with_f16_kv(a, (const void*)256, (const void*)256);
+        FattnArgs c = kv_is_tma_ready(a) ? a : with_f16_kv(a, (const void*)256, (const void*)256);
+        if (!r_is_tma_ready(a)) c = with_f16_r(c, (const void*)256);
         if (tc5_supported(c)) {
             kernel = B200_KERNEL_PREFILL_TC5;
-            plan->cast_kv = true;
-            plan->cast_each = ((size_t)a.hd * 2 * a.Lk * a.Hkv * (a.B / a.bq) + 255) / 256 * 256;
+            plan->cast_kv = !kv_is_tma_ready(a);
+            plan->cast_r = !r_is_tma_ready(a);
+            if (plan->cast_kv) plan->cast_each = ((size_t)a.hd * 2 * a.Lk * a.Hkv * (a.B / a.bq) + 255) / 256 * 256;
+            if (plan->cast_r) plan->cast_r_bytes = ((size_t)a.hd * 2 * (2 * a.Tq - 1) * a.H * a.r_ne3 + 255) / 256 * 256;
         }
     }
     plan->kernel = kernel;
     a.n_splits = 1;
-    plan->ws_bytes = plan->cast_kv ? 2 * plan->cast_each : 0;
+    plan->ws_bytes = 2 * plan->cast_each + plan->cast_r_bytes;
     if (kernel == B200_KERNEL_DECODE_SPLIT) {
         a.n_splits = decode_split_choose(a.B, a.Hkv, a.Lk, sm_count);
         plan->ws_bytes = decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
@@ -240,15 +261,24 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
 
 int do_launch(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st) {
     FattnArgs& a = plan.args;
-    if (plan.cast_kv) {
+    if (plan.cast_kv || plan.cast_r) {
         if (!workspace || ws_bytes < plan.ws_bytes || (uintptr_t)workspace % 256) return B200_E_WORKSPACE;
-        void* kbuf = workspace;
-        void* vbuf = (uint8_t*)workspace + plan.cast_each;
-        const int Bk = a.B / a.bq;
-        int ce = launch_kv_to_f16(a.k, kbuf, a.hd, a.Lk, a.Hkv, Bk, st);
-        if (ce == 0) ce = launch_kv_to_f16(a.v, vbuf, a.hd, a.Lk, a.Hkv, Bk, st);
-        if (ce != 0) return cuda_fail((cudaError_t)ce, "K/V conversion launch");
-        const FattnArgs c = with_f16_kv(a, kbuf, vbuf);
+        FattnArgs c = a;
+        int ce = 0;
+        if (plan.cast_kv) {
+            void* kbuf = workspace;
+            void* vbuf = (uint8_t*)workspace + plan.cast_each;
+            const int Bk = a.B / a.bq;
+            ce = launch_kv_to_f16(a.k, kbuf, a.hd, a.Lk, a.Hkv, Bk, st);
+            if (ce == 0) ce = launch_kv_to_f16(a.v, vbuf, a.hd, a.Lk, a.Hkv, Bk, st);
+            c = with_f16_kv(c, kbuf, vbuf);
+        }
+        if (ce == 0 && plan.cast_r) {
+            void* rbuf = (uint8_t*)workspace + 2 * plan.cast_each;
+            ce = launch_kv_to_f16(a.r, rbuf, a.hd, 2 * a.Tq - 1, a.H, a.r_ne3, st);
+            c = with_f16_r(c, rbuf);
+        }
+        if (ce != 0) return cuda_fail((cudaError_t)ce, "operand conversion launch");
         const int rc = launch_prefill_tc5(c, st, g_cuda_err, sizeof(g_cuda_err));
         if (rc != B200_OK) return rc;
         g_last_kernel = plan.kernel;

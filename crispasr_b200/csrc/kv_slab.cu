@@ -177,4 +177,25 @@ B200_API int b200_kv_append(b200_kv_cache* kv, int layer, const b200_tensor* k_n
     return B200_OK;
 }
 
+B200_API int b200_kv_copy_stream(b200_kv_cache* kv, int dst_stream, int src_stream, int64_t n_rows, void* cuda_stream) {
+    if (!kv) return B200_E_NULL;
+    if (dst_stream < 0 || src_stream < 0 || dst_stream >= kv->cfg.n_streams || src_stream >= kv->cfg.n_streams)
+        return B200_E_SHAPE;
+    if (n_rows < 0 || n_rows > kv->ctx_rows) return B200_E_SHAPE;
+    if (dst_stream == src_stream || n_rows == 0) return B200_OK;
+    const size_t head_pitch = kv->row_bytes * kv->ctx_rows;
+    const size_t stream_pitch = head_pitch * kv->cfg.n_kv_heads;
+    for (int slab = 0; slab < 2 * kv->cfg.n_layers; slab++) {
+        uint8_t* base = kv->base + kv->slab_bytes * slab;
+        // one 2-D copy per slab: n_kv_heads rows of n_rows*row_bytes bytes, head_pitch apart
+        if (cudaMemcpy2DAsync(base + stream_pitch * dst_stream, head_pitch, base + stream_pitch * src_stream, head_pitch,
+                              (size_t)n_rows * kv->row_bytes, kv->cfg.n_kv_heads, cudaMemcpyDeviceToDevice,
+                              (cudaStream_t)cuda_stream) != cudaSuccess) {
+            cudaGetLastError();
+            return B200_E_CUDA;
+        }
+    }
+    return B200_OK;
+}
+
 }  // extern "C"

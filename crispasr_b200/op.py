@@ -164,6 +164,15 @@ class KvCache:
             raise _err(rc, "b200_kv_append")
 
 
+    def copy_stream(self, dst_stream, src_stream, n_rows, stream=None):
+        """Fork a hypothesis: rows [0, n_rows) of every layer/head from one stream to another (kv_snapshot_pool)."""
+        import torch
+        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        rc = _lib().b200_kv_copy_stream(self._h, int(dst_stream), int(src_stream), int(n_rows), st)
+        if rc:
+            raise _err(rc, "b200_kv_copy_stream")
+
+
 class SegmentScheduler:
     """b200_sched_*: independent units over one worker thread per GPU (or host-only workers)."""
 

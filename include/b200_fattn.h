@@ -252,6 +252,15 @@ B200_API int b200_kv_view(const b200_kv_cache* kv, int layer, int64_t n_rows, b2
 B200_API int b200_kv_append(b200_kv_cache* kv, int layer, const b200_tensor* k_new, const b200_tensor* v_new,
                             const int32_t* pos, int32_t pos0, void* cuda_stream);
 
+/*
+ * b200_kv_copy_stream — replaces core_attn::kv_snapshot_pool save/restore (src/core/attention.h:198-320), the
+ * device-to-device blits that branched beam search uses to fork a hypothesis: copies rows [0, n_rows) of every
+ * layer and head from stream `src_stream` to stream `dst_stream` of the same cache (one 2-D copy per slab),
+ * asynchronously on `cuda_stream`.  Beams that only share a prefix need no copy at all: they can read the same
+ * stream with different kv_len / masks.
+ */
+B200_API int b200_kv_copy_stream(b200_kv_cache* kv, int dst_stream, int src_stream, int64_t n_rows, void* cuda_stream);
+
 /* ------------------------------------------------------------------------------------------
  * Segment scheduler.  Replaces the `-p N` worker instances with an atomic next-slice cursor
  * (examples/cli/crispasr_run.cpp:1882-1930) and whisper_full_parallel (src/crispasr.cpp:8755-8880)

@@ -218,6 +218,8 @@ def test_cfg5_fused_relpos_bias(b200, orc, kernel, T):
     ref = orc.flash_attn_ext(q_u, k, v, mask, scale=scale)
     got_fused = gpu_op(b200, q_u, k, v, scale=scale, q_v=q_v, r=r)
     assert_close(got_fused, ref, f"cfg5 fused T={T}")
+    got_f32r = gpu_op(b200, q_u, k, v, scale=scale, q_v=q_v, r=r.astype(np.float32))   # R as the runtimes hold it (F32)
+    assert_close(got_f32r, ref, f"cfg5 fused, F32 R, T={T}")
     got_mask = gpu_op(b200, q_u, k, v, mask, scale=scale)       # per-head mask form of the plain op
     assert_close(got_mask, ref, f"cfg5 per-head mask T={T}")
 

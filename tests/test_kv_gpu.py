@@ -84,6 +84,27 @@ def test_decode_through_slab(b200, orc, type_):
     kv.close()
 
 
+def test_copy_stream_forks_a_beam(b200):
+    """kv_snapshot_pool semantics: after the copy the destination stream reads the source's first n rows, other
+    streams and rows beyond n are untouched."""
+    hd, heads, streams = 64, 3, 4
+    kv = b200.KvCache(abi.F16, hd, heads, n_layers=2, max_ctx=64, n_streams=streams)
+    rng = np.random.default_rng(5)
+    x = torch.from_numpy(rng.standard_normal((streams, heads, 40, hd)).astype(np.float32)).cuda()
+    for layer in range(2):
+        kv.append(layer, x + layer, x - layer, pos0=0)
+    kv.copy_stream(dst_stream=2, src_stream=0, n_rows=25)
+    torch.cuda.synchronize()
+    for layer in range(2):
+        k, _ = kv.view(layer, 40)
+        raw = _read_slab(k, k.nb[3] * streams).view(np.float16).reshape(streams, heads, -1, hd)[:, :, :40]
+        want = (x + layer).cpu().numpy().astype(np.float16)
+        assert np.array_equal(raw[2, :, :25], want[0, :, :25])
+        assert np.array_equal(raw[2, :, 25:], want[2, :, 25:])
+        assert np.array_equal(raw[[0, 1, 3]], want[[0, 1, 3]])
+    kv.close()
+
+
 def test_scheduler_on_device(b200, orc):
     """Units processed by the per-GPU worker thread on its own stream."""
     rng = np.random.default_rng(7)
