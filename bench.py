@@ -44,6 +44,9 @@ WORKLOADS = {
     # config 4, prefill half: 375 audio + 32 text tokens, causal, GQA 32/8 over a Q8_0 cache, 8 streams
     "voxtral_prefill_q8_0": dict(kind="prefill", layers=30, units=8, H=32, Hkv=8, Tq=407, Lk=407, hd=128, kv="q8_0",
                                  seed=3, unit_name="streams", causal=True),
+    # roofline probe, not a BASELINE config: the FastConformer dims without the rel-pos bias (plain hd-128 prefill)
+    "hd128_prefill_probe": dict(kind="prefill", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128, kv="f16",
+                                seed=4, unit_name="utterances"),
     "parakeet_relpos_encoder": dict(kind="relpos", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128,
                                     kv="f16", seed=4, unit_name="utterances"),
 }
