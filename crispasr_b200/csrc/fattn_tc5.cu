@@ -657,7 +657,8 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmR) {
     constexpr int HD = 128;
     constexpr int TILE_BYTES = 2 * kPanelBytes;  // 128 rows x 128 halves
-    constexpr uint32_t IDESC_S = idesc_f16(kTile, false);   // also used for each 128-column half of X
+    constexpr uint32_t IDESC_S = idesc_f16(kTile, false);
+    constexpr uint32_t IDESC_X = idesc_f16(2 * kTile, false);  // N = 256: the whole band in one instruction
     constexpr uint32_t IDESC_PV = idesc_f16(HD, true);
 
     extern __shared__ uint8_t smem_dyn[];
@@ -693,12 +694,14 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     }
     const int rb0 = a.Tq - 1 - q0 - 127;  // first R row of half-block 0 (may be negative: TMA zero-fills)
 
-    // half-block m of R -> ring slot m % 2 (two 64-column panels of 128 rows)
+    // half-block m of R -> ring slot m % 2.  The ring is laid out panel-major, [panel 0: slot 0 | slot 1][panel 1:
+    // slot 0 | slot 1] (16 KB each), so that per 64-column panel the 256 rows of both slots are contiguous and the
+    // band GEMM can address them as one N = 256 operand.
     auto load_r = [&](int m) {
         const int slot = m & 1;
         mbar_arrive_expect_tx(bar_r_full + 8 * slot, TILE_BYTES);
-        tma_load_4d(sR + slot * TILE_BYTES, &tmR, bar_r_full + 8 * slot, 0, rb0 + kTile * m, h, rb3);
-        tma_load_4d(sR + slot * TILE_BYTES + kPanelBytes, &tmR, bar_r_full + 8 * slot, 64, rb0 + kTile * m, h, rb3);
+        tma_load_4d(sR + slot * kPanelBytes, &tmR, bar_r_full + 8 * slot, 0, rb0 + kTile * m, h, rb3);
+        tma_load_4d(sR + 2 * kPanelBytes + slot * kPanelBytes, &tmR, bar_r_full + 8 * slot, 64, rb0 + kTile * m, h, rb3);
     };
     auto load_kv = [&](int j, bool is_v) {
         const uint32_t bar = is_v ? bar_v_full : bar_k_full;
@@ -768,16 +771,16 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     } else if (warp == 5) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            auto issue_x = [&](int j) {  // X[j] from half-blocks j (columns 0..127) and j+1 (columns 128..255)
+            // X[j] = Q_v . [ring slot 0 | ring slot 1]^T as ONE N=256 MMA per k-step (A is fetched once instead of
+            // twice).  Slot 0 holds half-block j for even j and half-block j+1 for odd j, so for odd j the two
+            // 128-column halves of X come out swapped; the softmax threads account for that in their column base.
+            auto issue_x = [&](int j) {
 #pragma unroll
-                for (int hb = 0; hb < 2; hb++) {
-                    const uint32_t rslot = sR + ((j + hb) & 1) * TILE_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < HD / 16; ks++) {
-                        const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-                        mma_ss(tmem_X + hb * 128, smem_desc(sQv + off, 16, 1024), smem_desc(rslot + off, 16, 1024), IDESC_S,
-                               ks > 0 ? 1u : 0u);
-                    }
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    // per panel: rows 0..127 of the B operand are slot 0, rows 128..255 slot 1 (contiguous 32 KB)
+                    const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+                    const uint32_t roff = (ks >> 2) * 2 * kPanelBytes + (ks & 3) * 32;
+                    mma_ss(tmem_X, smem_desc(sQv + off, 16, 1024), smem_desc(sR + roff, 16, 1024), IDESC_X, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(bar_x_full);
                 tc_commit(bar_r_empty + 8 * (j & 1));
@@ -855,18 +858,18 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             float u[4][32];
             auto bounce_chunk = [&](const uint32_t (&xr)[32], int k) {
                 // scale, then round to 11 significant bits (the f16 the reference casts its mask to) with Veltkamp's
-                // splitting: three fp32 operations instead of two format conversions; store chunk k in the ring
+                // splitting: three fp32 operations instead of two format conversions; store chunk k in the ring.
+                // All 32 values are computed before the first store so the arithmetic of different elements overlaps.
+                uint32_t w[32];
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float v = __fmul_rn(__uint_as_float(xr[i + e]), bscale);   // _rn: never contracted
-                        const float g = __fmul_rn(v, 8193.0f);
-                        w[e] = __float_as_uint(__fsub_rn(g, __fsub_rn(g, v)));
-                    }
-                    st_shared_v4(bnc_row + ((((k & 1) * 32 + i) * 4 + rot * 4) & 255), w[0], w[1], w[2], w[3]);
+                for (int i = 0; i < 32; i++) {
+                    const float v = __fmul_rn(__uint_as_float(xr[i]), bscale);   // _rn: never contracted into an fma
+                    const float g = __fmul_rn(v, 8193.0f);
+                    w[i] = __float_as_uint(__fsub_rn(g, __fsub_rn(g, v)));
                 }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    st_shared_v4(bnc_row + ((((k & 1) * 32 + i) * 4 + rot * 4) & 255), w[i], w[i + 1], w[i + 2], w[i + 3]);
             };
             auto read_quarter = [&](int qq) {  // tile columns [32qq, 32qq+32): ring words shift .. shift+31 of chunks qq, qq+1
 #pragma unroll
@@ -874,37 +877,16 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                     u[qq][t2] = __uint_as_float(ld_shared_b32(bnc_row + (((qq * 32 + shift + t2) * 4 + rot * 4) & 255)));
             };
             {
+                const uint32_t xswap = (j & 1) ? 128u : 0u;  // odd tiles: the two 128-column halves of X are swapped
                 uint32_t xa[3][32], xb[2][32];
-#ifdef B200_TC5_TRACE
-                long long c0 = clock64();
-#endif
 #pragma unroll
-                for (int k = 0; k < 3; k++) tmem_ld32(tmem_X + lane_base + x_col0 + k * 32, xa[k]);
-#ifdef B200_TC5_TRACE
-                long long c1 = clock64();
-#endif
+                for (int k = 0; k < 3; k++) tmem_ld32(tmem_X + lane_base + ((x_col0 + k * 32 + xswap) & 255u), xa[k]);
                 tmem_wait_ld();
-#ifdef B200_TC5_TRACE
-                long long c2 = clock64();
-#endif
 #pragma unroll
-                for (int k = 0; k < 2; k++) tmem_ld32(tmem_X + lane_base + x_col0 + (3 + k) * 32, xb[k]);
-#ifdef B200_TC5_TRACE
-                long long c3 = clock64();
-#endif
+                for (int k = 0; k < 2; k++) tmem_ld32(tmem_X + lane_base + ((x_col0 + (3 + k) * 32 + xswap) & 255u), xb[k]);
                 bounce_chunk(xa[0], 0);
-#ifdef B200_TC5_TRACE
-                long long c4 = clock64();
-#endif
                 bounce_chunk(xa[1], 1);
                 read_quarter(0);
-#ifdef B200_TC5_TRACE
-                long long c5 = clock64();
-                if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == 0 && j < 64) {
-                    g_tc5_trace[2][j][2] = c1 - c0; g_tc5_trace[2][j][3] = c2 - c1; g_tc5_trace[2][j][4] = c3 - c2;
-                    g_tc5_trace[2][j][5] = c4 - c3; g_tc5_trace[2][j][6] = c5 - c4;
-                }
-#endif
                 bounce_chunk(xa[2], 2);
                 read_quarter(1);
                 tmem_wait_ld();
