@@ -52,6 +52,19 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel for one launch, from the ncu captures summarised
+# under profiles/ (bytes, units per GPU of the captured launch).  Traffic grows in proportion to the units, so the
+# bench scales it to its own launch size.
+NCU_TRAFFIC = {
+    "whisper_large_v3_encoder": (122.38e6, 8),
+    "whisper_large_v3_decode_cross": (498.06e6, 64),
+    "whisper_large_v3_decode_self": (761.43e6, 64),
+    "voxtral_decode_q8_0": (307.89e6, 256),
+    "parakeet_relpos_encoder": (103.99e6, 1),
+    "hd128_prefill_probe": (48.01e6, 1),
+}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -383,7 +396,10 @@ def main():
     achieved = work["amount"] / launch_s / work["div"]
     peak = pk["tensor"] if work["bound"] == "tensor" else pk["hbm"]
     roofline = {"bound": work["bound"], "achieved": achieved, "peak": peak, "unit": work["unit"],
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak,
+                "traffic": (NCU_TRAFFIC[args.workload][0] * units / NCU_TRAFFIC[args.workload][1]
+                            if args.workload in NCU_TRAFFIC else None),
+                "traffic_source": "ncu capture under profiles/, scaled by units" if args.workload in NCU_TRAFFIC else None,
                 "peak_source": f"{pk['src']} ({'sustained bf16 GEMM' if work['bound'] == 'tensor' else 'copy'})",
                 "kernel": abi.KERNEL_NAMES[kernel_id], "launch_ms": launch_s * 1e3,
                 "algorithmic_per_launch": work["amount"]}
