@@ -207,7 +207,7 @@ def run_reference(args, w, rank, world):
         "impl": "reference", "metric": f"attention {unit} ({args.workload})", "value": value, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 softmax/accumulate over f16/q8_0 operands",
-        "data": "synthetic", "config": config_of(args, w, 1),
+        "data": "synthetic", "config": config_of(args, w, args.units or w["units"]),
         "cpu_baseline": {"value": value, "unit": unit, "cores": orc.max_threads(), "kind": "port",
                          "sample": f"1 {w['unit_name'][:-1]} x {layers_per_step} of {w['layers']} layers per step, scaled to the full stack"},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import os
+import shutil
 import subprocess
 import sys
 
@@ -36,6 +37,9 @@ def needs_build() -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
+        return LIB
+    if not force and os.path.exists(LIB) and shutil.which(_nvcc()) is None and not os.path.exists(_nvcc()):
+        # a prebuilt library travelled here and there is no compiler to refresh it with: use it as it is
         return LIB
     objs = []
     procs = []
