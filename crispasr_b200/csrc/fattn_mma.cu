@@ -379,7 +379,10 @@ __device__ __forceinline__ void issue_tile_q8raw(uint8_t* sm, const uint8_t* bas
 template <int HD>
 __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, int rows_valid, int tid) {
     constexpr int NBLK = HD / 32, RB = NBLK * 34;
-    for (int idx = tid; idx < kDecBN * NBLK; idx += kThreads) {
+#pragma unroll
+    for (int idx0 = 0; idx0 < kDecBN * NBLK; idx0 += kThreads) {
+        const int idx = idx0 + tid;
+        if (kDecBN * NBLK % kThreads != 0 && idx >= kDecBN * NBLK) break;
         const int row = idx / NBLK, blk = idx % NBLK;
         const uint16_t* src = reinterpret_cast<const uint16_t*>(raw + row * RB + blk * 34);
         if (row >= rows_valid) {  // rows past the valid length read as zeros whatever the copy brought in
@@ -424,7 +427,7 @@ template <int HD, int MODE>
 __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
     constexpr int RAW_BYTES = kDecBN * (HD / 32 * 34);    // one raw Q8_0 K or V tile
-    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 3);
+    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 2);
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);              // [16][HD]
     // fp16 tiles: NS stages (async F16) or one pair (sync, Q8)
@@ -684,7 +687,7 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
 
 template <int HD, int MODE>
 int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
-    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 3);
+    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 2);
     constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
     size_t smem = (size_t)(kDecRows + F16_STAGES * 2 * kDecBN) * HD * sizeof(__half);
     if (MODE == kDecAsyncQ8) smem += (size_t)NS * 2 * kDecBN * (HD / 32 * 34);

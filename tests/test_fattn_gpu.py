@@ -301,6 +301,29 @@ def test_host_buffer_entry_point(b200, orc):
     b200.lib().b200_host_arena_release()
 
 
+def test_full_size_properties_cfg3(b200, orc):
+    """BASELINE size of the encoder workload (64 segments x 20 heads x 1500 frames, one layer): two sampled
+    segments against the oracle, batch invariance (a segment computed inside the batch equals the same segment
+    computed alone, bit for bit), softmax weights summing to one (V = ones), and linearity in V."""
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    S, H, T, hd = 64, 20, 1500, 64
+    q, k, v = (torch.randn((S, H, T, hd), generator=gen, device="cuda", dtype=torch.float32).half() for _ in range(3))
+    out = b200.flash_attn_ext(q, k, v, scale=0.125)
+    torch.cuda.synchronize()
+    assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5 and b200.lib().b200_device_status() == 0
+    for seg in (0, 41):
+        ref = orc.flash_attn_ext(q[seg:seg + 1].cpu().numpy(), k[seg:seg + 1].cpu().numpy(), v[seg:seg + 1].cpu().numpy(), scale=0.125)
+        assert_close(out[seg:seg + 1].cpu().numpy(), ref, f"cfg3 full batch, segment {seg}")
+        alone = b200.flash_attn_ext(q[seg:seg + 1], k[seg:seg + 1], v[seg:seg + 1], scale=0.125)
+        assert torch.equal(alone[0], out[seg]), "a segment's result must not depend on its batch neighbours"
+    ones = b200.flash_attn_ext(q, k, torch.ones_like(v), scale=0.125)
+    assert float((ones - 1.0).abs().max()) < 2e-3
+    v2 = torch.randn((S, H, T, hd), generator=gen, device="cuda", dtype=torch.float32).half()
+    lin = b200.flash_attn_ext(q[:4], k[:4], (v[:4].float() * 0.5 + v2[:4].float() * 0.25).half(), scale=0.125)
+    want = 0.5 * out[:4] + 0.25 * b200.flash_attn_ext(q[:4], k[:4], v2[:4], scale=0.125)
+    assert float((lin - want).abs().max()) < 4e-3   # V is re-rounded to f16 after the combination
+
+
 def test_full_size_properties_cfg5(b200, orc):
     """BASELINE size (T = 7500, 8 heads, hd 128): sampled query rows against the oracle, plus the
     size-independent property that softmax weights sum to one (V = ones gives ones)."""
