@@ -641,16 +641,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
 // MMA order: X[0] S[0] | per tile j: X[j+1] as soon as the softmax threads have drained X[j]; then, once
 // P[j] is in TMEM, PV[j] and S[j+1].
 // ------------------------------------------------------------------------------------------------------
-constexpr int kBncStride = 256;  // bytes per bounce row: a ring of 64 fp32 words
-
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_shared_b32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
+constexpr int kBncStride = 128;  // bytes per bounce row: a ring of 64 f16 values
 
 __global__ void __launch_bounds__(kThreadsTc5, 1)
 fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
@@ -840,10 +831,11 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         const float bscale = a.relscale;   // == a.scale: the tcgen05 path is not taken with a softcap
         const int shift = 31 - lane;                        // band offset of this row inside the warp's columns
-        // Bounce ring of this row: 64 fp32 words, rotated by 4*lane words so that the 16-byte stores (same logical
-        // chunk in every lane) and the 4-byte loads (logical word c - lane) are both bank-conflict free.
-        const uint32_t bnc_row = sBnc + r * kBncStride;
-        const uint32_t rot = 4u * lane;
+        // Bounce ring of this row: 64 f16 values (two 32-column chunks) = 32 words.
+        uint8_t* const bnc_gen = smem_gen + (sBnc - smem_base) + r * kBncStride;   // this thread's ring (generic pointer)
+        // rotation in words: 16-byte stores of the same logical chunk by the 8 lanes of a quarter-warp, and 4-byte
+        // loads of logical word (const - lane/2) by all 32 lanes, both hit 32 distinct banks (found by enumeration)
+        const uint32_t rot = 4u * ((lane + 3u * (lane >> 3)) & 7u);
         const uint32_t x_col0 = 96 - 32 * warp;             // first X column any row of this warp can need
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
@@ -857,24 +849,27 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             // so they are issued in two deep batches per phase and overlapped with the arithmetic of the previous batch.
             float u[4][32];
             auto bounce_chunk = [&](const uint32_t (&xr)[32], int k) {
-                // scale, then round to 11 significant bits (the f16 the reference casts its mask to) with Veltkamp's
-                // splitting: three fp32 operations instead of two format conversions; store chunk k in the ring.
-                // All 32 values are computed before the first store so the arithmetic of different elements overlaps.
-                uint32_t w[32];
+                // scale*x rounded to f16 (the reference's cast of its mask), 32 values = 16 words, into ring half k&1
+                uint32_t w[16];
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float v = __fmul_rn(__uint_as_float(xr[i]), bscale);   // _rn: never contracted into an fma
-                    const float g = __fmul_rn(v, 8193.0f);
-                    w[i] = __float_as_uint(__fsub_rn(g, __fsub_rn(g, v)));
-                }
+                for (int i = 0; i < 16; i++)
+                    w[i] = cvt_f16x2(__uint_as_float(xr[2 * i]) * bscale, __uint_as_float(xr[2 * i + 1]) * bscale);
 #pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    st_shared_v4(bnc_row + ((((k & 1) * 32 + i) * 4 + rot * 4) & 255), w[i], w[i + 1], w[i + 2], w[i + 3]);
+                for (int i = 0; i < 16; i += 4)
+                    *reinterpret_cast<uint4*>(bnc_gen + ((((k & 1) * 16 + i + rot) & 31) << 2)) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
             };
-            auto read_quarter = [&](int qq) {  // tile columns [32qq, 32qq+32): ring words shift .. shift+31 of chunks qq, qq+1
+            auto read_quarter = [&](int qq) {  // tile columns [32qq, 32qq+32): ring halves shift .. shift+31 of chunks qq, qq+1
+                const uint32_t h0 = (uint32_t)(qq * 32 + shift);  // first half-word (mod 64)
+                const uint32_t fs = (h0 & 1u) * 16u;
+                uint32_t prev = *reinterpret_cast<const uint32_t*>(bnc_gen + ((((h0 >> 1) + rot) & 31) << 2));
 #pragma unroll
-                for (int t2 = 0; t2 < 32; t2++)
-                    u[qq][t2] = __uint_as_float(ld_shared_b32(bnc_row + (((qq * 32 + shift + t2) * 4 + rot * 4) & 255)));
+                for (int p2 = 0; p2 < 16; p2++) {
+                    const uint32_t next = *reinterpret_cast<const uint32_t*>(bnc_gen + ((((h0 >> 1) + p2 + 1 + rot) & 31) << 2));
+                    const uint32_t pk = __funnelshift_r(prev, next, fs);
+                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&pk));
+                    u[qq][2 * p2] = f2.x, u[qq][2 * p2 + 1] = f2.y;
+                    prev = next;
+                }
             };
             {
                 const uint32_t xswap = (j & 1) ? 128u : 0u;  // odd tiles: the two 128-column halves of X are swapped
