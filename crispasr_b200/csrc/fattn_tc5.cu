@@ -643,7 +643,9 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
 // ------------------------------------------------------------------------------------------------------
 constexpr int kBncStride = 128;  // bytes per bounce row: a ring of 64 f16 values
 
-__global__ void __launch_bounds__(kThreadsTc5, 1)
+constexpr int kThreadsRelpos = 320;  // 8 softmax warps (two threads per query row), TMA warp, MMA warp
+
+__global__ void __launch_bounds__(kThreadsRelpos, 1)
 fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
                                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmR) {
     constexpr int HD = 128;
@@ -656,13 +658,15 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
     const uint32_t sQ = smem_base, sQv = sQ + TILE_BYTES, sK = sQv + TILE_BYTES, sV = sK + TILE_BYTES,
-                   sR = sV + TILE_BYTES, sBnc = sR + 2 * TILE_BYTES, sBar = sBnc + kTile * kBncStride;
+                   sR = sV + TILE_BYTES, sBnc = sR + 2 * TILE_BYTES, sBar = sBnc + 2 * kTile * kBncStride;
     const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8, bar_v_full = sBar + 16, bar_v_empty = sBar + 24,
                    bar_r_full = sBar + 32 /* [2] */, bar_r_empty = sBar + 48 /* [2] */, bar_s_full = sBar + 64,
-                   bar_x_full = sBar + 72, bar_x_free = sBar + 80, bar_p_ready = sBar + 88, bar_o_done = sBar + 96;
-    uint8_t* misc = smem_gen + 6 * TILE_BYTES + kTile * kBncStride + 104;
+                   bar_x_full = sBar + 72, bar_x_free = sBar + 80, bar_p_ready = sBar + 88, bar_o_done = sBar + 96,
+                   bar_pair = sBar + 104 /* [4]: the two warps that share 32 TMEM lanes */;
+    uint8_t* misc = smem_gen + 6 * TILE_BYTES + 2 * kTile * kBncStride + 136;
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
     volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
+    volatile float* s_xchg = reinterpret_cast<volatile float*>(misc + 8);   // [2][128]: row maximum exchange of a thread pair
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int q0 = blockIdx.x * kTile, h = blockIdx.y, b = blockIdx.z;
@@ -703,10 +707,10 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     };
 
     // ---- set-up ----
-    if (tid == 4 * 32) {
-        for (int i = 0; i < 13; i++) {
+    if (tid == 8 * 32) {
+        for (int i = 0; i < 17; i++) {
             const uint32_t bar = sBar + 8 * i;
-            mbar_init(bar, (bar == bar_x_free || bar == bar_p_ready) ? kTile : 1);
+            mbar_init(bar, (bar == bar_x_free || bar == bar_p_ready) ? 2 * kTile : (bar >= bar_pair ? 64 : 1));
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -718,19 +722,30 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         load_kv(0, false);
         load_kv(0, true);
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem_base))),
                      "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (warp < 4) {
-        const int r = tid;
+    if (warp < 8) {
+        // Q_u and Q_v tiles -> shared memory: thread (r, ch) converts and stores half of each row
+        const int r = tid & 127, ch = tid >> 7;
         const int iq = q0 + r;
-        load_q_row<HD>(smem_gen, r, a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.type,
-                       a.q.vec16 != 0, iq < a.Tq);
-        load_q_row<HD>(smem_gen + TILE_BYTES, r, a.qv.p + (int64_t)iq * a.qv.nb1 + (int64_t)h * a.qv.nb2 + (int64_t)b * a.qv.nb3,
-                       a.qv.type, a.qv.vec16 != 0, iq < a.Tq);
+#pragma unroll
+        for (int which = 0; which < 2; which++) {
+            const View& qv = which ? a.qv : a.q;
+            const uint8_t* rowp = qv.p + (int64_t)iq * qv.nb1 + (int64_t)h * qv.nb2 + (int64_t)b * qv.nb3;
+            uint4 v[HD / 16];
+#pragma unroll
+            for (int c = 0; c < HD / 16; c++)
+                v[c] = (iq < a.Tq) ? q_chunk(rowp, qv.type, (ch * (HD / 16) + c) * 8, qv.vec16 != 0) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int c = 0; c < HD / 16; c++) {
+                const int cc = ch * (HD / 16) + c;
+                *reinterpret_cast<uint4*>(smem_gen + which * TILE_BYTES + r * 128 + (cc >> 3) * kPanelBytes + (((cc & 7) ^ (r & 7)) << 4)) = v[c];
+            }
+        }
         fence_proxy_async();
     }
     tc_fence_before();
@@ -739,7 +754,7 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     const uint32_t tmem_base = *s_tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_P = tmem_base, tmem_O = tmem_base + 128, tmem_X = tmem_base + 256;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================= TMA producer =================
         if (lane == 0) {
             bool ok = true;
@@ -759,7 +774,7 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 for (uint32_t it = 0; it < 65536; ++it) __nanosleep(64);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ================= MMA issuer =================
         if (lane == 0) {
             // X[j] = Q_v . [ring slot 0 | ring slot 1]^T as ONE N=256 MMA per k-step (A is fetched once instead of
@@ -825,29 +840,42 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             }
         }
     } else {
-        // ================= softmax / bias / epilogue =================
-        const int r = tid;
+        // ================= softmax / bias / epilogue: thread (r, ch) owns columns [64ch, 64ch+64) of row r ========
+        // Eight softmax warps: warps w and w+4 see the same 32 TMEM lanes. The two threads of a row agree on the
+        // running maximum through shared memory and a 64-thread named barrier once per tile; each keeps a partial
+        // row sum and owns half of the O columns.
+        const int r = tid & 127, ch = tid >> 7;
         const int iq = q0 + r;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t my_pair_bar = bar_pair + 8 * (warp & 3);
+        uint32_t pair_phase = 0;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float bscale = a.relscale;   // == a.scale: the tcgen05 path is not taken with a softcap
-        const int shift = 31 - lane;                        // band offset of this row inside the warp's columns
-        // Bounce ring of this row: 64 f16 values (two 32-column chunks) = 32 words.
-        uint8_t* const bnc_gen = smem_gen + (sBnc - smem_base) + r * kBncStride;   // this thread's ring (generic pointer)
+        const int shift = 31 - lane;       // band offset of this row inside the warp's columns
+        // Bounce ring of this thread: 64 f16 values (two 32-column chunks) = 32 words.
+        uint8_t* const bnc_gen = smem_gen + (sBnc - smem_base) + tid * kBncStride;
         // rotation in words: 16-byte stores of the same logical chunk by the 8 lanes of a quarter-warp, and 4-byte
         // loads of logical word (const - lane/2) by all 32 lanes, both hit 32 distinct banks (found by enumeration)
         const uint32_t rot = 4u * ((lane + 3u * (lane >> 3)) & 7u);
-        const uint32_t x_col0 = 96 - 32 * warp;             // first X column any row of this warp can need
+        const uint32_t x_col0 = 96 - 32 * (warp & 3) + 64 * ch;   // first X column this thread's warp can need
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
+        // Publish a value, meet the partner warp at the pair barrier (bounded wait), read the partner's value.
+        // One slot per thread is enough: the partner's next write comes after its wait for the next S tile, which the
+        // tensor pipe only produces after the P*V product that needed this thread's later arrival on bar_p_ready.
+        auto exchange = [&](float mine) {
+            s_xchg[ch * 128 + r] = mine;
+            mbar_arrive(my_pair_bar);
+            ok = mbar_wait(my_pair_bar, pair_phase, s_abort);
+            pair_phase ^= 1;
+            return s_xchg[(ch ^ 1) * 128 + r];
+        };
         for (int j = 0; j < n_tiles; j++) {
-            // ---- phase A: the 128 bias values of this row, fp32 registers holding f16-rounded numbers ----
+            // ---- phase A: the 64 bias values of this half row, fp32 registers holding f16-rounded numbers ----
             ok = mbar_wait(bar_x_full, j & 1, s_abort);
             if (!ok) break;
             if (tid == 0) TC5_TRACE(0, j, 0);
             tc_fence_after();
-            // TMEM loads are slow while the tensor pipe is running (the accumulator traffic of the MMAs has priority),
-            // so they are issued in two deep batches per phase and overlapped with the arithmetic of the previous batch.
-            float u[4][32];
+            float u[2][32];
             auto bounce_chunk = [&](const uint32_t (&xr)[32], int k) {
                 // scale*x rounded to f16 (the reference's cast of its mask), 32 values = 16 words, into ring half k&1
                 uint32_t w[16];
@@ -858,8 +886,8 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 for (int i = 0; i < 16; i += 4)
                     *reinterpret_cast<uint4*>(bnc_gen + ((((k & 1) * 16 + i + rot) & 31) << 2)) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
             };
-            auto read_quarter = [&](int qq) {  // tile columns [32qq, 32qq+32): ring halves shift .. shift+31 of chunks qq, qq+1
-                const uint32_t h0 = (uint32_t)(qq * 32 + shift);  // first half-word (mod 64)
+            auto read_quarter = [&](int qq) {  // half-row columns [32qq, 32qq+32): ring halves shift .. shift+31 of chunks qq, qq+1
+                const uint32_t h0 = (uint32_t)(qq * 32 + shift);
                 const uint32_t fs = (h0 & 1u) * 16u;
                 uint32_t prev = *reinterpret_cast<const uint32_t*>(bnc_gen + ((((h0 >> 1) + rot) & 31) << 2));
 #pragma unroll
@@ -873,22 +901,15 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             };
             {
                 const uint32_t xswap = (j & 1) ? 128u : 0u;  // odd tiles: the two 128-column halves of X are swapped
-                uint32_t xa[3][32], xb[2][32];
+                uint32_t xa[3][32];
 #pragma unroll
                 for (int k = 0; k < 3; k++) tmem_ld32(tmem_X + lane_base + ((x_col0 + k * 32 + xswap) & 255u), xa[k]);
                 tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 2; k++) tmem_ld32(tmem_X + lane_base + ((x_col0 + (3 + k) * 32 + xswap) & 255u), xb[k]);
                 bounce_chunk(xa[0], 0);
                 bounce_chunk(xa[1], 1);
                 read_quarter(0);
                 bounce_chunk(xa[2], 2);
                 read_quarter(1);
-                tmem_wait_ld();
-                bounce_chunk(xb[0], 3);
-                read_quarter(2);
-                bounce_chunk(xb[1], 4);
-                read_quarter(3);
             }
             tc_fence_before();
             mbar_arrive(bar_x_free);
@@ -902,25 +923,28 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             const int n_valid = len_b - j * kTile;
             const bool full_tile = n_valid >= kTile;   // uniform over the CTA: only the last tile is partial
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int hh = 0; hh < 2; hh++) {
+            {
                 uint32_t sreg[2][32];
-                tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
-                tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                tmem_ld32(tmem_S + lane_base + ch * 64, sreg[0]);
+                tmem_ld32(tmem_S + lane_base + ch * 64 + 32, sreg[1]);
                 tmem_wait_ld();
 #pragma unroll
                 for (int q2 = 0; q2 < 2; q2++)
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
-                        float uv = fmaf(__uint_as_float(sreg[q2][i]), bscale, u[hh * 2 + q2][i]);
-                        if (!full_tile && hh * 64 + q2 * 32 + i >= n_valid) uv = -INFINITY;
-                        u[hh * 2 + q2][i] = uv;
+                        float uv = fmaf(__uint_as_float(sreg[q2][i]), bscale, u[q2][i]);
+                        if (!full_tile && ch * 64 + q2 * 32 + i >= n_valid) uv = -INFINITY;
+                        u[q2][i] = uv;
                         mx[i & 3] = fmaxf(mx[i & 3], uv);
                     }
             }
             if (tid == 0) TC5_TRACE(0, j, 3);
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * kLog2e;
-            // lazy rescale: O and l are only touched when a row outgrew its reference maximum by 2^8
+            const float mx_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // after this barrier both threads of the row have read their S columns: P stores may alias them
+            const float m_tile = fmaxf(mx_half, exchange(mx_half)) * kLog2e;
+            if (!ok) break;
+            // lazy rescale: O and l are only touched when a row outgrew its reference maximum by 2^8; both warps of a
+            // pair see the same row maxima and take the same branch
             const bool grow = m_tile > m_ref + kRescaleThreshold;  // also true for -inf -> finite
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = fmaxf(m_ref, m_tile);
@@ -928,13 +952,13 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 l_run *= alpha;
                 if (j > 0) {
 #pragma unroll
-                    for (int q4 = 0; q4 < HD / 32; q4++) {
+                    for (int q4 = 0; q4 < 2; q4++) {
                         uint32_t oreg[32];
-                        tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                        tmem_ld32(tmem_O + lane_base + ch * 64 + q4 * 32, oreg);
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-                        tmem_st32(tmem_O + lane_base + q4 * 32, oreg);
+                        tmem_st32(tmem_O + lane_base + ch * 64 + q4 * 32, oreg);
                     }
                 }
                 m_ref = m_new;
@@ -942,20 +966,17 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
             // P = exp2(u*log2(e) - m_ref) from registers; masked columns hold -inf and give 0
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t preg[32];
 #pragma unroll
-            for (int hh = 0; hh < 2; hh++) {
-                uint32_t preg[32];
+            for (int q2 = 0; q2 < 2; q2++)
 #pragma unroll
-                for (int q2 = 0; q2 < 2; q2++)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2(fmaf(u[hh * 2 + q2][i], kLog2e, -m_use));
-                        const float p1 = ex2(fmaf(u[hh * 2 + q2][i + 1], kLog2e, -m_use));
-                        ls[(i >> 1) & 3] += p0 + p1;
-                        preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
-                    }
-                tmem_st32(tmem_P + lane_base + hh * 32, preg);
-            }
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = ex2(fmaf(u[q2][i], kLog2e, -m_use));
+                    const float p1 = ex2(fmaf(u[q2][i + 1], kLog2e, -m_use));
+                    ls[(i >> 1) & 3] += p0 + p1;
+                    preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
+                }
+            tmem_st32(tmem_P + lane_base + ch * 32, preg);
             l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
             tmem_wait_st();
             tc_fence_before();
@@ -965,12 +986,13 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
         if (ok) {
             tc_fence_after();
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * HD;
+            const float l_tot = l_run + exchange(l_run);   // a failed wait has set the abort flag: the host reports it
+            const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+            float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * HD + ch * 64;
 #pragma unroll
-            for (int q4 = 0; q4 < HD / 32; q4++) {
+            for (int q4 = 0; q4 < 2; q4++) {
                 uint32_t oreg[32];
-                tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                tmem_ld32(tmem_O + lane_base + ch * 64 + q4 * 32, oreg);
                 tmem_wait_ld();
                 if (iq < a.Tq) {
 #pragma unroll
@@ -985,7 +1007,7 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
@@ -1044,13 +1066,13 @@ int launch_relpos(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errl
         snprintf(errbuf, errlen, "cuTensorMapEncodeTiled failed for K/V/R");
         return B200_E_CUDA;
     }
-    const size_t smem = 1024 + (size_t)6 * 2 * kPanelBytes + (size_t)kTile * kBncStride + 104 + 16;
+    const size_t smem = 1024 + (size_t)6 * 2 * kPanelBytes + (size_t)2 * kTile * kBncStride + 136 + 8 + 2 * 128 * sizeof(float) + 16;
     auto kern = fattn_prefill_tc5_relpos_kernel;
     static bool smem_set[64] = {false};
     cudaError_t e = set_smem_once(kern, smem, smem_set);
     if (e == cudaSuccess) {
         dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
-        kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV, tmR);
+        kern<<<grid, kThreadsRelpos, smem, st>>>(a, tmK, tmV, tmR);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) {
