@@ -104,6 +104,21 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
     return d;
 }
 
+// The two 32-bit words of a descriptor.  Only the low word carries the address (bits 0-13, in 16-byte units),
+// so stepping through an operand is one 32-bit add: the issuing thread's instruction latency, not the tensor
+// pipe, bounds how fast small MMAs can be issued.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor for kind::f16: F16 A/B, F32 accumulate, M = 128.
 __host__ __device__ constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
@@ -158,6 +173,36 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Packed fp32 pairs (one issue slot for two lanes of work on sm_100) and the three-input maximum.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // Eight Q elements [c0, c0+8) of one row as packed f16 (F32 rows are rounded to nearest even).
 __device__ __forceinline__ uint4 q_chunk(const uint8_t* rowp, int type, int c0, bool vec16) {
     uint4 out;
@@ -194,11 +239,12 @@ __device__ __forceinline__ float row_max64(const uint32_t (&sreg)[2][32], int co
 #pragma unroll
     for (int q2 = 0; q2 < 2; q2++)
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-            const float sv = (col0 + q2 * 32 + i < n_valid) ? __uint_as_float(sreg[q2][i]) : -INFINITY;
-            mx[i & 3] = fmaxf(mx[i & 3], sv);
+        for (int i = 0; i < 32; i += 2) {
+            const float s0 = (col0 + q2 * 32 + i < n_valid) ? __uint_as_float(sreg[q2][i]) : -INFINITY;
+            const float s1 = (col0 + q2 * 32 + i + 1 < n_valid) ? __uint_as_float(sreg[q2][i + 1]) : -INFINITY;
+            mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], s0, s1);
         }
-    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    return max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]);
 }
 
 // 64 score columns -> 32 packed f16x2 probabilities exp2(s*c - m); updates the running raw maximum and the
@@ -206,8 +252,10 @@ __device__ __forceinline__ float row_max64(const uint32_t (&sreg)[2][32], int co
 template <bool MASKED>
 __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_t (&preg)[32], float c, float m_use,
                                           int col0, int n_valid, float& mx_io, float& lsum_io) {
+    // Per pair of columns: one three-input max, one packed FMA, two MUFU, one packed add, one f16x2 convert.
     float mx[8];
-    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+    uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};   // four packed pairs of fp32 partial sums
+    const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_use, -m_use);
 #pragma unroll
     for (int i = 0; i < 8; i++) mx[i] = -INFINITY;
 #pragma unroll
@@ -219,14 +267,17 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
                 if (col0 + q2 * 32 + i >= n_valid) s0 = -INFINITY;
                 if (col0 + q2 * 32 + i + 1 >= n_valid) s1 = -INFINITY;
             }
-            mx[(i >> 1) & 7] = fmaxf(mx[(i >> 1) & 7], fmaxf(s0, s1));
-            const float p0 = ex2(fmaf(s0, c, -m_use));
-            const float p1 = ex2(fmaf(s1, c, -m_use));
-            ls[(i >> 1) & 3] += p0 + p1;
+            mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], s0, s1);
+            float t0, t1;
+            unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
+            const float p0 = ex2(t0), p1 = ex2(t1);
+            ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
             preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
         }
-    mx_io = fmaxf(mx_io, fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))));
-    lsum_io += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+    mx_io = max3(mx_io, max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]), max3(fmaxf(mx[4], mx[5]), mx[6], mx[7]));
+    float l0, l1;
+    unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
+    lsum_io += l0 + l1;
 }
 
 // Explicit F16 mask: turns 64 raw scores into log2-domain logits t = s*c + mask*log2(e) in place (mask -inf stays
@@ -357,7 +408,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             mbar_init(bar_v_empty + 8 * i, 1);
         }
         mbar_init(bar_s_full, 1);
-        mbar_init(bar_p_ready, kTile);
+        mbar_init(bar_p_ready, 4);   // one arrival per softmax warp
         mbar_init(bar_o_done, 1);
         mbar_init(bar_pv_done, 1);
         *s_abort = 0;
@@ -442,6 +493,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         // as the tensor pipe allows.  S[j+1] overwrites the columns P[j] lives in; tcgen05.mma executes in
         // issue order, so PV[j] has consumed P[j] before S[j+1] writes.
         if (lane == 0) {
+            const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, kPanelBytes);
+            constexpr uint32_t desc_hi = smem_desc_hi(1024);
             bool ok = mbar_wait(bar_k_full, 0, s_abort);
             if (ok) {
                 TC5_TRACE(1, 0, 0);
@@ -467,25 +520,34 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 if (!ok) break;
                 TC5_TRACE(1, j, 3);
                 tc_fence_after();
+                // Descriptors differ only in the low word (address in 16-byte units): one add per MMA.  The issuing
+                // thread's latency, about 50 clocks per MMA and 100 per commit, is what the softmax threads wait for.
                 auto issue_next_s = [&]() {
+                    const uint32_t kd = k_lo + nslot * (TILE_BYTES >> 4);
 #pragma unroll
                     for (int ks = 0; ks < HD / 16; ks++) {
-                        const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-                        mma_ss(tmem_S, smem_desc(sQ + off, 16, 1024), smem_desc(sK + nslot * TILE_BYTES + off, 16, 1024),
-                               IDESC_S, ks > 0 ? 1u : 0u);
+                        const uint32_t off16 = (uint32_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
+                        mma_ss(tmem_S, desc64(q_lo + off16, desc_hi), desc64(kd + off16, desc_hi), IDESC_S, ks > 0 ? 1u : 0u);
                     }
                     tc_commit(bar_s_full);
-                    tc_commit(bar_k_empty + 8 * nslot);
                 };
                 // with P in its own columns the next S goes first: the softmax threads wake after 4 MMAs, not 12
                 if (SEP_P && more) issue_next_s();
+                const uint32_t vd = v_lo + slot * (TILE_BYTES >> 4);
+                mma_ts(tmem_O, tmem_P, desc64(vd, desc_hi), IDESC_PV, j > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < kTile / 16; ks++)
-                    mma_ts(tmem_O, tmem_P + ks * 8, smem_desc(sV + slot * TILE_BYTES + ks * 2048, kPanelBytes, 1024),
-                           IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit(bar_v_empty + 8 * slot);
-                if (SEP_P) tc_commit(bar_pv_done);
-                if (!SEP_P && more) issue_next_s();
+                for (int ks = 1; ks < kTile / 16; ks++) mma_ts(tmem_O, tmem_P + ks * 8, desc64(vd + ks * (2048 >> 4), desc_hi), IDESC_PV, 1u);
+                if (SEP_P) {
+                    if (more) tc_commit(bar_k_empty + 8 * nslot);   // after the P.V MMAs: off the softmax threads' critical path
+                    tc_commit(bar_v_empty + 8 * slot);
+                    tc_commit(bar_pv_done);
+                } else {
+                    tc_commit(bar_v_empty + 8 * slot);
+                    if (more) {
+                        issue_next_s();
+                        tc_commit(bar_k_empty + 8 * nslot);
+                    }
+                }
                 if (!more) tc_commit(bar_o_done);
                 TC5_TRACE(1, j, 4);
             }
@@ -591,7 +653,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             tmem_st32(tmem_P + lane_base + 32, preg[1]);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar_p_ready);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_ready);
             if (tid == 0) TC5_TRACE(0, j, 2);
         }
         if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
@@ -710,7 +773,7 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
     if (tid == 8 * 32) {
         for (int i = 0; i < 17; i++) {
             const uint32_t bar = sBar + 8 * i;
-            mbar_init(bar, (bar == bar_x_free || bar == bar_p_ready) ? 2 * kTile : (bar >= bar_pair ? 64 : 1));
+            mbar_init(bar, (bar == bar_x_free || bar == bar_p_ready) ? 8 : (bar >= bar_pair ? 64 : 1));   // 8 = one arrival per softmax warp
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -850,6 +913,7 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         uint32_t pair_phase = 0;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float bscale = a.relscale;   // == a.scale: the tcgen05 path is not taken with a softcap
+        const uint64_t bscale2 = pack2(bscale, bscale);
         const int shift = 31 - lane;       // band offset of this row inside the warp's columns
         // Bounce ring of this thread: 64 f16 values (two 32-column chunks) = 32 words.
         uint8_t* const bnc_gen = smem_gen + (sBnc - smem_base) + tid * kBncStride;
@@ -880,8 +944,11 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 // scale*x rounded to f16 (the reference's cast of its mask), 32 values = 16 words, into ring half k&1
                 uint32_t w[16];
 #pragma unroll
-                for (int i = 0; i < 16; i++)
-                    w[i] = cvt_f16x2(__uint_as_float(xr[2 * i]) * bscale, __uint_as_float(xr[2 * i + 1]) * bscale);
+                for (int i = 0; i < 16; i++) {
+                    float x0, x1;
+                    unpack2(mul2(pack2(__uint_as_float(xr[2 * i]), __uint_as_float(xr[2 * i + 1])), bscale2), x0, x1);
+                    w[i] = cvt_f16x2(x0, x1);
+                }
 #pragma unroll
                 for (int i = 0; i < 16; i += 4)
                     *reinterpret_cast<uint4*>(bnc_gen + ((((k & 1) * 16 + i + rot) & 31) << 2)) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
@@ -912,7 +979,8 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 read_quarter(1);
             }
             tc_fence_before();
-            mbar_arrive(bar_x_free);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_x_free);
             if (tid == 0) TC5_TRACE(0, j, 1);
 
             // ---- phase B: u = S*scale + bias (natural units), row maximum ----
@@ -931,11 +999,16 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
 #pragma unroll
                 for (int q2 = 0; q2 < 2; q2++)
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        float uv = fmaf(__uint_as_float(sreg[q2][i]), bscale, u[q2][i]);
-                        if (!full_tile && ch * 64 + q2 * 32 + i >= n_valid) uv = -INFINITY;
-                        u[q2][i] = uv;
-                        mx[i & 3] = fmaxf(mx[i & 3], uv);
+                    for (int i = 0; i < 32; i += 2) {
+                        float u0, u1;
+                        unpack2(fma2(pack2(__uint_as_float(sreg[q2][i]), __uint_as_float(sreg[q2][i + 1])), bscale2,
+                                     pack2(u[q2][i], u[q2][i + 1])), u0, u1);
+                        if (!full_tile) {
+                            if (ch * 64 + q2 * 32 + i >= n_valid) u0 = -INFINITY;
+                            if (ch * 64 + q2 * 32 + i + 1 >= n_valid) u1 = -INFINITY;
+                        }
+                        u[q2][i] = u0, u[q2][i + 1] = u1;
+                        mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], u0, u1);
                     }
             }
             if (tid == 0) TC5_TRACE(0, j, 3);
@@ -965,22 +1038,29 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             }
             const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
             // P = exp2(u*log2(e) - m_ref) from registers; masked columns hold -inf and give 0
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};
+            const uint64_t l2e2 = pack2(kLog2e, kLog2e), nm2 = pack2(-m_use, -m_use);
             uint32_t preg[32];
 #pragma unroll
             for (int q2 = 0; q2 < 2; q2++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(fmaf(u[q2][i], kLog2e, -m_use));
-                    const float p1 = ex2(fmaf(u[q2][i + 1], kLog2e, -m_use));
-                    ls[(i >> 1) & 3] += p0 + p1;
+                    float t0, t1;
+                    unpack2(fma2(pack2(u[q2][i], u[q2][i + 1]), l2e2, nm2), t0, t1);
+                    const float p0 = ex2(t0), p1 = ex2(t1);
+                    ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
                     preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
                 }
             tmem_st32(tmem_P + lane_base + ch * 32, preg);
-            l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            {
+                float l0, l1;
+                unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
+                l_run += l0 + l1;
+            }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar_p_ready);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_ready);
             if (tid == 0) TC5_TRACE(0, j, 4);
         }
         if (ok) ok = mbar_wait(bar_o_done, 0, s_abort);
