@@ -444,7 +444,33 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     const size_t kvlen_off = (ext && ext->kv_len) ? bump((size_t)q->ne[3] * 4) : 0;
     const size_t dst_bytes = (size_t)dst->ne[0] * dst->ne[1] * dst->ne[2] * dst->ne[3] * 4;
     const size_t dst_off = bump(dst_bytes);
-    const size_t ws_off = bump(2 * ((plan.ws_bytes + 255) / 256 * 256));  // one per stream in flight
+
+    // Batch entries are independent, so the call is pipelined over chunks of the batch dimension on two
+    // streams: the H2D copy of chunk i+1 overlaps the kernel and the D2H copy of chunk i (separate copy
+    // engines).  Chunking needs the batch dimension outermost in every batched operand; otherwise one chunk.
+    const int64_t B = q->ne[3];
+    auto batch_outermost = [](const b200_tensor* t) {
+        b200_tensor one = *t;
+        one.ne[3] = 1;
+        return t->ne[3] == 1 || t->nb[3] >= span_bytes(&one);
+    };
+    bool chunkable = B >= 2 && k->ne[3] == B;
+    for (int i = 0; i < 6 && chunkable; i++)
+        if (in[i] && in[i]->ne[3] != 1 && (in[i]->ne[3] != B || !batch_outermost(in[i]))) chunkable = false;
+    const int n_chunks = chunkable ? (int)(B < 4 ? B : 4) : 1;
+    // Workspace of one chunk: a smaller batch may be split over more KV ranges than the whole call would be,
+    // so the split-decode workspace is sized for the chunk batches, not taken from the full plan.
+    size_t ws_need = plan.ws_bytes;
+    if (plan.kernel == B200_KERNEL_DECODE_SPLIT) {
+        for (int c = 0; c < n_chunks; c++) {
+            const int nb = (int)(B * (c + 1) / n_chunks - B * c / n_chunks);
+            const int ns = decode_split_choose(nb, plan.args.Hkv, plan.args.Lk, di.sm_count);
+            const size_t w = decode_split_ws_bytes(nb, plan.args.Hkv, ns, plan.args.hd);
+            if (w > ws_need) ws_need = w;
+        }
+    }
+    const size_t ws_each = (ws_need + 255) / 256 * 256;
+    const size_t ws_off = bump(2 * ws_each);  // one per stream in flight
 
     Arena& ar = g_arena;
     cudaError_t e;
@@ -463,20 +489,6 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     if (!ar.stream2 && (e = cudaStreamCreateWithFlags(&ar.stream2, cudaStreamNonBlocking)) != cudaSuccess)
         return cuda_fail(e, "cudaStreamCreate");
 
-    // Batch entries are independent, so the call is pipelined over chunks of the batch dimension on two
-    // streams: the H2D copy of chunk i+1 overlaps the kernel and the D2H copy of chunk i (separate copy
-    // engines).  Chunking needs the batch dimension outermost in every batched operand; otherwise one chunk.
-    const int64_t B = q->ne[3];
-    auto batch_outermost = [](const b200_tensor* t) {
-        b200_tensor one = *t;
-        one.ne[3] = 1;
-        return t->ne[3] == 1 || t->nb[3] >= span_bytes(&one);
-    };
-    bool chunkable = B >= 2 && k->ne[3] == B;
-    for (int i = 0; i < 6 && chunkable; i++)
-        if (in[i] && in[i]->ne[3] != 1 && (in[i]->ne[3] != B || !batch_outermost(in[i]))) chunkable = false;
-    const int n_chunks = chunkable ? (int)(B < 4 ? B : 4) : 1;
-    const size_t ws_each = (plan.ws_bytes + 255) / 256 * 256;  // chunk plans never need more than the full plan
     cudaStream_t streams[2] = {ar.stream, ar.stream2};
 
     // operands without a batch dimension (ne[3] == 1) are copied once, ahead of everything, on stream 0

@@ -328,12 +328,14 @@ int launch_tile_t(const FattnArgs& a, cudaStream_t st) {
 // ------------------------------------------------------------------------------------------
 constexpr int kDecRows = 16;
 constexpr int kDecBN = 64;
+constexpr int kDecQ8Stages = 2;   // raw Q8_0 tile stages per warp; small footprint: four CTAs per SM hide the latency
 
 // How a decode CTA brings K/V tiles into shared memory.
 enum DecodeMode {
     kDecSync = 0,    // element loads + conversion (F32 K/V, unaligned or gapped layouts)
     kDecAsyncF16 = 1,  // cp.async 16-byte copies of F16 rows into a multi-stage ring
-    kDecAsyncQ8 = 2    // cp.async of the raw Q8_0 byte range of a tile, then a shared-to-shared dequantise
+    kDecAsyncQ8 = 2,   // bulk copy of the raw Q8_0 byte range of a tile, then a shared-to-shared dequantise (head_dim 32)
+    kDecRegQ8 = 3      // bulk copy of the raw Q8_0 bytes, dequantised in registers (head_dim 64 / 128)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -360,30 +362,64 @@ __device__ __forceinline__ void issue_tile_f16(__half* sm, const uint8_t* base, 
     }
 }
 
-// cp.async copy of the contiguous raw byte range of Q8_0 rows [row0, row0+64): 64 * (HD/32*34) bytes.
+// ---- bulk copies (one instruction per contiguous range) with a per-warp mbarrier per stage ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: a copy that never lands ends the wait after about a second; the tile is then multiplied as it is.
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        if (mbar_try_wait(bar, parity)) return;
+        if (it > 64) __nanosleep(64);
+    }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Raw bytes of this warp's 16 Q8_0 rows [row0 + 16*warp, +16) of a 64-row K tile and V tile: two contiguous,
+// 16-byte aligned ranges of at most 16 * (HD/32*34) bytes, one bulk copy each, issued by lane 0.  Only the bytes of
+// rows below row_hi are requested (rounded up to 16: the same footprint as 16-byte chunk copies; the rest of the
+// stage keeps old bytes, which the dequantiser replaces by zeros).  Each warp copies, dequantises and multiplies
+// only its own keys.
 template <int HD>
-__device__ __forceinline__ void issue_tile_q8raw(uint8_t* sm, const uint8_t* base, int row0, int row_hi, int tid) {
+__device__ __forceinline__ void issue_tile_q8raw(uint8_t* smK, uint8_t* smV, const uint8_t* kbase, const uint8_t* vbase, int row0,
+                                                 int row_hi, int warp, uint32_t bar) {
     constexpr int RB = HD / 32 * 34;
-    constexpr int CHUNKS = kDecBN * RB / 16;
-    const int64_t byte0 = (int64_t)row0 * RB;
-    const int64_t byte_hi = (int64_t)row_hi * RB;  // bytes at or beyond this belong to rows that are not read
-    for (int idx = tid; idx < CHUNKS; idx += kThreads) {
-        const int64_t off = byte0 + (int64_t)idx * 16;
-        const bool valid = off < byte_hi;  // a chunk straddling row_hi is still inside the allocation (rows < Lk)
-        cp_async16(smem_u32(sm) + idx * 16, base + (valid ? off : 0), valid);
+    const int r0 = row0 + 16 * warp;
+    const int n = min(16, max(0, row_hi - r0));
+    const uint32_t bytes = (uint32_t)((n * RB + 15) / 16 * 16);
+    mbar_expect_tx(bar, 2 * bytes);
+    if (bytes) {
+        bulk_g2s(smem_u32(smK) + 16 * warp * RB, kbase + (int64_t)r0 * RB, bytes, bar);
+        bulk_g2s(smem_u32(smV) + 16 * warp * RB, vbase + (int64_t)r0 * RB, bytes, bar);
     }
 }
 
 // Raw Q8_0 tile (64 rows of HD/32 blocks) in shared memory -> swizzled fp16 tile. x = fp16(d * q): the product of
 // an 11-bit and a 7-bit significand is exact before the single rounding, i.e. equal to fp32(d)*q rounded to fp16.
 template <int HD>
-__device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, int rows_valid, int tid) {
+__device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, int rows_valid, int warp, int lane) {
     constexpr int NBLK = HD / 32, RB = NBLK * 34;
+    // this warp's 16 rows x NBLK blocks, one block per lane and step
 #pragma unroll
-    for (int idx0 = 0; idx0 < kDecBN * NBLK; idx0 += kThreads) {
-        const int idx = idx0 + tid;
-        if (kDecBN * NBLK % kThreads != 0 && idx >= kDecBN * NBLK) break;
-        const int row = idx / NBLK, blk = idx % NBLK;
+    for (int idx0 = 0; idx0 < 16 * NBLK; idx0 += 32) {
+        const int idx = idx0 + lane;
+        const int row = 16 * warp + idx / NBLK, blk = idx % NBLK;
         const uint16_t* src = reinterpret_cast<const uint16_t*>(raw + row * RB + blk * 34);
         if (row >= rows_valid) {  // rows past the valid length read as zeros whatever the copy brought in
 #pragma unroll
@@ -424,16 +460,17 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
 }
 
 template <int HD, int MODE>
-__global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const FattnArgs a) {
+__global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
     constexpr int RAW_BYTES = kDecBN * (HD / 32 * 34);    // one raw Q8_0 K or V tile
-    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 2);
+    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : kDecQ8Stages);
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);              // [16][HD]
     // fp16 tiles: NS stages (async F16) or one pair (sync, Q8)
     __half* sKV = sQ + kDecRows * HD;
     constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
-    uint8_t* sRaw = reinterpret_cast<uint8_t*>(sKV + F16_STAGES * 2 * TILE_HALVES);  // Q8: NS stages of raw K|V
+    constexpr int F16_TILES = MODE == kDecAsyncQ8 ? 1 : F16_STAGES * 2;   // Q8: K and V take turns in one fp16 tile
+    uint8_t* sRaw = reinterpret_cast<uint8_t*>(sKV + F16_TILES * TILE_HALVES);  // Q8: NS stages of raw K|V
     float* sO = reinterpret_cast<float*>(sKV);                      // [16][HD] fp32, reused after the key loop
     __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
 
@@ -452,16 +489,29 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
     const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
     const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
 
+    __shared__ __align__(8) uint64_t s_q8bar[4][kDecQ8Stages];   // Q8_0: one barrier per (warp, raw stage)
+    if (MODE == kDecAsyncQ8) {
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < kDecQ8Stages; i++) mbar_init(smem_u32(&s_q8bar[warp][i]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+    }
     auto issue = [&](int tile) {
+        if (MODE == kDecAsyncQ8) {
+            if (tile < tile_hi && lane == 0) {
+                const int stage = (tile - tile_lo) % NS;
+                issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES, sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, kbase, vbase,
+                                     tile * kDecBN, len_b, warp, smem_u32(&s_q8bar[warp][stage]));
+            }
+            return;
+        }
         if (tile < tile_hi) {
             const int stage = (tile - tile_lo) % NS;
-            if (MODE == kDecAsyncF16) {
-                issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid);
-                issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid);
-            } else if (MODE == kDecAsyncQ8) {
-                issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES, kbase, tile * kDecBN, len_b, tid);
-                issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, vbase, tile * kDecBN, len_b, tid);
-            }
+            issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid);
+            issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid);
         }
         cp_async_commit();
     };
@@ -523,14 +573,15 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
             const int stage = (tile - tile_lo) % NS;
             sK = sKV + stage * 2 * TILE_HALVES, sV = sK + TILE_HALVES;
         } else {
-            cp_async_wait<NS - 2>();
-            __syncthreads();             // raw tile landed; everybody is done with the previous fp16 tiles
+            // Warp-local pipeline: a warp only ever touches its own 16 keys of a tile (raw bytes, fp16 rows, MMA
+            // operands), so the key loop needs no CTA-wide barrier and the four warps drift apart freely - one
+            // waits for its copy while another dequantises or multiplies.
             const int stage = (tile - tile_lo) % NS;
-            dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES, sKV, len_b - k0, tid);
-            dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, sKV + TILE_HALVES, len_b - k0, tid);
-            __syncthreads();
-            issue(tile + NS - 1);        // overwrites the raw stage of tile-1, which was dequantised an iteration ago
-            sK = sKV, sV = sKV + TILE_HALVES;
+            mbar_wait_bounded(smem_u32(&s_q8bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u);
+            __syncwarp();                // this warp's raw rows landed; its previous fp16 rows have been consumed
+            dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES, sKV, len_b - k0, warp, lane);
+            __syncwarp();
+            sK = sKV, sV = sKV;          // V is dequantised into the same rows once the scores are in registers
         }
 
         // this warp's 16 keys: k0 + 16*warp ..
@@ -542,7 +593,26 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
             mma16816(s[0], qf[ks], bf[0], bf[1]);
             mma16816(s[1], qf[ks], bf[2], bf[3]);
         }
+        if (MODE == kDecAsyncQ8) {
+            __syncwarp();                // every lane has read its K fragments
+            const int stage = (tile - tile_lo) % NS;
+            dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, sKV, len_b - k0, warp, lane);
+            __syncwarp();
+            issue(tile + NS - 1);        // overwrites the raw stage of tile-1, which this warp dequantised an iteration ago
+        }
         float rmax[2] = {ninf, ninf};
+        // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
+        const bool plain_tile = !a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1);
+        if (plain_tile) {
+            const float c = a.scale * kLog2e;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    s[nt][e] *= c;
+                    rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+                }
+        } else
 #pragma unroll
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
@@ -580,18 +650,20 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
         pf[1] = pack_half2(s[0][2], s[0][3]);
         pf[2] = pack_half2(s[1][0], s[1][1]);
         pf[3] = pack_half2(s[1][2], s[1][3]);
+        // the running maxima settle after a few tiles: the accumulator is only rescaled when some row of the warp moved
+        if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < HD / 8; i++) o[i][0] *= alpha[0], o[i][1] *= alpha[0], o[i][2] *= alpha[1], o[i][3] *= alpha[1];
+        }
 #pragma unroll
         for (int np = 0; np < HD / 16; np++) {
-            o[2 * np][0] *= alpha[0], o[2 * np][1] *= alpha[0], o[2 * np][2] *= alpha[1], o[2 * np][3] *= alpha[1];
-            o[2 * np + 1][0] *= alpha[0], o[2 * np + 1][1] *= alpha[0], o[2 * np + 1][2] *= alpha[1],
-                o[2 * np + 1][3] *= alpha[1];
             uint32_t bf[4];
             ldsm_x4_t(bf, tile_addr<HD>(sV, warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
             mma16816(o[2 * np], pf, bf[0], bf[1]);
             mma16816(o[2 * np + 1], pf, bf[2], bf[3]);
         }
     }
-    if (MODE != kDecSync) cp_async_wait<0>();
+    if (MODE == kDecAsyncF16) cp_async_wait<0>();
 
     // ---- merge the four warps' (m, l, O) in shared memory ----
     __syncthreads();  // all warps are done with the K/V tiles
@@ -630,6 +702,303 @@ __global__ void __launch_bounds__(kThreads) fattn_decode_split_kernel(const Fatt
         for (int idx = tid; idx < R * HD; idx += kThreads) {
             const int rr = idx / HD, c = idx % HD;
             if (c >= a.hd) continue;
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            const float L = s_L[rr];
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? sO[idx] / L : 0.0f;
+        }
+    } else {
+        const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
+        float* wo = a.ws_o + unit * kDecRows * HD;
+        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = sO[idx];
+        if (tid < kDecRows) {
+            a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
+            a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Split-KV decode over a Q8_0 cache, dequantised in registers
+// ------------------------------------------------------------------------------------------
+// The raw 34-byte blocks go from HBM to shared memory by bulk copies and from there straight into MMA operand
+// registers: no fp16 staging tile (16 KB of the 25 KB of shared-memory traffic per warp and tile of the staged
+// form, which kept the shared-memory pipe 70 % busy), no barrier of any kind inside the key loop.
+// A thread's operand bytes are made contiguous by permuting the contraction index inside each 32-element block,
+// which is free as long as both operands of a product use the same order:
+//   Q.K^T (contraction over dims): per block, k-step A takes dims {4t..4t+3}, k-step B dims {16+4t..16+4t+3}
+//     of thread t -> one 32-bit word of quants per k-step and key; Q fragments are read in the same order.
+//   P.V (output dims): n-tile j of a block holds dims {4g + j}, so the four bytes at dims 4g..4g+3 of one key are
+//     thread g's column values for the block's four n-tiles; the epilogue undoes the mapping.
+// int8 -> f16: byte b -> half 0x6400 | (b ^ 0x80) = 1024 + (q + 128); minus 1152 is q exactly; times d rounds once:
+// fp16(d*q), bit-identical to the staged dequantiser and to the reference's dequantise-then-cast.
+constexpr int kDecRegStages = 3;
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const FattnArgs a) {
+    constexpr int NBLK = HD / 32, RB = NBLK * 34;
+    constexpr int RAW_BYTES = kDecBN * RB;   // one raw K or V tile
+    constexpr int NS = kDecRegStages;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __half* sQ = reinterpret_cast<__half*>(smem_raw);                                  // [16][HD], 16-byte chunks swizzled
+    uint8_t* sRaw = smem_raw + kDecRows * HD * sizeof(__half);                          // NS stages of raw K | V
+    float* sO = reinterpret_cast<float*>(sRaw);                                         // [16][HD] fp32, reused after the key loop
+    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
+    __shared__ __align__(8) uint64_t s_bar[4][NS];                                      // one barrier per (warp, stage)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int bk = b / a.bq;
+    const int R = a.Tq * a.gqa;  // <= 16; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
+    const float ninf = -INFINITY;
+
+    const int len_b = clamp_len(a, b);
+    int kmax = len_b;
+    if (a.causal) kmax = min(kmax, a.n_past + a.Tq);
+    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
+    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
+    const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
+    const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NS; i++) mbar_init(smem_u32(&s_bar[warp][i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    auto issue = [&](int tile) {
+        if (tile < tile_hi && lane == 0) {
+            const int stage = (tile - tile_lo) % NS;
+            issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES, sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, kbase, vbase, tile * kDecBN,
+                                 len_b, warp, smem_u32(&s_bar[warp][stage]));
+        }
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < NS; s0++) issue(tile_lo + s0);
+
+    // Q rows (tiny): one 8-element chunk per loop step
+    for (int idx = tid; idx < kDecRows * (HD / 8); idx += kThreads) {
+        const int rr = idx / (HD / 8), ch = idx % (HD / 8);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < R) {
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
+                                a.q.type, ch * 8, a.hd, a.q.vec16);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, ch)) * 16) = val;
+    }
+    __syncthreads();
+    // Q fragments in the permuted contraction order: k-step A of block blk uses dims 32blk + {4t..4t+3},
+    // k-step B dims 32blk + 16 + {4t..4t+3}; rows g and g+8.  qf[blk][ks] = {a0, a1, a2, a3}.
+    uint32_t qf[NBLK][2][4];
+#pragma unroll
+    for (int blk = 0; blk < NBLK; blk++)
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            const int ch = 4 * blk + 2 * ks + (t >> 1);   // 16-byte chunk holding dims 32blk + 16ks + 4t .. +3
+#pragma unroll
+            for (int rI = 0; rI < 2; rI++) {
+                const int rr = g + 8 * rI;
+                const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(sQ) +
+                                                                 (rr * (HD / 8) + swz<HD>(rr, ch)) * 16 + (t & 1) * 8);
+                qf[blk][ks][rI] = w.x, qf[blk][ks][2 + rI] = w.y;
+            }
+        }
+
+    // per-thread row metadata for rows g and g+8
+    int row_iq[2];
+    float row_slope[2];
+    const uint8_t* row_mask[2];
+#pragma unroll
+    for (int rI = 0; rI < 2; rI++) {
+        const int rr = g + rI * 8;
+        row_iq[rI] = rr / a.gqa;
+        const int hq = hk * a.gqa + rr % a.gqa;
+        row_slope[rI] = alibi_slope(a, hq);
+        row_mask[rI] = (a.has_mask && rr < R)
+                           ? a.mask.p + (int64_t)row_iq[rI] * a.mask.nb1 + (int64_t)(hq % a.mask_ne2) * a.mask.nb2 +
+                                 (int64_t)(b % a.mask_ne3) * a.mask.nb3
+                           : nullptr;
+    }
+
+    float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];   // n-tile 4*blk + j, column n <-> dim 32blk + 4n + j
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const __half2 bias = __float2half2_rn(1152.0f);
+    auto cvt2 = [&](uint32_t packed, __half2 d2) {   // {0x64 q1' 0x64 q0'} -> {d*q0, d*q1}
+        const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&packed), bias), d2);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    };
+
+    for (int tile = tile_lo; tile < tile_hi; tile++) {
+        const int k0 = tile * kDecBN;
+        const int stage = (tile - tile_lo) % NS;
+        mbar_wait_bounded(smem_u32(&s_bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u);
+        const uint8_t* rawK = sRaw + stage * 2 * RAW_BYTES + 16 * warp * RB;   // this warp's 16 keys
+        const uint8_t* rawV = rawK + RAW_BYTES;
+        const int rows_valid = len_b - (k0 + 16 * warp);   // keys at or beyond it hold stale bytes: their scale reads as 0
+        const bool all_live = rows_valid >= 16;            // warp-uniform: the common case needs no per-key test
+
+        // ---- S = Q.K^T for this warp's 16 keys ----
+        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            const int key = nt * 8 + g;
+            const uint8_t* rowp = rawK + key * RB;
+            const bool live = all_live || key < rows_valid;
+#pragma unroll
+            for (int blk = 0; blk < NBLK; blk++) {
+                const uint8_t* bp = rowp + blk * 34;
+                const uint16_t dbits = live ? *reinterpret_cast<const uint16_t*>(bp) : (uint16_t)0;
+                const __half2 d2 = __half2half2(__ushort_as_half(dbits));
+                // quants at bp + 2: words at byte offsets 4t and 16 + 4t of the block's 32 quants; block starts are
+                // 2 mod 4 for even blk (rows are multiples of 4 bytes), so those words are read as two halves there
+                uint32_t wA, wB;
+                if (blk & 1) {
+                    wA = *reinterpret_cast<const uint32_t*>(bp + 2 + 4 * t);
+                    wB = *reinterpret_cast<const uint32_t*>(bp + 2 + 16 + 4 * t);
+                } else {
+                    const uint16_t* hp = reinterpret_cast<const uint16_t*>(bp + 2 + 4 * t);
+                    wA = hp[0] | ((uint32_t)hp[1] << 16);
+                    wB = hp[8] | ((uint32_t)hp[9] << 16);
+                }
+                wA ^= 0x80808080u, wB ^= 0x80808080u;
+                mma16816(s[nt], qf[blk][0], cvt2(__byte_perm(wA, 0x64646464u, 0x5140), d2), cvt2(__byte_perm(wA, 0x64646464u, 0x7362), d2));
+                mma16816(s[nt], qf[blk][1], cvt2(__byte_perm(wB, 0x64646464u, 0x5140), d2), cvt2(__byte_perm(wB, 0x64646464u, 0x7362), d2));
+            }
+        }
+
+        float rmax[2] = {ninf, ninf};
+        // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
+        const bool plain_tile = !a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1);
+        if (plain_tile) {
+            const float c = a.scale * kLog2e;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    s[nt][e] *= c;
+                    rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int rI = e >> 1;
+                    const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
+                    float val = s[nt][e] * a.scale;
+                    if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
+                    const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + row_iq[rI]);
+                    if (row_mask[rI] && valid)
+                        val += row_slope[rI] * __half2float(*reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2));
+                    val = valid ? val * kLog2e : ninf;
+                    s[nt][e] = val;
+                    rmax[rI] = fmaxf(rmax[rI], val);
+                }
+        }
+        // Lazy rescale: m_run is a reference, not the exact running maximum - it is only raised (and O, l rescaled)
+        // when a row's tile maximum outgrew it by 2^8, so P <= 256 stays inside f16 and most tiles skip the rescale.
+        float alpha[2], muse[2];
+#pragma unroll
+        for (int rI = 0; rI < 2; rI++) {
+            const float mt = quad_max(rmax[rI]);
+            const float mnew = (mt > m_run[rI] + 8.0f) ? mt : m_run[rI];   // -inf + 8 = -inf: the first finite maximum is taken
+            muse[rI] = mnew == ninf ? 0.0f : mnew;
+            alpha[rI] = (mnew == m_run[rI]) ? 1.0f : exp2f(m_run[rI] - muse[rI]);
+            m_run[rI] = mnew;
+            l_run[rI] *= alpha[rI];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = exp2f(s[nt][e] - muse[e >> 1]);
+                s[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+        uint32_t pf[4];
+        pf[0] = pack_half2(s[0][0], s[0][1]);
+        pf[1] = pack_half2(s[0][2], s[0][3]);
+        pf[2] = pack_half2(s[1][0], s[1][1]);
+        pf[3] = pack_half2(s[1][2], s[1][3]);
+        // the running maxima settle after a few tiles: the accumulator is only rescaled when some row of the warp moved
+        if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < HD / 8; i++) o[i][0] *= alpha[0], o[i][1] *= alpha[0], o[i][2] *= alpha[1], o[i][3] *= alpha[1];
+        }
+
+        // ---- O += P.V: keys 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1); this thread's bytes are dims 4g..4g+3 of each block ----
+#pragma unroll
+        for (int blk = 0; blk < NBLK; blk++) {
+            uint32_t w[4];
+            uint16_t db[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int key = 2 * t + (i & 1) + 8 * (i >> 1);
+                const uint8_t* bp = rawV + key * RB + blk * 34;
+                db[i] = (all_live || key < rows_valid) ? *reinterpret_cast<const uint16_t*>(bp) : (uint16_t)0;
+                if (blk & 1) {
+                    w[i] = *reinterpret_cast<const uint32_t*>(bp + 2 + 4 * g);
+                } else {
+                    const uint16_t* hp = reinterpret_cast<const uint16_t*>(bp + 2 + 4 * g);
+                    w[i] = hp[0] | ((uint32_t)hp[1] << 16);
+                }
+                w[i] ^= 0x80808080u;
+            }
+            const uint32_t d01b = db[0] | ((uint32_t)db[1] << 16), d23b = db[2] | ((uint32_t)db[3] << 16);
+            const __half2 d01 = *reinterpret_cast<const __half2*>(&d01b), d23 = *reinterpret_cast<const __half2*>(&d23b);
+            // pair the two keys of an operand register: x = {k0.j, k1.j, k0.j', k1.j'}
+            const uint32_t x01a = __byte_perm(w[0], w[1], 0x5140), x01b = __byte_perm(w[0], w[1], 0x7362);
+            const uint32_t x23a = __byte_perm(w[2], w[3], 0x5140), x23b = __byte_perm(w[2], w[3], 0x7362);
+            mma16816(o[4 * blk + 0], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x5140), d23));
+            mma16816(o[4 * blk + 1], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x7362), d23));
+            mma16816(o[4 * blk + 2], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x5140), d23));
+            mma16816(o[4 * blk + 3], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x7362), d23));
+        }
+        __syncwarp();       // every lane is done with this stage's bytes
+        issue(tile + NS);   // the next tile that lives in this stage: NS-1 tiles stay in flight during the arithmetic
+    }
+
+    // ---- merge the four warps' (m, l, O) in shared memory ----
+    __syncthreads();  // all warps are done with the raw stages (sO aliases them)
+    const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
+    if (t == 0) {
+        s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
+        s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
+    }
+    for (int idx = tid; idx < kDecRows * HD; idx += kThreads) sO[idx] = 0.0f;
+    __syncthreads();
+    float fac[2];
+#pragma unroll
+    for (int rI = 0; rI < 2; rI++) {
+        const int rr = g + rI * 8;
+        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
+        fac[rI] = (m_run[rI] == ninf) ? 0.0f : exp2f(m_run[rI] - M);
+    }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int rI = e >> 1;
+            const int dim = 32 * (nt >> 2) + 4 * (2 * t + (e & 1)) + (nt & 3);   // undo the n-tile permutation
+            if (fac[rI] != 0.0f) atomicAdd(&sO[(g + rI * 8) * HD + dim], o[nt][e] * fac[rI]);
+        }
+    if (tid < kDecRows) {
+        const int rr = tid;
+        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
+        float L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) L += (s_m[w][rr] == ninf) ? 0.0f : s_l[w][rr] * exp2f(s_m[w][rr] - M);
+        s_M[rr] = M, s_L[rr] = L;
+    }
+    __syncthreads();
+
+    if (a.n_splits == 1) {
+        for (int idx = tid; idx < R * HD; idx += kThreads) {
+            const int rr = idx / HD, c = idx % HD;
             const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
             const float L = s_L[rr];
             a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? sO[idx] / L : 0.0f;
@@ -687,9 +1056,10 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
 
 template <int HD, int MODE>
 int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
-    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : 2);
+    constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : kDecQ8Stages);
     constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
-    size_t smem = (size_t)(kDecRows + F16_STAGES * 2 * kDecBN) * HD * sizeof(__half);
+    constexpr int F16_TILES = MODE == kDecAsyncQ8 ? 1 : F16_STAGES * 2;
+    size_t smem = (size_t)(kDecRows + F16_TILES * kDecBN) * HD * sizeof(__half);
     if (MODE == kDecAsyncQ8) smem += (size_t)NS * 2 * kDecBN * (HD / 32 * 34);
     auto kern = fattn_decode_split_kernel<HD, MODE>;
     static bool smem_set[64] = {false};
@@ -721,14 +1091,37 @@ int decode_mode(const FattnArgs& a, int hdp) {
         // start at or beyond row kv_len are zero-filled, so reads stay inside rows [0, Lk) when Lk*rb % 16 == 0
         // or the head slab continues behind row Lk-1 (nb2 > Lk*rb).
         const bool tail_ok = ((int64_t)a.Lk * rb) % 16 == 0 || a.k.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16;
-        if (contiguous_rows && aligned && tail_ok && a.v.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16) return kDecAsyncQ8;
+        if (contiguous_rows && aligned && tail_ok && a.v.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16)
+            return (a.hd == 64 || a.hd == 128) ? kDecRegQ8 : kDecAsyncQ8;
     }
     return kDecSync;
 }
 
 template <int HD>
+int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
+    const size_t smem = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
+    auto kern = fattn_decode_q8reg_kernel<HD>;
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(kern, smem, smem_set);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(a.n_splits, a.Hkv, a.B);
+    kern<<<grid, kThreads, smem, st>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (a.n_splits > 1) {
+        const int warps = a.B * a.Hkv * kDecRows;
+        fattn_merge_kernel<HD><<<(warps + 3) / 4, kThreads, 0, st>>>(a);
+        e = cudaGetLastError();
+    }
+    return (int)e;
+}
+
+template <int HD>
 int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
     switch (decode_mode(a, HD)) {
+        case kDecRegQ8:
+            if constexpr (HD == 64 || HD == 128) return launch_decode_q8reg<HD>(a, st);
+            else return launch_decode_m<HD, kDecAsyncQ8>(a, st);
         case kDecAsyncF16: return launch_decode_m<HD, kDecAsyncF16>(a, st);
         case kDecAsyncQ8: return launch_decode_m<HD, kDecAsyncQ8>(a, st);
         default: return launch_decode_m<HD, kDecSync>(a, st);
