@@ -628,12 +628,15 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
                 s[nt][e] = val;
                 rmax[rI] = fmaxf(rmax[rI], val);
             }
+        // Lazy rescale: m_run is a reference, not the exact running maximum - it is only raised (and O, l rescaled)
+        // when a row's tile maximum outgrew it by 2^8, so P <= 256 stays inside f16 and most tiles skip the rescale.
         float alpha[2], muse[2];
 #pragma unroll
         for (int rI = 0; rI < 2; rI++) {
-            const float mnew = fmaxf(m_run[rI], quad_max(rmax[rI]));
+            const float mt = quad_max(rmax[rI]);
+            const float mnew = (mt > m_run[rI] + 8.0f) ? mt : m_run[rI];   // -inf + 8 = -inf: the first finite maximum is taken
             muse[rI] = mnew == ninf ? 0.0f : mnew;
-            alpha[rI] = exp2f(m_run[rI] - muse[rI]);
+            alpha[rI] = (mnew == m_run[rI]) ? 1.0f : exp2f(m_run[rI] - muse[rI]);
             m_run[rI] = mnew;
             l_run[rI] *= alpha[rI];
         }

@@ -301,6 +301,26 @@ def test_host_buffer_entry_point(b200, orc):
     b200.lib().b200_host_arena_release()
 
 
+def test_host_entry_point_chunked_decode_workspace(b200, orc):
+    """A decode batch large enough for one KV split per (stream, head) as a whole, but split when the host entry
+    point pipelines it in four batch chunks: the chunk launches need more split workspace than the whole call
+    would.  The chunked host result must equal the one-launch device result."""
+    rng = np.random.default_rng(77)
+    B, H, Lk, hd = 80, 8, 300, 64
+    q = torch.from_numpy(randn_f16(rng, (B, H, 1, hd))).pin_memory()
+    k = torch.from_numpy(randn_f16(rng, (B, H, Lk, hd))).pin_memory()
+    v = torch.from_numpy(randn_f16(rng, (B, H, Lk, hd))).pin_memory()
+    out = b200.flash_attn_ext_host(q, k, v, scale=0.125)
+    dev = b200.flash_attn_ext(q.cuda(), k.cuda(), v.cuda(), scale=0.125)
+    torch.cuda.synchronize()
+    assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+    assert float((out - dev.cpu()).abs().max()) < 1e-3   # same kernel; split count differs (summation order, f16 rounding of P against another reference maximum)
+    for b in (0, 79):
+        ref = orc.flash_attn_ext(q[b:b + 1].numpy(), k[b:b + 1].numpy(), v[b:b + 1].numpy(), scale=0.125)
+        assert_close(out[b:b + 1].numpy(), ref, f"chunked host decode, stream {b}")
+    b200.lib().b200_host_arena_release()
+
+
 def test_full_size_properties_cfg3(b200, orc):
     """BASELINE size of the encoder workload (64 segments x 20 heads x 1500 frames, one layer): two sampled
     segments against the oracle, batch invariance (a segment computed inside the batch equals the same segment
