@@ -419,6 +419,7 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
 #pragma unroll
     for (int idx0 = 0; idx0 < 16 * NBLK; idx0 += 32) {
         const int idx = idx0 + lane;
+        if (16 * NBLK < 32 && idx >= 16 * NBLK) break;   // head_dim 32: one block per row, half of the lanes idle
         const int row = 16 * warp + idx / NBLK, blk = idx % NBLK;
         const uint16_t* src = reinterpret_cast<const uint16_t*>(raw + row * RB + blk * 34);
         if (row >= rows_valid) {  // rows past the valid length read as zeros whatever the copy brought in

@@ -184,6 +184,43 @@ def test_cfg4_decode_ragged_streams(b200, orc, kernel, lens):
         assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
 
 
+@pytest.mark.parametrize("hd", [32, 64, 128])
+@pytest.mark.parametrize("form", ["plain", "causal3", "mask", "softcap"])
+def test_q8_0_decode_forms(b200, orc, kernel, hd, form):
+    """Q8_0 cache decode at every head dim with its own staging form (32: staged dequantise, 64 / 128: register
+    dequantise) through the general softmax path: multi-token causal decode, explicit mask, softcap, ragged lengths."""
+    rng = np.random.default_rng(100 + hd)
+    S, H, Hkv, max_ctx = 3, 8, 2, 352
+    lens = [333, 64, 201]
+    Tq = 3 if form == "causal3" else 1
+    kc, vc = _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx), _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx)
+    q = randn_f16(rng, (S, H, Tq, hd)).astype(np.float32)
+    Lk = max(lens)
+    kv, vv = kc[:, :, :Lk], vc[:, :, :Lk]
+    kw = dict(scale=hd ** -0.5, kv_type=abi.Q8_0)
+    mask = None
+    if form == "causal3":
+        # three new tokens at the end of each stream: row i sees keys < len - 2 + i; expressed as explicit masks for the oracle
+        mask = np.zeros((S, 1, Tq, Lk), np.float16)
+        for b, n in enumerate(lens):
+            for i in range(Tq):
+                mask[b, 0, i, n - (Tq - 1) + i:] = -np.inf
+        ref = orc.flash_attn_ext(q, kv, vv, mask, **kw)
+        got = np.stack([gpu_op(b200, q[b:b + 1], cuda_view(kv[b:b + 1, :, :lens[b]], kc), cuda_view(vv[b:b + 1, :, :lens[b]], vc),
+                               causal=True, n_past=lens[b] - Tq, **kw)[0] for b in range(S)])
+    else:
+        if form == "mask":
+            mask = np.where(rng.random((S, 1, Tq, Lk)) < 0.3, -np.inf, 0.0).astype(np.float16)
+            mask[..., 0] = 0
+        if form == "softcap":
+            kw["softcap"] = 5.0
+        ref = orc.flash_attn_ext(q, kv, vv, mask, kv_len=lens, **kw)
+        got = gpu_op(b200, q, cuda_view(kv, kc), cuda_view(vv, vc), mask, kv_len=lens, **kw)
+    assert_close(got, ref, f"Q8_0 decode hd={hd} {form}")
+    if kernel == "auto":
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+
+
 def test_cfg4_decode_f16_cache_gqa(b200, orc, kernel):
     rng = np.random.default_rng(33)
     S, H, Hkv, hd, Lk = 4, 32, 8, 128, 535
