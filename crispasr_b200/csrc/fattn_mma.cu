@@ -472,7 +472,6 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
     constexpr int F16_TILES = MODE == kDecAsyncQ8 ? 1 : F16_STAGES * 2;   // Q8: K and V take turns in one fp16 tile
     uint8_t* sRaw = reinterpret_cast<uint8_t*>(sKV + F16_TILES * TILE_HALVES);  // Q8: NS stages of raw K|V
-    float* sO = reinterpret_cast<float*>(sKV);                      // [16][HD] fp32, reused after the key loop
     __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -669,14 +668,21 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     }
     if (MODE == kDecAsyncF16) cp_async_wait<0>();
 
+    // the merge kernel (if any) may start launching: it waits for this grid's completion before reading anything
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- merge the four warps' (m, l, O) in shared memory ----
     __syncthreads();  // all warps are done with the K/V tiles
+    // Each warp scales its partial O to the common maximum and parks it in its own padded slab (plain stores; the
+    // slabs start at the base of dynamic shared memory - Q and the tiles are dead by now); the CTA then sums the four
+    // slabs while writing out.  (Shared-memory atomics on one [16][HD] array serialised the four warps and cost
+    // about 15 us per launch when a CTA has a single tile.)
+    constexpr int SLAB_STRIDE = HD + 4;
+    float* slab = reinterpret_cast<float*>(smem_raw);   // [4][16][SLAB_STRIDE]
     const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
     if (t == 0) {
         s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
         s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
     }
-    for (int idx = tid; idx < kDecRows * HD; idx += kThreads) sO[idx] = 0.0f;
     __syncthreads();
     float fac[2];
 #pragma unroll
@@ -690,7 +696,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int rI = e >> 1;
-            if (fac[rI] != 0.0f) atomicAdd(&sO[(g + rI * 8) * HD + nt * 8 + 2 * t + (e & 1)], o[nt][e] * fac[rI]);
+            const int dim = nt * 8 + 2 * t + (e & 1);
+            slab[(warp * kDecRows + g + rI * 8) * SLAB_STRIDE + dim] = fac[rI] != 0.0f ? o[nt][e] * fac[rI] : 0.0f;
         }
     if (tid < kDecRows) {
         const int rr = tid;
@@ -701,6 +708,10 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         s_M[rr] = M, s_L[rr] = L;
     }
     __syncthreads();
+    auto merged = [&](int rr, int c) {
+        return (slab[(0 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(1 * kDecRows + rr) * SLAB_STRIDE + c]) +
+               (slab[(2 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(3 * kDecRows + rr) * SLAB_STRIDE + c]);
+    };
 
     if (a.n_splits == 1) {
         for (int idx = tid; idx < R * HD; idx += kThreads) {
@@ -708,12 +719,12 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             if (c >= a.hd) continue;
             const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
             const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? sO[idx] / L : 0.0f;
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? merged(rr, c) / L : 0.0f;
         }
     } else {
         const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
         float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = sO[idx];
+        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);
         if (tid < kDecRows) {
             a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
             a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
@@ -745,7 +756,6 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);                                  // [16][HD], 16-byte chunks swizzled
     uint8_t* sRaw = smem_raw + kDecRows * HD * sizeof(__half);                          // NS stages of raw K | V
-    float* sO = reinterpret_cast<float*>(sRaw);                                         // [16][HD] fp32, reused after the key loop
     __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
     __shared__ __align__(8) uint64_t s_bar[4][NS];                                      // one barrier per (warp, stage)
 
@@ -966,14 +976,21 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         issue(tile + NS);   // the next tile that lives in this stage: NS-1 tiles stay in flight during the arithmetic
     }
 
+    // the merge kernel (if any) may start launching: it waits for this grid's completion before reading anything
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- merge the four warps' (m, l, O) in shared memory ----
-    __syncthreads();  // all warps are done with the raw stages (sO aliases them)
+    __syncthreads();  // all warps are done with the raw stages (the merge slabs alias them)
+    // Each warp scales its partial O to the common maximum and parks it in its own padded slab (plain stores; the
+    // slabs start at the base of dynamic shared memory - Q and the tiles are dead by now); the CTA then sums the four
+    // slabs while writing out.  (Shared-memory atomics on one [16][HD] array serialised the four warps and cost
+    // about 15 us per launch when a CTA has a single tile.)
+    constexpr int SLAB_STRIDE = HD + 4;
+    float* slab = reinterpret_cast<float*>(smem_raw);   // [4][16][SLAB_STRIDE]
     const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
     if (t == 0) {
         s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
         s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
     }
-    for (int idx = tid; idx < kDecRows * HD; idx += kThreads) sO[idx] = 0.0f;
     __syncthreads();
     float fac[2];
 #pragma unroll
@@ -987,8 +1004,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int rI = e >> 1;
-            const int dim = 32 * (nt >> 2) + 4 * (2 * t + (e & 1)) + (nt & 3);   // undo the n-tile permutation
-            if (fac[rI] != 0.0f) atomicAdd(&sO[(g + rI * 8) * HD + dim], o[nt][e] * fac[rI]);
+            const int dim = 32 * (nt >> 2) + 4 * (2 * t + (e & 1)) + (nt & 3);
+            slab[(warp * kDecRows + g + rI * 8) * SLAB_STRIDE + dim] = fac[rI] != 0.0f ? o[nt][e] * fac[rI] : 0.0f;
         }
     if (tid < kDecRows) {
         const int rr = tid;
@@ -999,18 +1016,23 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         s_M[rr] = M, s_L[rr] = L;
     }
     __syncthreads();
+    auto merged = [&](int rr, int c) {
+        return (slab[(0 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(1 * kDecRows + rr) * SLAB_STRIDE + c]) +
+               (slab[(2 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(3 * kDecRows + rr) * SLAB_STRIDE + c]);
+    };
 
     if (a.n_splits == 1) {
         for (int idx = tid; idx < R * HD; idx += kThreads) {
             const int rr = idx / HD, c = idx % HD;
+            if (c >= a.hd) continue;
             const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
             const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? sO[idx] / L : 0.0f;
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? merged(rr, c) / L : 0.0f;
         }
     } else {
         const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
         float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = sO[idx];
+        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);
         if (tid < kDecRows) {
             a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
             a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
@@ -1021,6 +1043,9 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
 // One warp per (batch, kv-head, row): log-sum-exp merge of the split partials.
 template <int HD>
 __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a) {
+    // Launched with programmatic stream serialisation: its CTAs may become resident while the split kernel drains;
+    // nothing of the workspace is read before the split grid has completed and flushed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp_global = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int R = a.Tq * a.gqa;
@@ -1039,14 +1064,26 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
 #pragma unroll
     for (int i = 0; i < HD / 32; i++) acc[i] = 0.0f;
     float L = 0.0f;
-    for (int s = 0; s < a.n_splits; s++) {
-        const float ms = a.ws_ml[((unit0 + s) * kDecRows + rr) * 2];
-        if (ms == -INFINITY) continue;
-        const float w = exp2f(ms - M);
-        L += w * a.ws_ml[((unit0 + s) * kDecRows + rr) * 2 + 1];
-        const float* po = a.ws_o + ((unit0 + s) * kDecRows + rr) * HD;
+    // eight splits per round: all their loads are issued before the first is used (a round trip per round, not per split)
+    for (int s0 = 0; s0 < a.n_splits; s0 += 8) {
+        float2 ml[8];
+        float po[8][HD / 32];
 #pragma unroll
-        for (int i = 0; i < HD / 32; i++) acc[i] += w * po[lane + 32 * i];
+        for (int u = 0; u < 8; u++) {
+            const int s = min(s0 + u, a.n_splits - 1);
+            ml[u] = *reinterpret_cast<const float2*>(a.ws_ml + ((unit0 + s) * kDecRows + rr) * 2);
+            const float* p = a.ws_o + ((unit0 + s) * kDecRows + rr) * HD;
+#pragma unroll
+            for (int i = 0; i < HD / 32; i++) po[u][i] = p[lane + 32 * i];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (s0 + u >= a.n_splits || ml[u].x == -INFINITY) continue;
+            const float w = exp2f(ml[u].x - M);
+            L += w * ml[u].y;
+#pragma unroll
+            for (int i = 0; i < HD / 32; i++) acc[i] += w * po[u][i];
+        }
     }
     const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
     float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd;
@@ -1056,6 +1093,24 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
         const int c = lane + 32 * i;
         if (c < a.hd) out[c] = acc[i] * inv;
     }
+}
+
+// Merge kernel with programmatic stream serialisation (its launch overlaps the tail of the split kernel; the
+// kernel itself waits for the split grid before it reads the workspace).
+template <int HD>
+cudaError_t launch_merge(const FattnArgs& a, cudaStream_t st) {
+    const int warps = a.B * a.Hkv * kDecRows;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((warps + 3) / 4);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, fattn_merge_kernel<HD>, a);
 }
 
 template <int HD, int MODE>
@@ -1073,11 +1128,7 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     kern<<<grid, kThreads, smem, st>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (a.n_splits > 1) {
-        const int warps = a.B * a.Hkv * kDecRows;
-        fattn_merge_kernel<HD><<<(warps + 3) / 4, kThreads, 0, st>>>(a);
-        e = cudaGetLastError();
-    }
+    if (a.n_splits > 1) e = launch_merge<HD>(a, st);
     return (int)e;
 }
 
@@ -1112,11 +1163,7 @@ int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
     kern<<<grid, kThreads, smem, st>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (a.n_splits > 1) {
-        const int warps = a.B * a.Hkv * kDecRows;
-        fattn_merge_kernel<HD><<<(warps + 3) / 4, kThreads, 0, st>>>(a);
-        e = cudaGetLastError();
-    }
+    if (a.n_splits > 1) e = launch_merge<HD>(a, st);
     return (int)e;
 }
 
