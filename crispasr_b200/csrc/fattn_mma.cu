@@ -1048,36 +1048,43 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp_global = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    const int R = a.Tq * a.gqa;
-    const int total = a.B * a.Hkv * kDecRows;
+    const int R = a.Tq * a.gqa;   // live rows per (batch, kv head); one warp each
+    const int total = a.B * a.Hkv * R;
     if (warp_global >= total) return;
-    const int rr = warp_global % kDecRows;
-    const int hk = (warp_global / kDecRows) % a.Hkv;
-    const int b = warp_global / (kDecRows * a.Hkv);
-    if (rr >= R) return;
+    const int rr = warp_global % R;
+    const int hk = (warp_global / R) % a.Hkv;
+    const int b = warp_global / (R * a.Hkv);
     const int64_t unit0 = ((int64_t)b * a.Hkv + hk) * a.n_splits;
-    float M = -INFINITY;
-    for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, a.ws_ml[((unit0 + s) * kDecRows + rr) * 2]);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    // One pass, sixteen splits per round: every load of a round is issued before the first is used (one memory
+    // round trip per round), and the running (M, L, acc) are rescaled when a round raises the maximum.
+    float M = -INFINITY, L = 0.0f;
     float acc[HD / 32];
 #pragma unroll
     for (int i = 0; i < HD / 32; i++) acc[i] = 0.0f;
-    float L = 0.0f;
-    // eight splits per round: all their loads are issued before the first is used (a round trip per round, not per split)
-    for (int s0 = 0; s0 < a.n_splits; s0 += 8) {
-        float2 ml[8];
-        float po[8][HD / 32];
+    for (int s0 = 0; s0 < a.n_splits; s0 += 16) {
+        float2 ml[16];
+        float po[16][HD / 32];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < 16; u++) {
             const int s = min(s0 + u, a.n_splits - 1);
             ml[u] = *reinterpret_cast<const float2*>(a.ws_ml + ((unit0 + s) * kDecRows + rr) * 2);
             const float* p = a.ws_o + ((unit0 + s) * kDecRows + rr) * HD;
 #pragma unroll
             for (int i = 0; i < HD / 32; i++) po[u][i] = p[lane + 32 * i];
         }
+        float Mr = M;
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < 16; u++)
+            if (s0 + u < a.n_splits) Mr = fmaxf(Mr, ml[u].x);
+        if (Mr > M) {
+            const float scale_old = (M == -INFINITY) ? 0.0f : exp2f(M - Mr);
+            L *= scale_old;
+#pragma unroll
+            for (int i = 0; i < HD / 32; i++) acc[i] *= scale_old;
+            M = Mr;
+        }
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
             if (s0 + u >= a.n_splits || ml[u].x == -INFINITY) continue;
             const float w = exp2f(ml[u].x - M);
             L += w * ml[u].y;
@@ -1099,7 +1106,7 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
 // kernel itself waits for the split grid before it reads the workspace).
 template <int HD>
 cudaError_t launch_merge(const FattnArgs& a, cudaStream_t st) {
-    const int warps = a.B * a.Hkv * kDecRows;
+    const int warps = a.B * a.Hkv * a.Tq * a.gqa;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((warps + 3) / 4);
     cfg.blockDim = dim3(kThreads);
