@@ -377,7 +377,15 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q0 = blockIdx.x * kTile, h = blockIdx.y, b = blockIdx.z;
+    // Causal launches hand out the query tiles with the most KV tiles first (longest-processing-time order over
+    // the whole grid: the tile index becomes the slowest-varying coordinate, reversed), which shortens the tail of
+    // short prefills; otherwise consecutive CTAs are the query tiles of one head, which share K/V in L2.
+    int q0 = blockIdx.x * kTile, h = blockIdx.y, b = blockIdx.z;
+    if (a.causal) {
+        const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), hb = gridDim.y * gridDim.z;
+        q0 = (gridDim.x - 1 - lin / hb) * kTile;
+        h = (lin % hb) % gridDim.y, b = (lin % hb) / gridDim.y;
+    }
     const int hk = h / a.gqa, bk = b / a.bq;
 
     int len_b = a.Lk;
