@@ -269,8 +269,7 @@ int do_launch(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st) {
             void* kbuf = workspace;
             void* vbuf = (uint8_t*)workspace + plan.cast_each;
             const int Bk = a.B / a.bq;
-            ce = launch_kv_to_f16(a.k, kbuf, a.hd, a.Lk, a.Hkv, Bk, st);
-            if (ce == 0) ce = launch_kv_to_f16(a.v, vbuf, a.hd, a.Lk, a.Hkv, Bk, st);
+            ce = launch_kv_pair_to_f16(a.k, kbuf, a.v, vbuf, a.hd, a.Lk, a.Hkv, Bk, st);
             c = with_f16_kv(c, kbuf, vbuf);
         }
         if (ce == 0 && plan.cast_r) {

@@ -72,6 +72,8 @@ int launch_tile_mma(const FattnArgs& a, cudaStream_t st);
 int launch_decode_split(const FattnArgs& a, cudaStream_t st);
 // Converts K or V (F32 / Q8_0 / unaligned F16, any strides) to contiguous F16 [hd, Lk, Hkv, Bk] at `dst`.
 int launch_kv_to_f16(const View& src, void* dst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st);
+// K and V of one call in one launch.
+int launch_kv_pair_to_f16(const View& k, void* kdst, const View& v, void* vdst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st);
 size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd);
 int decode_split_choose(int B, int Hkv, int Lk, int sm_count);
 

@@ -1187,7 +1187,11 @@ int launch_decode_t(const FattnArgs& a, cudaStream_t st) {
 }
 
 // K or V of any supported type / stride -> contiguous F16 [hd, Lk, Hkv, Bk] (the operand form of the tcgen05 kernels).
-__global__ void kv_to_f16_kernel(const View src, uint8_t* dst, int hd, int Lk, int Hkv, int Bk) {
+// blockIdx.y selects the tensor: K and V of one call are converted by one launch.
+__global__ void kv_to_f16_kernel(const View src0, uint8_t* dst0, const View src1, uint8_t* dst1, int hd, int Lk, int Hkv, int Bk) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the attention kernel may start its set-up
+    const View& src = blockIdx.y ? src1 : src0;
+    uint8_t* dst = blockIdx.y ? dst1 : dst0;
     const int cpr = hd / 8;
     const int64_t total = (int64_t)Bk * Hkv * Lk * cpr;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -1206,7 +1210,14 @@ __global__ void kv_to_f16_kernel(const View src, uint8_t* dst, int hd, int Lk, i
 int launch_kv_to_f16(const View& src, void* dst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st) {
     const int64_t total = (int64_t)Bk * Hkv * Lk * (hd / 8);
     const int blocks = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
-    kv_to_f16_kernel<<<blocks, 256, 0, st>>>(src, (uint8_t*)dst, hd, Lk, Hkv, Bk);
+    kv_to_f16_kernel<<<dim3(blocks, 1), 256, 0, st>>>(src, (uint8_t*)dst, src, (uint8_t*)dst, hd, Lk, Hkv, Bk);
+    return (int)cudaGetLastError();
+}
+
+int launch_kv_pair_to_f16(const View& k, void* kdst, const View& v, void* vdst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st) {
+    const int64_t total = (int64_t)Bk * Hkv * Lk * (hd / 8);
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    kv_to_f16_kernel<<<dim3(blocks, 2), 256, 0, st>>>(k, (uint8_t*)kdst, v, (uint8_t*)vdst, hd, Lk, Hkv, Bk);
     return (int)cudaGetLastError();
 }
 

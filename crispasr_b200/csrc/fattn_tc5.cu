@@ -377,6 +377,9 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // launched with programmatic stream serialisation: nothing is read or written before the previous kernel of the
+    // stream (e.g. the K/V conversion pass) has completed and flushed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Causal launches hand out the query tiles with the most KV tiles first (longest-processing-time order over
     // the whole grid: the tile index becomes the slowest-varying coordinate, reversed), which shortens the tail of
     // short prefills; otherwise consecutive CTAs are the query tiles of one head, which share K/V in L2.
@@ -1170,6 +1173,24 @@ int launch_relpos(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errl
     return B200_OK;
 }
 
+// Launch that may begin while the previous kernel of the stream drains, if that kernel allows it
+// (griddepcontrol.launch_dependents: the K/V conversion pre-pass does).  The kernels wait for the predecessor's
+// completion (griddepcontrol.wait) before they read anything it may have written.
+template <typename Kern, typename... Args>
+cudaError_t launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <int HD, int NSTG>
 int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     CUtensorMap tmK, tmV;
@@ -1186,16 +1207,14 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
-            e = cudaGetLastError();
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
         }
     } else {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            kern<<<grid, kThreadsTc5, smem, st>>>(a, tmK, tmV);
-            e = cudaGetLastError();
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
         }
     }
     if (e != cudaSuccess) {
