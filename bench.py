@@ -56,12 +56,12 @@ WORKLOADS = {
 # under profiles/ (bytes, units per GPU of the captured launch).  Traffic grows in proportion to the units, so the
 # bench scales it to its own launch size.
 NCU_TRAFFIC = {
-    "whisper_large_v3_encoder": (120.40e6, 8),
-    "whisper_large_v3_decode_cross": (497.02e6, 64),
-    "whisper_large_v3_decode_self": (762.05e6, 64),
-    "voxtral_decode_q8_0": (308.83e6, 256),
-    "parakeet_relpos_encoder": (106.33e6, 1),
-    "hd128_prefill_probe": (48.17e6, 1),
+    "whisper_large_v3_encoder": (120.89e6, 8),
+    "whisper_large_v3_decode_cross": (498.35e6, 64),
+    "whisper_large_v3_decode_self": (761.87e6, 64),
+    "voxtral_decode_q8_0": (307.60e6, 256),
+    "parakeet_relpos_encoder": (103.11e6, 1),
+    "hd128_prefill_probe": (48.61e6, 1),
 }
 
 
