@@ -591,16 +591,32 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             const int n_valid = kend - j * kTile;  // columns >= n_valid of this row are masked
             const bool full_tile = __all_sync(0xffffffffu, n_valid >= kTile);
             if (j == 0) {
-                // first tile: the reference maximum is the tile maximum (max-only pass over S)
+                // First tile: a first reference maximum.  Without a mask the maximum of the row's first 32 scores
+                // is enough - it is rarely more than 2^8 below the row's real maximum, and when it is (or when those
+                // columns are masked) the lazy-rescale check below redoes the tile against the exact maximum.
                 float mx = -INFINITY;
+                if (HASMASK) {
 #pragma unroll
-                for (int hh = 0; hh < 2; hh++) {
-                    uint32_t sreg[2][32];
-                    tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
-                    tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                    for (int hh = 0; hh < 2; hh++) {
+                        uint32_t sreg[2][32];
+                        tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                        tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                        tmem_wait_ld();
+                        apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
+                        mx = fmaxf(mx, row_max64(sreg, hh * 64, full_tile ? 2 * kTile : n_valid));
+                    }
+                } else {
+                    uint32_t s0[32];
+                    tmem_ld32(tmem_S + lane_base, s0);
                     tmem_wait_ld();
-                    if (HASMASK) apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
-                    mx = fmaxf(mx, row_max64(sreg, hh * 64, full_tile ? 2 * kTile : n_valid));
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float x0 = (i < n_valid) ? __uint_as_float(s0[i]) : -INFINITY;
+                        const float x1 = (i + 1 < n_valid) ? __uint_as_float(s0[i + 1]) : -INFINITY;
+                        m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], x0, x1);
+                    }
+                    mx = max3(fmaxf(m4[0], m4[1]), m4[2], m4[3]);
                 }
                 m_ref = mx * c_exp;  // c > 0
             }
