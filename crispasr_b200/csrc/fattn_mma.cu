@@ -472,6 +472,11 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     constexpr int F16_STAGES = MODE == kDecAsyncF16 ? NS : 1;
     constexpr int F16_TILES = MODE == kDecAsyncQ8 ? 1 : F16_STAGES * 2;   // Q8: K and V take turns in one fp16 tile
     uint8_t* sRaw = reinterpret_cast<uint8_t*>(sKV + F16_TILES * TILE_HALVES);  // Q8: NS stages of raw K|V
+    // F16 ring + explicit mask with 16-byte aligned rows: the mask values of a tile (R rows x 64 keys) travel with
+    // the K/V tile through the same cp.async stage, so the softmax reads them from shared memory instead of
+    // stalling on global loads issued right before their use.
+    const bool stage_mask = MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16;
+    __half* sMask = reinterpret_cast<__half*>(sRaw);   // [NS][R][64] (F16 ring mode has no raw stages)
     __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -512,6 +517,17 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             const int stage = (tile - tile_lo) % NS;
             issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid);
             issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid);
+            if (stage_mask && tid < R * 8) {
+                const int rr = tid >> 3, ch = tid & 7;
+                const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+                const int key0 = tile * kDecBN + ch * 8;
+                const int nbytes = max(0, min(8, a.Lk - key0)) * 2;   // the mask row holds Lk values; the rest reads as 0
+                const uint8_t* src = a.mask.p + (int64_t)iq * a.mask.nb1 + (int64_t)(hq % a.mask_ne2) * a.mask.nb2 +
+                                     (int64_t)(b % a.mask_ne3) * a.mask.nb3 + (int64_t)(nbytes ? key0 : 0) * 2;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(sMask + ((stage * R + rr) * kDecBN + ch * 8))),
+                             "l"(src), "r"(nbytes)
+                             : "memory");
+            }
         }
         cp_async_commit();
     };
@@ -622,8 +638,11 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
                 float val = s[nt][e] * a.scale;
                 if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
                 const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + row_iq[rI]);
-                if (row_mask[rI] && valid)
-                    val += row_slope[rI] * __half2float(*reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2));
+                if (row_mask[rI] && valid) {
+                    const __half mh = stage_mask ? sMask[(((tile - tile_lo) % NS) * R + g + rI * 8) * kDecBN + (ik - k0)]
+                                                 : *reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2);
+                    val += row_slope[rI] * __half2float(mh);
+                }
                 val = valid ? val * kLog2e : ninf;
                 s[nt][e] = val;
                 rmax[rI] = fmaxf(rmax[rI], val);
@@ -1127,9 +1146,12 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     constexpr int F16_TILES = MODE == kDecAsyncQ8 ? 1 : F16_STAGES * 2;
     size_t smem = (size_t)(kDecRows + F16_TILES * kDecBN) * HD * sizeof(__half);
     if (MODE == kDecAsyncQ8) smem += (size_t)NS * 2 * kDecBN * (HD / 32 * 34);
+    // the attribute is raised once, to the largest size this instantiation can ask for (mask staging for 16 rows)
+    const size_t smem_attr = smem + (MODE == kDecAsyncF16 ? (size_t)NS * kDecRows * kDecBN * sizeof(__half) : 0);
+    if (MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16) smem += (size_t)NS * (a.Tq * a.gqa) * kDecBN * sizeof(__half);
     auto kern = fattn_decode_split_kernel<HD, MODE>;
     static bool smem_set[64] = {false};
-    cudaError_t e = set_smem_once(kern, smem, smem_set);
+    cudaError_t e = set_smem_once(kern, smem_attr, smem_set);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(a.n_splits, a.Hkv, a.B);
     kern<<<grid, kThreads, smem, st>>>(a);
