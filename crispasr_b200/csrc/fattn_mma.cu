@@ -460,7 +460,7 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
     }
 }
 
-template <int HD, int MODE>
+template <int HD, int MODE, bool STAGE_MASK = false>
 __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
     constexpr int RAW_BYTES = kDecBN * (HD / 32 * 34);    // one raw Q8_0 K or V tile
@@ -475,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     // F16 ring + explicit mask with 16-byte aligned rows: the mask values of a tile (R rows x 64 keys) travel with
     // the K/V tile through the same cp.async stage, so the softmax reads them from shared memory instead of
     // stalling on global loads issued right before their use.
-    const bool stage_mask = MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16;
+    constexpr bool stage_mask = STAGE_MASK;   // separate instantiation: the maskless kernel carries none of it
     __half* sMask = reinterpret_cast<__half*>(sRaw);   // [NS][R][64] (F16 ring mode has no raw stages)
     __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
 
@@ -1149,12 +1149,21 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     // the attribute is raised once, to the largest size this instantiation can ask for (mask staging for 16 rows)
     const size_t smem_attr = smem + (MODE == kDecAsyncF16 ? (size_t)NS * kDecRows * kDecBN * sizeof(__half) : 0);
     if (MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16) smem += (size_t)NS * (a.Tq * a.gqa) * kDecBN * sizeof(__half);
-    auto kern = fattn_decode_split_kernel<HD, MODE>;
-    static bool smem_set[64] = {false};
-    cudaError_t e = set_smem_once(kern, smem_attr, smem_set);
-    if (e != cudaSuccess) return (int)e;
     dim3 grid(a.n_splits, a.Hkv, a.B);
-    kern<<<grid, kThreads, smem, st>>>(a);
+    cudaError_t e;
+    if (MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16) {
+        auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem_attr, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    } else {
+        auto kern = fattn_decode_split_kernel<HD, MODE, false>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (a.n_splits > 1) e = launch_merge<HD>(a, st);
