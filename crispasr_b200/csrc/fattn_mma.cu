@@ -767,7 +767,9 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
 // fp16(d*q), bit-identical to the staged dequantiser and to the reference's dequantise-then-cast.
 constexpr int kDecRegStages = 3;
 
-template <int HD>
+// PLAIN: no explicit mask, no softcap, no causal bound (single-token decode): only kv_len limits the keys.  A separate
+// instantiation, so the common case carries none of the general path's registers and code.
+template <int HD, bool PLAIN>
 __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const FattnArgs a) {
     constexpr int NBLK = HD / 32, RB = NBLK * 34;
     constexpr int RAW_BYTES = kDecBN * RB;   // one raw K or V tile
@@ -839,12 +841,12 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
             }
         }
 
-    // per-thread row metadata for rows g and g+8
-    int row_iq[2];
-    float row_slope[2];
-    const uint8_t* row_mask[2];
+    // per-thread row metadata for rows g and g+8 (general path only)
+    int row_iq[2] = {0, 0};
+    float row_slope[2] = {1.0f, 1.0f};
+    const uint8_t* row_mask[2] = {nullptr, nullptr};
 #pragma unroll
-    for (int rI = 0; rI < 2; rI++) {
+    for (int rI = 0; rI < 2 && !PLAIN; rI++) {
         const int rr = g + rI * 8;
         row_iq[rI] = rr / a.gqa;
         const int hq = hk * a.gqa + rr % a.gqa;
@@ -905,7 +907,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
 
         float rmax[2] = {ninf, ninf};
         // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
-        const bool plain_tile = !a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1);
+        const bool plain_tile = PLAIN ? (k0 + kDecBN <= len_b)
+                                      : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1));
         if (plain_tile) {
             const float c = a.scale * kLog2e;
 #pragma unroll
@@ -913,6 +916,16 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     s[nt][e] *= c;
+                    rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+                }
+        } else if (PLAIN) {   // last tile of the valid range
+            const float c = a.scale * kLog2e;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
+                    s[nt][e] = ik < len_b ? s[nt][e] * c : ninf;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
                 }
         } else {
@@ -1193,12 +1206,21 @@ int decode_mode(const FattnArgs& a, int hdp) {
 template <int HD>
 int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
     const size_t smem = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
-    auto kern = fattn_decode_q8reg_kernel<HD>;
-    static bool smem_set[64] = {false};
-    cudaError_t e = set_smem_once(kern, smem, smem_set);
-    if (e != cudaSuccess) return (int)e;
     dim3 grid(a.n_splits, a.Hkv, a.B);
-    kern<<<grid, kThreads, smem, st>>>(a);
+    cudaError_t e;
+    if (!a.has_mask && a.softcap == 0.0f && !a.causal) {
+        auto kern = fattn_decode_q8reg_kernel<HD, true>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    } else {
+        auto kern = fattn_decode_q8reg_kernel<HD, false>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (a.n_splits > 1) e = launch_merge<HD>(a, st);
