@@ -460,7 +460,8 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
     }
 }
 
-template <int HD, int MODE, bool STAGE_MASK = false>
+// PLAIN: no explicit mask, no softcap, no causal bound: only kv_len limits the keys (its own instantiation).
+template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false>
 __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
     constexpr int RAW_BYTES = kDecBN * (HD / 32 * 34);    // one raw Q8_0 K or V tile
@@ -553,11 +554,11 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     for (int ks = 0; ks < HD / 16; ks++) ldsm_x4(qf[ks], tile_addr<HD>(sQ, lane & 15, ks * 2 + (lane >> 4)));
 
     // per-thread row metadata for rows g and g+8
-    int row_iq[2];
-    float row_slope[2];
-    const uint8_t* row_mask[2];
+    int row_iq[2] = {0, 0};
+    float row_slope[2] = {1.0f, 1.0f};
+    const uint8_t* row_mask[2] = {nullptr, nullptr};
 #pragma unroll
-    for (int rI = 0; rI < 2; rI++) {
+    for (int rI = 0; rI < 2 && !PLAIN; rI++) {
         const int rr = g + rI * 8;
         row_iq[rI] = rr / a.gqa;
         const int hq = hk * a.gqa + rr % a.gqa;
@@ -618,7 +619,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         }
         float rmax[2] = {ninf, ninf};
         // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
-        const bool plain_tile = !a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1);
+        const bool plain_tile = PLAIN ? (k0 + kDecBN <= len_b)
+                                      : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1));
         if (plain_tile) {
             const float c = a.scale * kLog2e;
 #pragma unroll
@@ -626,6 +628,16 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     s[nt][e] *= c;
+                    rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+                }
+        } else if (PLAIN) {   // last tile of the valid range
+            const float c = a.scale * kLog2e;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
+                    s[nt][e] = ik < len_b ? s[nt][e] * c : ninf;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
                 }
         } else
@@ -1170,8 +1182,14 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
         e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         kern<<<grid, kThreads, smem, st>>>(a);
+    } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal) {
+        auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
     } else {
-        auto kern = fattn_decode_split_kernel<HD, MODE, false>;
+        auto kern = fattn_decode_split_kernel<HD, MODE, false, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
