@@ -49,6 +49,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x on the exponential unit, one instruction (exp2f adds a range fix-up that P in f16 does not need; -inf -> 0).
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Eight consecutive elements [c0, c0+8) of one row, converted to fp16 (zero beyond hd).
 __device__ __forceinline__ uint4 load8_as_half(const uint8_t* rowp, int type, int c0, int hd, bool vec16) {
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
@@ -265,7 +272,7 @@ __global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArg
         for (int nt = 0; nt < BN / 8; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const float p = exp2f(s[nt][e] - muse[e >> 1]);
+                const float p = fast_ex2(s[nt][e] - muse[e >> 1]);
                 s[nt][e] = p;
                 l_run[e >> 1] += p;
             }
@@ -675,7 +682,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const float p = exp2f(s[nt][e] - muse[e >> 1]);
+                const float p = fast_ex2(s[nt][e] - muse[e >> 1]);
                 s[nt][e] = p;
                 l_run[e >> 1] += p;
             }
@@ -973,7 +980,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const float p = exp2f(s[nt][e] - muse[e >> 1]);
+                const float p = fast_ex2(s[nt][e] - muse[e >> 1]);
                 s[nt][e] = p;
                 l_run[e >> 1] += p;
             }
