@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     float row_slope[2] = {1.0f, 1.0f};
     const uint8_t* row_mask[2] = {nullptr, nullptr};
 #pragma unroll
-    for (int rI = 0; rI < 2 && !PLAIN; rI++) {
+    for (int rI = 0; rI < 2 && !PLAIN && !STAGE_MASK; rI++) {
         const int rr = g + rI * 8;
         row_iq[rI] = rr / a.gqa;
         const int hq = hk * a.gqa + rr % a.gqa;
@@ -626,7 +626,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         }
         float rmax[2] = {ninf, ninf};
         // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
-        const bool plain_tile = PLAIN ? (k0 + kDecBN <= len_b)
+        const bool plain_tile = STAGE_MASK ? false : PLAIN ? (k0 + kDecBN <= len_b)
                                       : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1));
         if (plain_tile) {
             const float c = a.scale * kLog2e;
@@ -647,6 +647,22 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
                     s[nt][e] = ik < len_b ? s[nt][e] * c : ninf;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
                 }
+        } else if (STAGE_MASK) {
+            // this instantiation is only launched without softcap, ALiBi and causal bound: logit = s*scale + mask
+            const float c = a.scale * kLog2e;
+            const __half* mt = sMask + ((tile - tile_lo) % NS) * R * kDecBN + warp * 16 + 2 * t;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int rI = 0; rI < 2; rI++) {
+                    const int rr = g + rI * 8, ik = k0 + warp * 16 + nt * 8 + 2 * t;
+                    float2 m2 = make_float2(0.0f, 0.0f);
+                    if (rr < R) m2 = __half22float2(*reinterpret_cast<const __half2*>(mt + rr * kDecBN + nt * 8));
+                    const float v0 = ik < len_b ? fmaf(s[nt][2 * rI], c, m2.x * kLog2e) : ninf;
+                    const float v1 = ik + 1 < len_b ? fmaf(s[nt][2 * rI + 1], c, m2.y * kLog2e) : ninf;
+                    s[nt][2 * rI] = v0, s[nt][2 * rI + 1] = v1;
+                    rmax[rI] = fmaxf(rmax[rI], fmaxf(v0, v1));
+                }
         } else
 #pragma unroll
         for (int nt = 0; nt < 2; nt++)
@@ -657,11 +673,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
                 float val = s[nt][e] * a.scale;
                 if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
                 const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + row_iq[rI]);
-                if (row_mask[rI] && valid) {
-                    const __half mh = stage_mask ? sMask[(((tile - tile_lo) % NS) * R + g + rI * 8) * kDecBN + (ik - k0)]
-                                                 : *reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2);
-                    val += row_slope[rI] * __half2float(mh);
-                }
+                if (row_mask[rI] && valid)
+                    val += row_slope[rI] * __half2float(*reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2));
                 val = valid ? val * kLog2e : ninf;
                 s[nt][e] = val;
                 rmax[rI] = fmaxf(rmax[rI], val);
@@ -1180,10 +1193,11 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     if (MODE == kDecAsyncQ8) smem += (size_t)NS * 2 * kDecBN * (HD / 32 * 34);
     // the attribute is raised once, to the largest size this instantiation can ask for (mask staging for 16 rows)
     const size_t smem_attr = smem + (MODE == kDecAsyncF16 ? (size_t)NS * kDecRows * kDecBN * sizeof(__half) : 0);
-    if (MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16) smem += (size_t)NS * (a.Tq * a.gqa) * kDecBN * sizeof(__half);
+    const bool staged_mask = MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16 && a.softcap == 0.0f && !a.causal && a.n2 == 0;
+    if (staged_mask) smem += (size_t)NS * (a.Tq * a.gqa) * kDecBN * sizeof(__half);
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
-    if (MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16) {
+    if (staged_mask) {
         auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem_attr, smem_set);
