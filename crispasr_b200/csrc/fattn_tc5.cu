@@ -383,13 +383,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     // Causal launches hand out the query tiles with the most KV tiles first (longest-processing-time order over
     // the whole grid: the tile index becomes the slowest-varying coordinate, reversed), which shortens the tail of
     // short prefills; otherwise consecutive CTAs are the query tiles of one head, which share K/V in L2.
-    int q0 = blockIdx.x * kTile, h = blockIdx.y, b = blockIdx.z;
+    // GQA packing: the grid runs over KV heads, and a CTA's 128 rows are (query position, head of the group) pairs -
+    // packed row q0 + r is query (q0 + r) / gqa of head hk*gqa + (q0 + r) % gqa.  The heads of a group share their
+    // K/V tiles, and a short causal prefill covers fewer, fuller tiles (gqa = 1: the plain one-head tile).
+    int q0 = blockIdx.x * kTile, hk = blockIdx.y, b = blockIdx.z;
     if (a.causal) {
         const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), hb = gridDim.y * gridDim.z;
         q0 = (gridDim.x - 1 - lin / hb) * kTile;
-        h = (lin % hb) % gridDim.y, b = (lin % hb) / gridDim.y;
+        hk = (lin % hb) % gridDim.y, b = (lin % hb) / gridDim.y;
     }
-    const int hk = h / a.gqa, bk = b / a.bq;
+    const int bk = b / a.bq;
+    const int rows_total = a.Tq * a.gqa;   // packed rows of this (kv head, batch entry)
 
     int len_b = a.Lk;
     if (a.kv_len) {
@@ -397,12 +401,13 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         len_b = v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
     }
     int kmax = len_b;
-    if (a.causal) kmax = min(kmax, a.n_past + min(q0 + kTile, a.Tq));
+    if (a.causal) kmax = min(kmax, a.n_past + min((q0 + kTile - 1) / a.gqa + 1, a.Tq));
     const int n_tiles = kmax > 0 ? (kmax + kTile - 1) / kTile : 0;
 
     if (n_tiles == 0) {  // nothing to attend to: zeros
-        if (tid < kTile && q0 + tid < a.Tq) {
-            float4* out = reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + q0 + tid) * a.H + h) * HD);
+        if (tid < kTile && q0 + tid < rows_total) {
+            const int iq = (q0 + tid) / a.gqa, h = hk * a.gqa + (q0 + tid) % a.gqa;
+            float4* out = reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * HD);
 #pragma unroll
             for (int i = 0; i < HD / 4; i++) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -448,9 +453,9 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     if (warp < 4) {
         // Q tile -> shared memory (thread r writes row r)
         const int r = tid;
-        const int iq = q0 + r;
+        const int iq = (q0 + r) / a.gqa, h = hk * a.gqa + (q0 + r) % a.gqa;
         load_q_row<HD>(smem_gen, r, a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.type,
-                       a.q.vec16 != 0, iq < a.Tq);
+                       a.q.vec16 != 0, q0 + r < rows_total);
         fence_proxy_async();
         if (tid == 0) TC5_TRACE(2, 61, 1);
     }
@@ -571,7 +576,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     } else {
         // ================= softmax / correction / epilogue =================
         const int r = tid;
-        const int iq = q0 + r;
+        const bool row_live = q0 + r < rows_total;
+        const int iq = row_live ? (q0 + r) / a.gqa : a.Tq, h = hk * a.gqa + (q0 + r) % a.gqa;   // dead rows: iq = Tq
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         const float c = a.scale * kLog2e;
         int kend = len_b;
@@ -1217,7 +1223,7 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
     const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 32 + 16;
     cudaError_t e;
-    dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
+    dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
     if (a.has_mask) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true>;
         static bool smem_set[64] = {false};
