@@ -167,6 +167,15 @@ def oracle_kwargs(w, extra):
     return kw
 
 
+def host_threads():
+    """Host threads this process may use.  torchrun exports OMP_NUM_THREADS=1, which would turn the CPU arm into a
+    single-thread run: the thread count is passed to the oracle explicitly instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_sample(w, budget_s, steps=None):
     """Times the oracle on one unit, layer after layer, until `budget_s` or all layers; returns
     (units/s for the full layer stack, description, threads)."""
@@ -174,13 +183,14 @@ def cpu_sample(w, budget_s, steps=None):
     rng = np.random.default_rng(w["seed"])
     q, k, v, extra = make_inputs_np(w, 1, rng)
     kw = oracle_kwargs(w, extra)
+    kw["n_threads"] = host_threads()
     t0, done = time.perf_counter(), 0
     while done < w["layers"] and (time.perf_counter() - t0 < budget_s or done == 0):
         orc.flash_attn_ext(q, k, v, **kw)
         done += 1
     dt = time.perf_counter() - t0
     per_layer = dt / done
-    return 1.0 / (per_layer * w["layers"]), f"1 {w['unit_name'][:-1]} x {done} of {w['layers']} layers ({dt:.1f} s)", orc.max_threads()
+    return 1.0 / (per_layer * w["layers"]), f"1 {w['unit_name'][:-1]} x {done} of {w['layers']} layers ({dt:.1f} s)", kw["n_threads"]
 
 
 def run_reference(args, w, rank, world):
@@ -191,6 +201,7 @@ def run_reference(args, w, rank, world):
     rng = np.random.default_rng(w["seed"])
     q, k, v, extra = make_inputs_np(w, 1, rng)
     kw = oracle_kwargs(w, extra)
+    kw["n_threads"] = host_threads()
     layers_per_step = w["layers"] if w["kind"] != "relpos" else 1
     def step():
         for _ in range(layers_per_step):
@@ -208,7 +219,7 @@ def run_reference(args, w, rank, world):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 softmax/accumulate over f16/q8_0 operands",
         "data": "synthetic", "config": config_of(args, w, args.units or w["units"]),
-        "cpu_baseline": {"value": value, "unit": unit, "cores": orc.max_threads(), "kind": "port",
+        "cpu_baseline": {"value": value, "unit": unit, "cores": kw["n_threads"], "kind": "port",
                          "sample": f"1 {w['unit_name'][:-1]} x {layers_per_step} of {w['layers']} layers per step, scaled to the full stack"},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
