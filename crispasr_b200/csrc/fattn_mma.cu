@@ -775,7 +775,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     } else {
         const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
         float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);
+        for (int idx = tid; idx < R * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);   // live rows only: the merge kernel reads no others
         if (tid < kDecRows) {
             a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
             a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
@@ -1096,7 +1096,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     } else {
         const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
         float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < kDecRows * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);
+        for (int idx = tid; idx < R * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);   // live rows only: the merge kernel reads no others
         if (tid < kDecRows) {
             a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
             a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
