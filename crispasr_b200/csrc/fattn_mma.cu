@@ -801,8 +801,11 @@ constexpr int kDecRegStages = 3;
 
 // PLAIN: no explicit mask, no softcap, no causal bound (single-token decode): only kv_len limits the keys.  A separate
 // instantiation, so the common case carries none of the general path's registers and code.
-template <int HD, bool PLAIN>
+// LOW (with PLAIN): at most 8 live rows (Tq * gqa <= 8), so rows g+8 of every fragment are padding and their softmax
+// arithmetic is skipped.
+template <int HD, bool PLAIN, bool LOW = false>
 __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const FattnArgs a) {
+    constexpr int NR = LOW ? 1 : 2, NE = 2 * NR;   // live row halves / accumulator elements per n-tile
     constexpr int NBLK = HD / 32, RB = NBLK * 34;
     constexpr int RAW_BYTES = kDecBN * RB;   // one raw K or V tile
     constexpr int NS = kDecRegStages;
@@ -946,7 +949,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
+                for (int e = 0; e < NE; e++) {
                     s[nt][e] *= c;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
                 }
@@ -955,7 +958,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
+                for (int e = 0; e < NE; e++) {
                     const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
                     s[nt][e] = ik < len_b ? s[nt][e] * c : ninf;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
@@ -979,9 +982,9 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         }
         // Lazy rescale: m_run is a reference, not the exact running maximum - it is only raised (and O, l rescaled)
         // when a row's tile maximum outgrew it by 2^8, so P <= 256 stays inside f16 and most tiles skip the rescale.
-        float alpha[2], muse[2];
+        float alpha[2] = {1.0f, 1.0f}, muse[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int rI = 0; rI < 2; rI++) {
+        for (int rI = 0; rI < NR; rI++) {
             const float mt = quad_max(rmax[rI]);
             const float mnew = (mt > m_run[rI] + 8.0f) ? mt : m_run[rI];   // -inf + 8 = -inf: the first finite maximum is taken
             muse[rI] = mnew == ninf ? 0.0f : mnew;
@@ -993,6 +996,10 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
+                if (e >= NE) {
+                    s[nt][e] = 0.0f;   // padding rows: P = 0
+                    continue;
+                }
                 const float p = fast_ex2(s[nt][e] - muse[e >> 1]);
                 s[nt][e] = p;
                 l_run[e >> 1] += p;
@@ -1247,14 +1254,20 @@ int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
     const size_t smem = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
-    if (!a.has_mask && a.softcap == 0.0f && !a.causal) {
-        auto kern = fattn_decode_q8reg_kernel<HD, true>;
+    if (!a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
+        auto kern = fattn_decode_q8reg_kernel<HD, true, true>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    } else if (!a.has_mask && a.softcap == 0.0f && !a.causal) {
+        auto kern = fattn_decode_q8reg_kernel<HD, true, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
         kern<<<grid, kThreads, smem, st>>>(a);
     } else {
-        auto kern = fattn_decode_q8reg_kernel<HD, false>;
+        auto kern = fattn_decode_q8reg_kernel<HD, false, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
