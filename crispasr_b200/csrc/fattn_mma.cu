@@ -468,8 +468,10 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
 }
 
 // PLAIN: no explicit mask, no softcap, no causal bound: only kv_len limits the keys (its own instantiation).
-template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false>
+// LOW (with STAGE_MASK or PLAIN): at most 8 live rows, so rows g+8 of every fragment are padding and skipped.
+template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false, bool LOW = false>
 __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
+    constexpr int NR = LOW ? 1 : 2, NE = 2 * NR;   // live row halves / accumulator elements per n-tile
     constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
     constexpr int RAW_BYTES = kDecBN * (HD / 32 * 34);    // one raw Q8_0 K or V tile
     constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : kDecQ8Stages);
@@ -633,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
+                for (int e = 0; e < NE; e++) {
                     s[nt][e] *= c;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
                 }
@@ -642,7 +644,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
+                for (int e = 0; e < NE; e++) {
                     const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
                     s[nt][e] = ik < len_b ? s[nt][e] * c : ninf;
                     rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
@@ -654,7 +656,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-                for (int rI = 0; rI < 2; rI++) {
+                for (int rI = 0; rI < NR; rI++) {
                     const int rr = g + rI * 8, ik = k0 + warp * 16 + nt * 8 + 2 * t;
                     float2 m2 = make_float2(0.0f, 0.0f);
                     if (rr < R) m2 = __half22float2(*reinterpret_cast<const __half2*>(mt + rr * kDecBN + nt * 8));
@@ -681,9 +683,9 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             }
         // Lazy rescale: m_run is a reference, not the exact running maximum - it is only raised (and O, l rescaled)
         // when a row's tile maximum outgrew it by 2^8, so P <= 256 stays inside f16 and most tiles skip the rescale.
-        float alpha[2], muse[2];
+        float alpha[2] = {1.0f, 1.0f}, muse[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int rI = 0; rI < 2; rI++) {
+        for (int rI = 0; rI < NR; rI++) {
             const float mt = quad_max(rmax[rI]);
             const float mnew = (mt > m_run[rI] + 8.0f) ? mt : m_run[rI];   // -inf + 8 = -inf: the first finite maximum is taken
             muse[rI] = mnew == ninf ? 0.0f : mnew;
@@ -695,6 +697,10 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         for (int nt = 0; nt < 2; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
+                if (e >= NE) {
+                    s[nt][e] = 0.0f;   // padding rows: P = 0
+                    continue;
+                }
                 const float p = fast_ex2(s[nt][e] - muse[e >> 1]);
                 s[nt][e] = p;
                 l_run[e >> 1] += p;
@@ -1204,10 +1210,23 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     if (staged_mask) smem += (size_t)NS * (a.Tq * a.gqa) * kDecBN * sizeof(__half);
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
-    if (staged_mask) {
+    const bool low = a.Tq * a.gqa <= 8;
+    if (staged_mask && low) {
+        auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16, false, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem_attr, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    } else if (staged_mask) {
         auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem_attr, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, st>>>(a);
+    } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal && low) {
+        auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
         kern<<<grid, kThreads, smem, st>>>(a);
     } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal) {
