@@ -57,9 +57,9 @@ WORKLOADS = {
 # bench scales it to its own launch size.
 NCU_TRAFFIC = {
     "whisper_large_v3_encoder": (120.89e6, 8),
-    "whisper_large_v3_decode_cross": (498.09e6, 64),
-    "whisper_large_v3_decode_self": (761.80e6, 64),
-    "voxtral_decode_q8_0": (307.78e6, 256),
+    "whisper_large_v3_decode_cross": (497.06e6, 64),
+    "whisper_large_v3_decode_self": (760.78e6, 64),
+    "voxtral_decode_q8_0": (310.18e6, 256),
     "parakeet_relpos_encoder": (103.11e6, 1),
     "hd128_prefill_probe": (48.61e6, 1),
 }
