@@ -49,6 +49,16 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Same product with the accumulator rows g+8 in caller-chosen registers: when those rows are padding (all zeros in
+// A and in C) a few shared zero registers stand in for them and the real accumulator needs half the registers.
+__device__ __forceinline__ void mma16816_lo(float& c0, float& c1, float& z0, float& z1, const uint32_t (&a)[4], uint32_t b0,
+                                            uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1)
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 // 2^x on the exponential unit, one instruction (exp2f adds a range fix-up that P in f16 does not need; -inf -> 0).
 __device__ __forceinline__ float fast_ex2(float x) {
     float y;
@@ -902,6 +912,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     float o[HD / 8][4];   // n-tile 4*blk + j, column n <-> dim 32blk + 4n + j
 #pragma unroll
     for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float zpad[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // LOW: stand-ins for the padding rows of O (stay 0)
     const __half2 bias = __float2half2_rn(1152.0f);
     auto cvt2 = [&](uint32_t packed, __half2 d2) {   // {0x64 q1' 0x64 q0'} -> {d*q0, d*q1}
         const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&packed), bias), d2);
@@ -1018,7 +1029,10 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         // the running maxima settle after a few tiles: the accumulator is only rescaled when some row of the warp moved
         if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-            for (int i = 0; i < HD / 8; i++) o[i][0] *= alpha[0], o[i][1] *= alpha[0], o[i][2] *= alpha[1], o[i][3] *= alpha[1];
+            for (int i = 0; i < HD / 8; i++) {
+                o[i][0] *= alpha[0], o[i][1] *= alpha[0];
+                if (!LOW) o[i][2] *= alpha[1], o[i][3] *= alpha[1];
+            }
         }
 
         // ---- O += P.V: keys 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1); this thread's bytes are dims 4g..4g+3 of each block ----
@@ -1044,10 +1058,14 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
             // pair the two keys of an operand register: x = {k0.j, k1.j, k0.j', k1.j'}
             const uint32_t x01a = __byte_perm(w[0], w[1], 0x5140), x01b = __byte_perm(w[0], w[1], 0x7362);
             const uint32_t x23a = __byte_perm(w[2], w[3], 0x5140), x23b = __byte_perm(w[2], w[3], 0x7362);
-            mma16816(o[4 * blk + 0], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x5140), d23));
-            mma16816(o[4 * blk + 1], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x7362), d23));
-            mma16816(o[4 * blk + 2], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x5140), d23));
-            mma16816(o[4 * blk + 3], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x7362), d23));
+            if (LOW) mma16816_lo(o[4 * blk + 0][0], o[4 * blk + 0][1], zpad[0][0], zpad[0][1], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x5140), d23));
+            else mma16816(o[4 * blk + 0], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x5140), d23));
+            if (LOW) mma16816_lo(o[4 * blk + 1][0], o[4 * blk + 1][1], zpad[1][0], zpad[1][1], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x7362), d23));
+            else mma16816(o[4 * blk + 1], pf, cvt2(__byte_perm(x01a, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23a, 0x64646464u, 0x7362), d23));
+            if (LOW) mma16816_lo(o[4 * blk + 2][0], o[4 * blk + 2][1], zpad[2][0], zpad[2][1], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x5140), d23));
+            else mma16816(o[4 * blk + 2], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x5140), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x5140), d23));
+            if (LOW) mma16816_lo(o[4 * blk + 3][0], o[4 * blk + 3][1], zpad[3][0], zpad[3][1], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x7362), d23));
+            else mma16816(o[4 * blk + 3], pf, cvt2(__byte_perm(x01b, 0x64646464u, 0x7362), d01), cvt2(__byte_perm(x23b, 0x64646464u, 0x7362), d23));
         }
         __syncwarp();       // every lane is done with this stage's bytes
         issue(tile + NS);   // the next tile that lives in this stage: NS-1 tiles stay in flight during the arithmetic
