@@ -44,6 +44,8 @@ class Ext(C.Structure):
     _fields_ = [
         ("q_v", C.POINTER(Tensor)),
         ("r", C.POINTER(Tensor)),
+        ("pos_bias_u", C.POINTER(Tensor)),
+        ("pos_bias_v", C.POINTER(Tensor)),
         ("causal", C.c_int32),
         ("n_past", C.c_int32),
         ("kv_len", C.c_void_p),

@@ -197,9 +197,11 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
         a.m1 = powf(2.0f, -(p->max_bias / 2.0f) / (float)a.n2);
     }
     if (ext) {
-        if ((ext->q_v != nullptr) != (ext->r != nullptr)) return B200_E_NULL;
-        if (ext->q_v) {
-            const b200_tensor *qv = ext->q_v, *r = ext->r;
+        const bool fused_bias = ext->pos_bias_u != nullptr || ext->pos_bias_v != nullptr;
+        if (fused_bias && (!ext->pos_bias_u || !ext->pos_bias_v || ext->q_v || !ext->r)) return B200_E_NULL;
+        if (!fused_bias && (ext->q_v != nullptr) != (ext->r != nullptr)) return B200_E_NULL;
+        if (ext->r) {
+            const b200_tensor *qv = fused_bias ? q : ext->q_v, *r = ext->r;
             if ((rc = check_operand(qv, true, true, false))) return rc;
             if ((rc = check_operand(r, true, true, false))) return rc;
             for (int i = 0; i < 4; i++)
@@ -207,6 +209,18 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
             if (Lk != Tq) return B200_E_SHAPE;
             if (r->ne[0] != hd || r->ne[1] != 2 * Tq - 1 || r->ne[2] != H) return B200_E_SHAPE;
             if (r->ne[3] != 1 && r->ne[3] != B) return B200_E_SHAPE;
+            if (fused_bias) {
+                const b200_tensor* bb[2] = {ext->pos_bias_u, ext->pos_bias_v};
+                for (int i = 0; i < 2; i++) {
+                    if (!bb[i]->data) return B200_E_NULL;
+                    if (bb[i]->type != B200_TYPE_F32) return B200_E_TYPE;
+                    if (bb[i]->ne[0] != hd || bb[i]->ne[1] != H || bb[i]->ne[2] != 1 || bb[i]->ne[3] != 1) return B200_E_SHAPE;
+                    if (bb[i]->nb[0] != 4 || bb[i]->nb[1] != (uint64_t)hd * 4) return B200_E_STRIDE;
+                    if (((uintptr_t)bb[i]->data & 3) != 0) return B200_E_ALIGN;
+                }
+                a.bias_u = (const float*)ext->pos_bias_u->data;
+                a.bias_v = (const float*)ext->pos_bias_v->data;
+            }
             a.qv = make_view(qv);
             a.r = make_view(r);
             a.r_ne3 = (int)r->ne[3];
@@ -431,15 +445,17 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     int dev = 0;
     cudaGetDevice(&dev);
 
-    // operands to stage: q, k, v, [mask], [q_v, r], [kv_len]; then dst and workspace
-    const b200_tensor* in[6] = {q, k, v, mask, ext ? ext->q_v : nullptr, ext ? ext->r : nullptr};
-    size_t off[6], total = 0;
+    // operands to stage: q, k, v, [mask], [q_v, r, pos_bias_u, pos_bias_v], [kv_len]; then dst and workspace
+    constexpr int NIN = 8;
+    const b200_tensor* in[NIN] = {q, k, v, mask, ext ? ext->q_v : nullptr, ext ? ext->r : nullptr,
+                                  ext ? ext->pos_bias_u : nullptr, ext ? ext->pos_bias_v : nullptr};
+    size_t off[NIN], total = 0;
     auto bump = [&](size_t n) {
         const size_t o = total;
         total += (n + 255) / 256 * 256;
         return o;
     };
-    for (int i = 0; i < 6; i++) off[i] = in[i] ? bump(span_bytes(in[i])) : 0;
+    for (int i = 0; i < NIN; i++) off[i] = in[i] ? bump(span_bytes(in[i])) : 0;
     const size_t kvlen_off = (ext && ext->kv_len) ? bump((size_t)q->ne[3] * 4) : 0;
     const size_t dst_bytes = (size_t)dst->ne[0] * dst->ne[1] * dst->ne[2] * dst->ne[3] * 4;
     const size_t dst_off = bump(dst_bytes);
@@ -454,7 +470,7 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
         return t->ne[3] == 1 || t->nb[3] >= span_bytes(&one);
     };
     bool chunkable = B >= 2 && k->ne[3] == B;
-    for (int i = 0; i < 6 && chunkable; i++)
+    for (int i = 0; i < NIN && chunkable; i++)
         if (in[i] && in[i]->ne[3] != 1 && (in[i]->ne[3] != B || !batch_outermost(in[i]))) chunkable = false;
     const int n_chunks = chunkable ? (int)(B < 4 ? B : 4) : 1;
     // Workspace of one chunk: a smaller batch may be split over more KV ranges than the whole call would be,
@@ -491,9 +507,9 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     cudaStream_t streams[2] = {ar.stream, ar.stream2};
 
     // operands without a batch dimension (ne[3] == 1) are copied once, ahead of everything, on stream 0
-    b200_tensor dt[6];
+    b200_tensor dt[NIN];
     cudaEvent_t shared_ready = nullptr;
-    for (int i = 0; i < 6; i++) {
+    for (int i = 0; i < NIN; i++) {
         if (!in[i]) continue;
         dt[i] = *in[i];
         dt[i].data = ar.base + off[i];
@@ -518,8 +534,8 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     for (int c = 0; c < n_chunks && rc_chunks == B200_OK; c++) {
         const int64_t b0 = B * c / n_chunks, b1 = B * (c + 1) / n_chunks, nb = b1 - b0;
         cudaStream_t st = streams[c & 1];
-        b200_tensor ct[6];
-        for (int i = 0; i < 6; i++) {
+        b200_tensor ct[NIN];
+        for (int i = 0; i < NIN; i++) {
             if (!in[i]) continue;
             ct[i] = dt[i];
             if (n_chunks > 1 && in[i]->ne[3] != 1) {
@@ -538,6 +554,8 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
             dext = *ext;
             dext.q_v = ext->q_v ? &ct[4] : nullptr;
             dext.r = ext->r ? &ct[5] : nullptr;
+            dext.pos_bias_u = ext->pos_bias_u ? &ct[6] : nullptr;
+            dext.pos_bias_v = ext->pos_bias_v ? &ct[7] : nullptr;
             dext.kv_len = ext->kv_len ? (const int32_t*)(ar.base + kvlen_off) + b0 : nullptr;
         }
         b200_tensor cdst = *dst;

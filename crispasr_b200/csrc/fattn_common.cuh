@@ -31,6 +31,8 @@ struct FattnArgs {
     int32_t causal, n_past;
     const int32_t* kv_len;
     int32_t relpos, relpos_f32;
+    const float* bias_u;  // [hd, H] fp32 added to Q on load (content scores); nullptr = off
+    const float* bias_v;  // the same for the Q of the relative-position bias
     // split-KV
     int32_t n_splits;
     float* ws_o;   // [B][Hkv][n_splits][16][hd]
@@ -51,6 +53,42 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Eight Q elements [c0, c0+8) of one row plus eight fp32 bias values, as packed f16: the sum is formed in fp32
+// and rounded once (an F32 add followed by the conversion to F16). F16 and F32 rows only; c0 + 8 <= head_dim.
+__device__ __forceinline__ uint4 load8_plus_bias_as_half(const uint8_t* rowp, int type, int c0, bool vec16,
+                                                         const float* bias8) {
+    float f[8];
+    if (type == B200_TYPE_F16) {
+        uint32_t w[4];
+        if (vec16) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(rowp + 2 * c0));
+            w[0] = u.x, w[1] = u.y, w[2] = u.z, w[3] = u.w;
+        } else {
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(rowp + 2 * c0);
+#pragma unroll
+            for (int i = 0; i < 4; i++) w[i] = h[2 * i] | ((uint32_t)h[2 * i + 1] << 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = p.x, f[2 * i + 1] = p.y;
+        }
+    } else if (vec16) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(rowp + 4 * c0));
+        const float4 y = __ldg(reinterpret_cast<const float4*>(rowp + 4 * c0 + 16));
+        f[0] = x.x, f[1] = x.y, f[2] = x.z, f[3] = x.w, f[4] = y.x, f[5] = y.y, f[6] = y.z, f[7] = y.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] = *reinterpret_cast<const float*>(rowp + 4 * (c0 + i));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) f[i] = __fadd_rn(f[i], __ldg(bias8 + i));
+    uint4 out;
+    out.x = pack_half2(f[0], f[1]), out.y = pack_half2(f[2], f[3]);
+    out.z = pack_half2(f[4], f[5]), out.w = pack_half2(f[6], f[7]);
+    return out;
 }
 
 // Raises a kernel's dynamic shared memory limit once per (kernel instantiation, device): the attribute call is

@@ -126,6 +126,39 @@ __device__ __forceinline__ void load_tile(__half* sm, const uint8_t* base, int64
     }
 }
 
+// The same for a Q tile with an fp32 bias row [hd] added before the rounding to fp16 (F16 / F32 rows).
+template <int HD, int NROWS>
+__device__ __forceinline__ void load_tile_bias(__half* sm, const uint8_t* base, int64_t nb1, int type, bool vec16,
+                                               int row0, int row_hi, int hd, const float* bias, int tid) {
+    constexpr int CPR = HD / 8;
+    for (int idx = tid; idx < NROWS * CPR; idx += kThreads) {
+        const int row = idx / CPR, ch = idx % CPR, c0 = ch * 8;
+        const int grow = row0 + row;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (grow < row_hi && c0 < hd) {
+            const uint8_t* rowp = base + (int64_t)grow * nb1;
+            if (c0 + 8 <= hd) {
+                val = load8_plus_bias_as_half(rowp, type, c0, vec16, bias + c0);
+            } else {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    f[i] = 0.0f;
+                    if (c0 + i < hd) {
+                        const float x = type == B200_TYPE_F16
+                                            ? __half2float(*reinterpret_cast<const __half*>(rowp + 2 * (c0 + i)))
+                                            : *reinterpret_cast<const float*>(rowp + 4 * (c0 + i));
+                        f[i] = __fadd_rn(x, __ldg(bias + c0 + i));
+                    }
+                }
+                val.x = pack_half2(f[0], f[1]), val.y = pack_half2(f[2], f[3]);
+                val.z = pack_half2(f[4], f[5]), val.w = pack_half2(f[6], f[7]);
+            }
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * CPR + swz<HD>(row, ch)) * 16) = val;
+    }
+}
+
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -164,11 +197,18 @@ __global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArg
     const int hk = h / a.gqa, bk = b / a.bq;
     const float ninf = -INFINITY;
 
-    load_tile<HD, BM>(sQ, a.q.p + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.nb1, a.q.type, a.q.vec16, q0, 0,
-                      a.Tq, a.hd, tid);
-    if (RELPOS)
-        load_tile<HD, BM>(sQv, a.qv.p + (int64_t)h * a.qv.nb2 + (int64_t)b * a.qv.nb3, a.qv.nb1, a.qv.type,
-                          a.qv.vec16, q0, 0, a.Tq, a.hd, tid);
+    if (RELPOS && a.bias_u != nullptr) {
+        // untied position biases folded into the load: Q_u = Q + bias_u, Q_v = Q + bias_v (q_v aliases q)
+        const uint8_t* qb = a.q.p + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3;
+        load_tile_bias<HD, BM>(sQ, qb, a.q.nb1, a.q.type, a.q.vec16, q0, a.Tq, a.hd, a.bias_u + (int64_t)h * a.hd, tid);
+        load_tile_bias<HD, BM>(sQv, qb, a.q.nb1, a.q.type, a.q.vec16, q0, a.Tq, a.hd, a.bias_v + (int64_t)h * a.hd, tid);
+    } else {
+        load_tile<HD, BM>(sQ, a.q.p + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.nb1, a.q.type, a.q.vec16, q0, 0,
+                          a.Tq, a.hd, tid);
+        if (RELPOS)
+            load_tile<HD, BM>(sQv, a.qv.p + (int64_t)h * a.qv.nb2 + (int64_t)b * a.qv.nb3, a.qv.nb1, a.qv.type,
+                              a.qv.vec16, q0, 0, a.Tq, a.hd, tid);
+    }
 
     const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
     const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;

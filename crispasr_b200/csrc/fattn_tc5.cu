@@ -832,10 +832,20 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         for (int which = 0; which < 2; which++) {
             const View& qv = which ? a.qv : a.q;
             const uint8_t* rowp = qv.p + (int64_t)iq * qv.nb1 + (int64_t)h * qv.nb2 + (int64_t)b * qv.nb3;
+            const float* bias = which ? a.bias_v : a.bias_u;  // untied position biases folded into the load
             uint4 v[HD / 16];
+            if (bias != nullptr) {
 #pragma unroll
-            for (int c = 0; c < HD / 16; c++)
-                v[c] = (iq < a.Tq) ? q_chunk(rowp, qv.type, (ch * (HD / 16) + c) * 8, qv.vec16 != 0) : make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < HD / 16; c++) {
+                    const int c0 = (ch * (HD / 16) + c) * 8;
+                    v[c] = (iq < a.Tq) ? load8_plus_bias_as_half(rowp, qv.type, c0, qv.vec16 != 0, bias + h * HD + c0)
+                                       : make_uint4(0u, 0u, 0u, 0u);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < HD / 16; c++)
+                    v[c] = (iq < a.Tq) ? q_chunk(rowp, qv.type, (ch * (HD / 16) + c) * 8, qv.vec16 != 0) : make_uint4(0u, 0u, 0u, 0u);
+            }
 #pragma unroll
             for (int c = 0; c < HD / 16; c++) {
                 const int cc = ch * (HD / 16) + c;

@@ -26,15 +26,24 @@ class _Call:
     """Descriptors of one op call; keeps every ctypes object alive for the duration of the call."""
 
     def __init__(self, q, k, v, mask, dst, scale, max_bias, softcap, kv_type, causal, n_past, kv_len, q_v, r,
-                 relpos_bias_f32, conv):
+                 relpos_bias_f32, conv, pos_bias_u=None, pos_bias_v=None):
         self.q, self.k, self.v = conv(q), conv(k, kv_type), conv(v, kv_type)
         self.mask = conv(mask) if mask is not None else None
         self.dst = conv(dst)
         self.params = abi.Params(float(scale), float(max_bias), float(softcap), 0)
         self.ext = abi.Ext()
         if q_v is not None:
-            self.qv, self.r = conv(q_v), conv(r)
-            self.ext.q_v, self.ext.r = C.pointer(self.qv), C.pointer(self.r)
+            self.qv = conv(q_v)
+            self.ext.q_v = C.pointer(self.qv)
+        if r is not None:
+            self.r = conv(r)
+            self.ext.r = C.pointer(self.r)
+        if pos_bias_u is not None:  # (H, hd) f32: Q_u = Q + pos_bias_u formed inside the op
+            self.bu = conv(pos_bias_u)
+            self.ext.pos_bias_u = C.pointer(self.bu)
+        if pos_bias_v is not None:
+            self.bv = conv(pos_bias_v)
+            self.ext.pos_bias_v = C.pointer(self.bv)
         self.ext.causal, self.ext.n_past = int(bool(causal)), int(n_past)
         self.kv_len = kv_len
         if kv_len is not None:
@@ -56,7 +65,7 @@ def _dst_like(q, device=None):
 def _make(q, k, v, mask, dst, kw, conv):
     return _Call(q, k, v, mask, dst, kw["scale"], kw.get("max_bias", 0.0), kw.get("softcap", 0.0),
                  kw.get("kv_type"), kw.get("causal", False), kw.get("n_past", 0), kw.get("kv_len"), kw.get("q_v"),
-                 kw.get("r"), kw.get("relpos_bias_f32", False), conv)
+                 kw.get("r"), kw.get("relpos_bias_f32", False), conv, kw.get("pos_bias_u"), kw.get("pos_bias_v"))
 
 
 def supports(q, k, v, mask=None, **kw) -> bool:

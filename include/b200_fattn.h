@@ -78,9 +78,17 @@ typedef struct b200_fattn_ext {
      * src/core/fastconformer.h:880-918 builds (MUL_MAT(R,Q_v) -> rel_shift -> scale -> cast F16):
      *   bias[k,q,h] = f16( scale * sum_c q_v[c,q,h] * r[c, (Tq-1) + k - q, h] )
      * q_v has the shape and type rules of Q; r is [hd, 2*Tq-1, H, 1|B] F16 or F32. Requires
-     * Lk == Tq. May be combined with `mask` (added after the bias) and kv_len. */
+     * Lk == Tq and either q_v or the two position biases below. May be combined with `mask` (added after the bias) and kv_len. */
     const b200_tensor* q_v;
     const b200_tensor* r;
+    /* Untied position biases folded into the Q load, replacing the two ggml_add passes of
+     * src/core/fastconformer.h:846-847 (Q_u = Q + pos_bias_u, Q_v = Q + pos_bias_v): both are F32
+     * [hd, H] contiguous. Given together with `r` and a NULL q_v, the op reads Q once and uses
+     * f16(Q + pos_bias_u) for the content scores and f16(Q + pos_bias_v) for the bias (the sums are
+     * formed in fp32 and rounded once, as the reference's F32 add followed by the op's F16 conversion).
+     * With a non-NULL q_v they must be NULL. */
+    const b200_tensor* pos_bias_u;
+    const b200_tensor* pos_bias_v;
     /* Implicit causal mask of src/voxtral.cpp:1187-1194: key k is masked iff k > n_past + q. */
     int32_t causal;
     int32_t n_past;

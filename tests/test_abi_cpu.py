@@ -74,6 +74,15 @@ def test_validator_codes(b200):
     r = _desc((1, 8, 39, 64))
     assert _supports(b200, qq, k, k, q_v=qq, r=r)[0]
     assert _supports(b200, q, k, k, q_v=q, r=r)[1] == abi.E_SHAPE
+    # position biases folded into the Q load: both, F32 [hd, H], with r and without q_v
+    bu = _desc((8, 64), torch.float32)
+    kk = _desc((1, 8, 20, 64))
+    assert _supports(b200, qq, kk, kk, r=r, pos_bias_u=bu, pos_bias_v=bu) == (True, 0)
+    assert _supports(b200, qq, kk, kk, r=r, pos_bias_u=bu)[1] == abi.E_NULL
+    assert _supports(b200, qq, kk, kk, q_v=qq, r=r, pos_bias_u=bu, pos_bias_v=bu)[1] == abi.E_NULL
+    assert _supports(b200, qq, kk, kk, pos_bias_u=bu, pos_bias_v=bu)[1] == abi.E_NULL        # no r
+    assert _supports(b200, qq, kk, kk, r=r, pos_bias_u=bu, pos_bias_v=_desc((8, 64)))[1] == abi.E_TYPE
+    assert _supports(b200, qq, kk, kk, r=r, pos_bias_u=bu, pos_bias_v=_desc((4, 64), torch.float32))[1] == abi.E_SHAPE
     assert b200.lib().b200_fattn_supports(None, None, None, None, None, None, None, None) == 0
     assert b"NULL" in b200.lib().b200_strerror(abi.E_NULL)
 

@@ -276,6 +276,53 @@ def test_cfg5_relpos_with_padding_mask(b200, orc, kernel):
     assert_close(got2[:, :valid], ref[:, :valid], "cfg5 fused + kv_len")
 
 
+@pytest.mark.parametrize("T,hd,H", [(200, 128, 8), (611, 128, 8), (150, 64, 4), (97, 80, 4)])
+@pytest.mark.parametrize("qdtype", [np.float32, np.float16])
+def test_cfg5_position_biases_folded_into_q_load(b200, orc, kernel, T, hd, H, qdtype):
+    """Q_u = Q + pos_bias_u and Q_v = Q + pos_bias_v (src/core/fastconformer.h:846-847) formed inside the op
+    from one Q: the oracle gets the sums formed ahead of the call in fp32, as the reference's two adds do.
+    Q, K and V are views into one fused (T, 3d) projection result, as src/core/fastconformer.h:830-838 builds them."""
+    import torch
+    rng = np.random.default_rng(46)
+    d = H * hd
+    qkv = rng.standard_normal((T, 3 * d)).astype(np.float32)
+    if qdtype == np.float16:
+        qkv = qkv.astype(np.float16).astype(np.float32)
+    u = (rng.standard_normal((H, hd)) * 0.3).astype(np.float32)
+    vb = (rng.standard_normal((H, hd)) * 0.3).astype(np.float32)
+    pe = orc.make_pos_enc(d, T)
+    w = (rng.standard_normal((d, d)) / np.sqrt(d)).astype(np.float32)
+    r = np.ascontiguousarray((pe @ w).reshape(2 * T - 1, H, hd).transpose(1, 0, 2)[None]).astype(np.float16)
+
+    def heads(x):                                        # (T, d) -> (1, H, T, hd)
+        return x.reshape(T, H, hd).transpose(1, 0, 2)[None]
+
+    q, k, v = heads(qkv[:, :d]), heads(qkv[:, d:2 * d]), heads(qkv[:, 2 * d:])
+    scale = hd ** -0.5
+    ref = orc.flash_attn_ext(q + u[None, :, None], k, v, scale=scale, q_v=q + vb[None, :, None], r=r)
+
+    dev = torch.from_numpy(qkv).cuda()
+    if qdtype == np.float16:
+        dev = dev.half()
+
+    def dheads(x):
+        return x.reshape(T, H, hd).permute(1, 0, 2)[None]  # strided view, no copy
+
+    dq, dk, dv = dheads(dev[:, :d]), dheads(dev[:, d:2 * d]), dheads(dev[:, 2 * d:])
+    got = gpu_op(b200, dq, dk, dv, scale=scale, r=r, pos_bias_u=u, pos_bias_v=vb)
+    assert_close(got, ref, f"cfg5 folded biases T={T} hd={hd} {np.dtype(qdtype).name}")
+    # identical to the two-tensor form when that form is fed the same rounded sums
+    q_u = torch.from_numpy(np.ascontiguousarray(q + u[None, :, None])).cuda()
+    q_v = torch.from_numpy(np.ascontiguousarray(q + vb[None, :, None])).cuda()
+    two = gpu_op(b200, q_u, dk, dv, scale=scale, q_v=q_v, r=r)
+    assert np.array_equal(got, two)
+    if T == 200:   # the same call with host buffers (bias rows are staged with the other operands)
+        hq, hk, hv = (x.cpu() for x in (dq, dk, dv))
+        host = b200.flash_attn_ext_host(hq, hk, hv, scale=scale, r=torch.from_numpy(r), pos_bias_u=torch.from_numpy(u),
+                                        pos_bias_v=torch.from_numpy(vb)).numpy()
+        assert np.array_equal(host, got)
+
+
 # ---- golden fixtures and edge cases ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("name", ["enc64", "gqa128_causal", "perhead_mask", "decode1", "beams5"])
 def test_golden_sdpa_fixtures(b200, kernel, name):

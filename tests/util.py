@@ -71,7 +71,7 @@ def gpu_op(b200, q, k, v, mask=None, **kw):
         return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
     kw = dict(kw)
-    for name in ("q_v", "r"):
+    for name in ("q_v", "r", "pos_bias_u", "pos_bias_v"):
         if kw.get(name) is not None:
             kw[name] = dev(kw[name])
     if kw.get("kv_len") is not None:
