@@ -3,6 +3,7 @@
 // sizing, launch, and the host-buffer round trip.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -472,7 +473,12 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     bool chunkable = B >= 2 && k->ne[3] == B;
     for (int i = 0; i < NIN && chunkable; i++)
         if (in[i] && in[i]->ne[3] != 1 && (in[i]->ne[3] != B || !batch_outermost(in[i]))) chunkable = false;
-    const int n_chunks = chunkable ? (int)(B < 4 ? B : 4) : 1;
+    static const int max_chunks = [] {  // B200_HOST_CHUNKS=1..16 overrides the default pipeline depth
+        const char* e = getenv("B200_HOST_CHUNKS");
+        const int n = e ? atoi(e) : 0;
+        return n >= 1 && n <= 16 ? n : 4;
+    }();
+    const int n_chunks = chunkable ? (int)(B < max_chunks ? B : max_chunks) : 1;
     // Workspace of one chunk: a smaller batch may be split over more KV ranges than the whole call would be,
     // so the split-decode workspace is sized for the chunk batches, not taken from the full plan.
     size_t ws_need = plan.ws_bytes;
