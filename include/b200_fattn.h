@@ -184,8 +184,9 @@ B200_API int b200_fattn_launch(const b200_tensor* q, const b200_tensor* k, const
  * device arena that grows on demand, copied in, computed and copied back, and
  * the call returns after the result is in `dst->data`.  Batch entries (ne[3]) are
  * independent, so the call is pipelined over up to four chunks of the batch on two
- * streams: the upload of one chunk overlaps the kernel and the download of the
- * previous one.  Pinned host buffers are needed for that overlap to happen.
+ * streams (environment variable B200_HOST_CHUNKS = 1..16 changes the depth): the
+ * upload of one chunk overlaps the kernel and the download of the previous one.
+ * Pinned host buffers are needed for that overlap to happen.
  */
 B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
                                      const b200_tensor* mask, const b200_tensor* dst,
