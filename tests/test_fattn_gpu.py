@@ -350,6 +350,74 @@ def test_ragged_shapes(b200, orc, kernel, Tq, Lk, hd, H, Hkv):
     assert_close(gpu_op(b200, q, k, v, scale=hd ** -0.5), ref, f"Tq={Tq} Lk={Lk} hd={hd}")
 
 
+def _random_case(orc, seed):
+    """One seeded draw over the op's operand forms; every query row keeps key 0 visible."""
+    rng = np.random.default_rng(9000 + seed)
+    hd = int(rng.choice([32, 64, 80, 128]))
+    kv_kind = str(rng.choice(["f16", "f32", "q8_0"])) if hd % 32 == 0 else str(rng.choice(["f16", "f32"]))
+    gqa = int(rng.choice([1, 2, 4]))
+    Hkv = int(rng.choice([1, 2, 3]))
+    H = Hkv * gqa
+    B = int(rng.choice([1, 2, 3]))
+    Tq = int(rng.choice([1, 1, 2, 5, 17, 64, 130, 257]))
+    Lk = int(rng.integers(Tq, 700)) if rng.random() < 0.5 else int(rng.choice([Tq, 64, 128, 129, 512]))
+    Lk = max(Lk, Tq)
+    Bk = B if rng.random() < 0.8 else 1
+    q = rng.standard_normal((B, H, Tq, hd)).astype(np.float32)
+    if rng.random() < 0.5:
+        q = q.astype(np.float16)
+    x_k = rng.standard_normal((Bk, Hkv, Lk, hd)).astype(np.float32)
+    x_v = rng.standard_normal((Bk, Hkv, Lk, hd)).astype(np.float32)
+    kw = dict(scale=float(hd ** -0.5 * rng.choice([1.0, 0.5, 2.0])))
+    if kv_kind == "q8_0":
+        k, v = orc.quantize_q8_0(x_k), orc.quantize_q8_0(x_v)
+        kw["kv_type"] = abi.Q8_0
+    elif kv_kind == "f16":
+        k, v = x_k.astype(np.float16), x_v.astype(np.float16)
+    else:
+        k, v = x_k, x_v
+    mask = None
+    form = str(rng.choice(["none", "mask", "causal", "kv_len", "mask+kv_len"]))
+    if "mask" in form:
+        Hm, Bm = int(rng.choice([1, H])), int(rng.choice([1, B]))
+        m = np.where(rng.random((Bm, Hm, Tq, Lk)) < 0.35, -np.inf, 0.0)
+        if rng.random() < 0.5:   # finite additive biases as well as -inf
+            m = m + np.where(np.isfinite(m), rng.standard_normal(m.shape) * 0.5, 0.0)
+        m[..., 0] = 0.0
+        mask = m.astype(np.float16)
+    if form == "causal":
+        kw.update(causal=True, n_past=Lk - Tq)
+    if "kv_len" in form:
+        kw["kv_len"] = [int(rng.integers(1, Lk + 1)) for _ in range(B)]
+    if rng.random() < 0.25:
+        kw["softcap"] = float(rng.choice([5.0, 30.0]))
+    if mask is not None and rng.random() < 0.3:
+        kw["max_bias"] = 8.0
+    desc = f"seed {seed}: hd {hd} {kv_kind} q {q.dtype.name} B {B}/{Bk} H {H}/{Hkv} Tq {Tq} Lk {Lk} {form} {sorted(kw)}"
+    return q, k, v, mask, kw, desc
+
+
+@pytest.mark.parametrize("seed", range(96))
+def test_random_operand_forms(b200, orc, seed):
+    """Seeded sweep over head dims, GQA ratios, batch broadcast, K/V types, mask shapes, causal bound, device
+    kv_len, softcap and ALiBi, with the automatic kernel choice and with the general tile kernel forced."""
+    import torch
+    q, k, v, mask, kw, desc = _random_case(orc, seed)
+    ref = orc.flash_attn_ext(q.astype(np.float32), k, v, mask, **kw)
+    dk, dv = k, v
+    if seed % 2:   # token-major cache rows (Bk, Lk, Hkv, row) read through a head-major strided view
+        dk = torch.from_numpy(np.ascontiguousarray(k.transpose(0, 2, 1, 3))).cuda().permute(0, 2, 1, 3)
+        dv = torch.from_numpy(np.ascontiguousarray(v.transpose(0, 2, 1, 3))).cuda().permute(0, 2, 1, 3)
+        desc += " token-major K/V"
+    for kern in (abi.KERNEL_NONE, abi.KERNEL_TILE_MMA):
+        assert b200.lib().b200_set_kernel_override(kern) == 0
+        try:
+            got = gpu_op(b200, q, dk, dv, mask, **kw)
+        finally:
+            b200.lib().b200_set_kernel_override(abi.KERNEL_NONE)
+        assert_close(got, ref, f"{desc} override {kern}")
+
+
 def test_f32_kv_softcap_alibi(b200, orc, kernel):
     rng = np.random.default_rng(8)
     q = randn_f16(rng, (1, 6, 70, 64)).astype(np.float32)
