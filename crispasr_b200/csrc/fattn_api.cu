@@ -268,7 +268,7 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     a.n_splits = 1;
     plan->ws_bytes = 2 * plan->cast_each + plan->cast_r_bytes;
     if (kernel == B200_KERNEL_DECODE_SPLIT) {
-        a.n_splits = decode_split_choose(a.B, a.Hkv, a.Lk, sm_count);
+        a.n_splits = decode_split_choose(a.B, a.Hkv, a.Lk, sm_count, decode_cluster_merge_ok(a));
         plan->ws_bytes = decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
     }
     return B200_OK;
@@ -485,7 +485,7 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     if (plan.kernel == B200_KERNEL_DECODE_SPLIT) {
         for (int c = 0; c < n_chunks; c++) {
             const int nb = (int)(B * (c + 1) / n_chunks - B * c / n_chunks);
-            const int ns = decode_split_choose(nb, plan.args.Hkv, plan.args.Lk, di.sm_count);
+            const int ns = decode_split_choose(nb, plan.args.Hkv, plan.args.Lk, di.sm_count, decode_cluster_merge_ok(plan.args));
             const size_t w = decode_split_ws_bytes(nb, plan.args.Hkv, ns, plan.args.hd);
             if (w > ws_need) ws_need = w;
         }

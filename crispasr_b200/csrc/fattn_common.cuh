@@ -31,6 +31,7 @@ struct FattnArgs {
     int32_t causal, n_past;
     const int32_t* kv_len;
     int32_t relpos, relpos_f32;
+    int32_t cluster_merge;  // split-KV: the splits of one (batch, kv-head) form a thread-block cluster and merge through distributed shared memory
     const float* bias_u;  // [hd, H] fp32 added to Q on load (content scores); nullptr = off
     const float* bias_v;  // the same for the Q of the relative-position bias
     // split-KV
@@ -113,6 +114,8 @@ int launch_kv_to_f16(const View& src, void* dst, int hd, int Lk, int Hkv, int Bk
 // K and V of one call in one launch.
 int launch_kv_pair_to_f16(const View& k, void* kdst, const View& v, void* vdst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st);
 size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd);
-int decode_split_choose(int B, int Hkv, int Lk, int sm_count);
+// cluster_merge_ok: the launch can use the in-cluster merge (Q8_0 cache, head_dim 64 / 128), which caps the split count at 8.
+int decode_split_choose(int B, int Hkv, int Lk, int sm_count, bool cluster_merge_ok);
+bool decode_cluster_merge_ok(const FattnArgs& a);
 
 }  // namespace b200

@@ -13,6 +13,7 @@
 //    GQA, beams sharing a cross-attention cache): one (split, kv-head, batch) per CTA streams its
 //    share of the keys once, the four warps own 16-key slices of each tile, and partial
 //    (O, m, l) go to the workspace; fattn_merge_kernel combines splits with a log-sum-exp merge.
+#include <cstdlib>
 #include "fattn_common.cuh"
 
 namespace b200 {
@@ -519,6 +520,57 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
 
 // PLAIN: no explicit mask, no softcap, no causal bound: only kv_len limits the keys (its own instantiation).
 // LOW (with STAGE_MASK or PLAIN): at most 8 live rows, so rows g+8 of every fragment are padding and skipped.
+// ---- split merge inside a thread-block cluster ------------------------------------------------------------------
+// When the splits of one (batch entry, kv-head) are launched as one cluster (n_splits <= 8), no workspace and no
+// merge kernel are needed: every CTA leaves its partial (O scaled to its own row maxima, m, l) in its shared
+// memory, the cluster meets at its hardware barrier, and each CTA finishes a slice of the output rows by reading
+// all peers' partials through distributed shared memory.  A second barrier keeps every CTA's shared memory alive
+// until its peers are done reading.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* p, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+// `part` is this CTA's merged partial [16][HD + 4]; s_M / s_L its row maxima and sums.
+template <int HD>
+__device__ __forceinline__ void cluster_merge_store(const FattnArgs& a, const float* part, const float* s_M, const float* s_L,
+                                                    int R, int b, int hk, int split, int tid) {
+    constexpr int STRIDE = HD + 4;
+    cluster_sync_all();
+    const int n = a.n_splits;
+    for (int idx = split * kThreads + tid; idx < R * HD; idx += n * kThreads) {
+        const int rr = idx / HD, c = idx % HD;
+        if (c >= a.hd) continue;
+        float m[8], l[8], o[8];
+        float M = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            m[s] = -INFINITY, l[s] = 0.0f, o[s] = 0.0f;
+            if (s < n) {
+                m[s] = ld_peer_f32(s_M + rr, s);
+                l[s] = ld_peer_f32(s_L + rr, s);
+                o[s] = ld_peer_f32(part + rr * STRIDE + c, s);
+            }
+            M = fmaxf(M, m[s]);
+        }
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            const float w = m[s] == -INFINITY ? 0.0f : exp2f(m[s] - M);
+            L = fmaf(w, l[s], L), acc = fmaf(w, o[s], acc);
+        }
+        const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+        a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? acc / L : 0.0f;
+    }
+    cluster_sync_all();
+}
+
 template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false, bool LOW = false>
 __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int NR = LOW ? 1 : 2, NE = 2 * NR;   // live row halves / accumulator elements per n-tile
@@ -828,6 +880,12 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             const float L = s_L[rr];
             a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? merged(rr, c) / L : 0.0f;
         }
+    } else if (a.cluster_merge) {
+        for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
+            const int rr = idx / HD, c = idx % HD;
+            slab[rr * SLAB_STRIDE + c] = merged(rr, c);
+        }
+        cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
     } else {
         const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
         float* wo = a.ws_o + unit * kDecRows * HD;
@@ -1164,6 +1222,12 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
             const float L = s_L[rr];
             a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? merged(rr, c) / L : 0.0f;
         }
+    } else if (a.cluster_merge) {
+        for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
+            const int rr = idx / HD, c = idx % HD;
+            slab[rr * SLAB_STRIDE + c] = merged(rr, c);
+        }
+        cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
     } else {
         const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
         float* wo = a.ws_o + unit * kDecRows * HD;
@@ -1255,6 +1319,46 @@ cudaError_t launch_merge(const FattnArgs& a, cudaStream_t st) {
     return cudaLaunchKernelEx(&cfg, fattn_merge_kernel<HD>, a);
 }
 
+// The splits of one (batch entry, kv-head) of the Q8_0 register kernel run as one thread-block cluster when there
+// are at most 8 of them (the portable cluster size): they merge through distributed shared memory and the merge
+// kernel is not launched.  (Measured on the F16 kernel, whose CTAs hold 100 KB of shared memory, the cluster form
+// was 3-6 % slower than workspace + merge kernel, so that kernel keeps the latter.)
+// B200_DECODE_CLUSTER_MERGE=0 keeps the workspace + merge-kernel form everywhere.
+bool cluster_merge_enabled() {
+    static const bool enabled = [] {
+        const char* e = getenv("B200_DECODE_CLUSTER_MERGE");
+        return !(e && e[0] == '0');
+    }();
+    return enabled;
+}
+
+bool use_cluster_merge(const FattnArgs& a) {
+    // only while the whole grid is resident at once (4 CTAs on each of 148 SMs): with several waves the cluster
+    // barriers hold finished CTAs on their SMs and the form measured 10 % slower than the merge kernel
+    return decode_cluster_merge_ok(a) && a.n_splits > 1 && a.n_splits <= 8 && (long)a.n_splits * a.Hkv * a.B <= 4L * 148;
+}
+
+template <typename Kern>
+void launch_split(Kern kern, dim3 grid, size_t smem, cudaStream_t st, const FattnArgs& a) {
+    if (!use_cluster_merge(a)) {
+        kern<<<grid, kThreads, smem, st>>>(a);
+        return;
+    }
+    FattnArgs ac = a;
+    ac.cluster_merge = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = grid.x, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, ac);   // errors are picked up by the caller's cudaGetLastError
+}
+
 template <int HD, int MODE>
 int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     constexpr int NS = MODE == kDecSync ? 1 : (MODE == kDecAsyncF16 ? (HD >= 128 ? 3 : 4) : kDecQ8Stages);
@@ -1274,35 +1378,35 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     } else if (staged_mask) {
         auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal && low) {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal) {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     } else {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (a.n_splits > 1) e = launch_merge<HD>(a, st);
+    if (a.n_splits > 1 && !use_cluster_merge(a)) e = launch_merge<HD>(a, st);
     return (int)e;
 }
 
@@ -1336,23 +1440,23 @@ int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     } else if (!a.has_mask && a.softcap == 0.0f && !a.causal) {
         auto kern = fattn_decode_q8reg_kernel<HD, true, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     } else {
         auto kern = fattn_decode_q8reg_kernel<HD, false, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, st>>>(a);
+        launch_split(kern, grid, smem, st, a);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (a.n_splits > 1) e = launch_merge<HD>(a, st);
+    if (a.n_splits > 1 && !use_cluster_merge(a)) e = launch_merge<HD>(a, st);
     return (int)e;
 }
 
@@ -1432,13 +1536,25 @@ size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd) {
 }
 
 // Enough CTAs to put about four on every SM, never more splits than 64-key tiles.
-int decode_split_choose(int B, int Hkv, int Lk, int sm_count) {
+bool decode_cluster_merge_ok(const FattnArgs& a) {
+    return cluster_merge_enabled() && a.k.type == B200_TYPE_Q8_0 && (a.hd == 64 || a.hd == 128);
+}
+
+int decode_split_choose(int B, int Hkv, int Lk, int sm_count, bool cluster_merge_ok) {
     const int tiles = (Lk + kDecBN - 1) / kDecBN;
     const long units = (long)B * Hkv;
-    long want = (4L * sm_count + units - 1) / units;
+    static const int per_sm = [] {  // B200_DECODE_CTAS_PER_SM=1..16: target CTAs per SM of the split grid (default 4)
+        const char* e = getenv("B200_DECODE_CTAS_PER_SM");
+        const int n = e ? atoi(e) : 0;
+        return n >= 1 && n <= 16 ? n : 4;
+    }();
+    long want = ((long)per_sm * sm_count + units - 1) / units;
     if (want < 1) want = 1;
     if (want > tiles) want = tiles;
     if (want > 64) want = 64;
+    if (cluster_merge_ok && want > 8) want = 8;   // one cluster per (batch entry, kv-head)
+    const long tps = (tiles + want - 1) / want;   // tiles per split; drop the splits that would get none
+    want = (tiles + tps - 1) / tps;
     return (int)(want < 1 ? 1 : want);
 }
 
