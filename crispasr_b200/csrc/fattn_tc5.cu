@@ -259,7 +259,12 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
 #pragma unroll
     for (int i = 0; i < 8; i++) mx[i] = -INFINITY;
 #pragma unroll
-    for (int q2 = 0; q2 < 2; q2++)
+    for (int q2 = 0; q2 < 2; q2++) {
+        if (MASKED && col0 + q2 * 32 >= n_valid) {   // a 32-column chunk beyond the last key: P = 0 without the exponentials
+#pragma unroll
+            for (int i = 0; i < 16; i++) preg[q2 * 16 + i] = 0u;
+            continue;
+        }
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
             float s0 = __uint_as_float(sreg[q2][i]), s1 = __uint_as_float(sreg[q2][i + 1]);
@@ -274,6 +279,7 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
             ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
             preg[q2 * 16 + (i >> 1)] = cvt_f16x2(p0, p1);
         }
+    }
     mx_io = max3(mx_io, max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]), max3(fmaxf(mx[4], mx[5]), mx[6], mx[7]));
     float l0, l1;
     unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
