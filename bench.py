@@ -176,6 +176,24 @@ def host_threads():
         return max(1, os.cpu_count() or 1)
 
 
+def gpu_local_cpus(index):
+    """CPUs of the NUMA node the GPU's PCIe slot hangs off (sysfs local_cpulist), restricted to this process's
+    affinity mask; None when the topology cannot be read.  Pinned staging buffers allocated by a thread bound to
+    these CPUs land in the memory next to the GPU, which matters once several ranks copy at the same time."""
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(index)
+        path = f"/sys/bus/pci/devices/{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0/local_cpulist"
+        cpus = set()
+        for part in open(path).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        return cpus or None
+    except Exception:
+        return None
+
+
 def cpu_sample(w, budget_s, steps=None):
     """Times the oracle on one unit, layer after layer, until `budget_s` or all layers; returns
     (units/s for the full layer stack, description, threads)."""
@@ -367,6 +385,10 @@ def main():
     e2e = None
     if not args.no_e2e:
         e2e_units = min(units, 16 if w["kind"] == "prefill" else units)
+        affinity0 = os.sched_getaffinity(0)
+        near_cpus = gpu_local_cpus(dev.index if dev.index is not None else 0)
+        if near_cpus:
+            os.sched_setaffinity(0, near_cpus)   # staging buffers next to the GPU; restored after the measurement
         hq, hk, hv = (x[:e2e_units].contiguous().cpu().pin_memory() for x in (q, k, v))
         hkw = dict(kw)
         if w["kind"] == "relpos":
@@ -394,6 +416,8 @@ def main():
         e2e = {"value": e2e_units * world / dt, "unit": f"{w['unit_name']}/s", "h2d_bytes_per_step": h2d * e2e_layers,
                "d2h_bytes_per_step": int(hout.numel() * 4) * e2e_layers, "units_per_gpu": e2e_units,
                "api": "b200_fattn_forward_host (pinned host buffers, per-layer H2D of Q/K/V and D2H of the output)"}
+        e2e["host_cpus"] = f"{len(near_cpus)} of {len(affinity0)} (NUMA-local to the GPU)" if near_cpus else f"{len(affinity0)} (topology unknown)"
+        os.sched_setaffinity(0, affinity0)
         b200.lib().b200_host_arena_release()
 
     if rank != 0:
