@@ -73,6 +73,7 @@ TP = C.POINTER(Tensor)
 _OP_ARGS = [TP, TP, TP, TP, TP, C.POINTER(Params), C.POINTER(Ext)]
 SYMBOLS = {
     "b200_set_kernel_override": (C.c_int, [C.c_int]),
+    "b200_set_decode_splits": (C.c_int, [C.c_int]),
     "b200_strerror": (C.c_char_p, [C.c_int]),
     "b200_version": (C.c_char_p, []),
     "b200_last_cuda_error": (C.c_char_p, []),

@@ -268,7 +268,7 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     a.n_splits = 1;
     plan->ws_bytes = 2 * plan->cast_each + plan->cast_r_bytes;
     if (kernel == B200_KERNEL_DECODE_SPLIT) {
-        a.n_splits = decode_split_choose(a.B, a.Hkv, a.Lk, sm_count, decode_cluster_merge_ok(a));
+        a.n_splits = decode_split_choose(a, a.B, sm_count);
         plan->ws_bytes = decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
     }
     return B200_OK;
@@ -384,6 +384,12 @@ B200_API int b200_device_status(void) {
     return st ? B200_E_DEVICE_WAIT : B200_OK;
 }
 
+B200_API int b200_set_decode_splits(int n_splits) {
+    if (n_splits < 0 || n_splits > 64) return B200_E_LIMIT;
+    decode_split_force(n_splits);
+    return B200_OK;
+}
+
 B200_API int b200_set_kernel_override(int kernel) {
     if (kernel < B200_KERNEL_NONE || kernel > B200_KERNEL_PREFILL_TC5) return B200_E_SHAPE;
     g_override = kernel;
@@ -484,8 +490,20 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     size_t ws_need = plan.ws_bytes;
     if (plan.kernel == B200_KERNEL_DECODE_SPLIT) {
         for (int c = 0; c < n_chunks; c++) {
-            const int nb = (int)(B * (c + 1) / n_chunks - B * c / n_chunks);
-            const int ns = decode_split_choose(nb, plan.args.Hkv, plan.args.Lk, di.sm_count, decode_cluster_merge_ok(plan.args));
+            const int64_t b0 = B * c / n_chunks;
+            const int nb = (int)(B * (c + 1) / n_chunks - b0);
+            // the split count depends on operand alignment: describe the operands where the chunk will find them
+            // (arena offsets behind a notional 1 MiB-aligned base), not where the host buffers are
+            FattnArgs ca = plan.args;
+            View* views[4] = {&ca.q, &ca.k, &ca.v, &ca.mask};
+            for (int i = 0; i < 4; i++) {
+                if (!in[i]) continue;
+                b200_tensor t = *in[i];
+                t.data = (void*)(uintptr_t)(((size_t)1 << 20) + off[i] +
+                                            (n_chunks > 1 && in[i]->ne[3] != 1 ? (size_t)b0 * in[i]->nb[3] : 0));
+                *views[i] = make_view(&t);
+            }
+            const int ns = decode_split_choose(ca, nb, di.sm_count);
             const size_t w = decode_split_ws_bytes(nb, plan.args.Hkv, ns, plan.args.hd);
             if (w > ws_need) ws_need = w;
         }

@@ -114,8 +114,8 @@ int launch_kv_to_f16(const View& src, void* dst, int hd, int Lk, int Hkv, int Bk
 // K and V of one call in one launch.
 int launch_kv_pair_to_f16(const View& k, void* kdst, const View& v, void* vdst, int hd, int Lk, int Hkv, int Bk, cudaStream_t st);
 size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd);
-// cluster_merge_ok: the launch can use the in-cluster merge (Q8_0 cache, head_dim 64 / 128), which caps the split count at 8.
-int decode_split_choose(int B, int Hkv, int Lk, int sm_count, bool cluster_merge_ok);
+int decode_split_choose(const FattnArgs& a, int B, int sm_count);
+void decode_split_force(int n_splits);  // 0 = automatic
 bool decode_cluster_merge_ok(const FattnArgs& a);
 
 }  // namespace b200

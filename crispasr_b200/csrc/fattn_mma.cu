@@ -1540,22 +1540,61 @@ bool decode_cluster_merge_ok(const FattnArgs& a) {
     return cluster_merge_enabled() && a.k.type == B200_TYPE_Q8_0 && (a.hd == 64 || a.hd == 128);
 }
 
-int decode_split_choose(int B, int Hkv, int Lk, int sm_count, bool cluster_merge_ok) {
-    const int tiles = (Lk + kDecBN - 1) / kDecBN;
-    const long units = (long)B * Hkv;
-    static const int per_sm = [] {  // B200_DECODE_CTAS_PER_SM=1..16: target CTAs per SM of the split grid (default 4)
+// CTAs of the split kernel that fit on one SM for these operands (shared memory of the staging form; registers
+// allow four).
+static int decode_ctas_per_sm(const FattnArgs& a) {
+    const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
+    size_t smem;
+    switch (decode_mode(a, hdp)) {
+        case kDecRegQ8: smem = (size_t)kDecRows * hdp * 2 + (size_t)kDecRegStages * 2 * kDecBN * (hdp / 32 * 34); break;
+        case kDecAsyncF16: {
+            const int ns = hdp >= 128 ? 3 : 4;
+            smem = (size_t)(kDecRows + ns * 2 * kDecBN) * hdp * 2;
+            if (a.has_mask && a.mask.vec16) smem += (size_t)ns * (a.Tq * a.gqa) * kDecBN * 2;
+            break;
+        }
+        case kDecAsyncQ8: smem = (size_t)(kDecRows + kDecBN) * hdp * 2 + (size_t)kDecQ8Stages * 2 * kDecBN * (hdp / 32 * 34); break;
+        default: smem = (size_t)(kDecRows + 2 * kDecBN) * hdp * 2; break;
+    }
+    const int n = (int)((size_t)227 * 1024 / (smem + 1024));
+    return n < 1 ? 1 : (n > 4 ? 4 : n);
+}
+
+// Split count of the KV range for `B` batch entries of these operands.  A small cost model in units of one 64-key
+// tile of one CTA: a split costs its tiles plus 1.5 (set-up, epilogue) plus its share of the merge (1.0 through the
+// workspace and the merge kernel, 0.5 inside a cluster), the grid runs in whole waves while it is at most four waves
+// long, and a merge kernel adds its launch latency (1.5).  The candidates it separates were measured on the Q8_0
+// kernel (9 tiles): 16 streams 3 splits 47.3 k vs 5 splits 38.0 k stream-steps/s; 32 streams 2 vs 3 splits 58.3 k
+// vs 54.3 k; 64 streams 1 vs 2 splits 80.9 k vs 68.7 k.
+static int g_forced_splits = 0;
+void decode_split_force(int n_splits) { g_forced_splits = n_splits; }
+
+int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
+    const int forced = g_forced_splits;
+    static const int per_sm_env = [] {  // B200_DECODE_CTAS_PER_SM=1..16 overrides the resident-CTA estimate
         const char* e = getenv("B200_DECODE_CTAS_PER_SM");
         const int n = e ? atoi(e) : 0;
-        return n >= 1 && n <= 16 ? n : 4;
+        return n >= 1 && n <= 16 ? n : 0;
     }();
-    long want = ((long)per_sm * sm_count + units - 1) / units;
-    if (want < 1) want = 1;
-    if (want > tiles) want = tiles;
-    if (want > 64) want = 64;
-    if (cluster_merge_ok && want > 8) want = 8;   // one cluster per (batch entry, kv-head)
-    const long tps = (tiles + want - 1) / want;   // tiles per split; drop the splits that would get none
-    want = (tiles + tps - 1) / tps;
-    return (int)(want < 1 ? 1 : want);
+    const int tiles = (a.Lk + kDecBN - 1) / kDecBN;
+    if (tiles <= 1) return 1;
+    if (forced) return forced < tiles ? forced : tiles;
+    const double units = (double)B * a.Hkv;
+    const double cap = (double)(per_sm_env ? per_sm_env : decode_ctas_per_sm(a)) * sm_count;
+    const bool cluster_ok = decode_cluster_merge_ok(a);
+    int best = 1;
+    double best_cost = 0.0;
+    for (int n = 1; n <= tiles && n <= 64; n++) {
+        const int tps = (tiles + n - 1) / n;
+        if ((tiles + tps - 1) / tps != n) continue;   // some split would get no tile
+        const double w = units * n / cap;
+        const double waves = w <= 4.0 ? ceil(w) : w + 0.5;
+        const bool cluster = cluster_ok && n > 1 && n <= 8 && units * n <= 4.0 * 148;
+        double cost = waves * (tps + 1.5 + (n == 1 ? 0.0 : (cluster ? 0.5 : 1.0)));
+        if (n > 1 && !cluster) cost += 1.5;
+        if (n == 1 || cost < best_cost - 1e-9) best = n, best_cost = cost;
+    }
+    return best;
 }
 
 }  // namespace b200

@@ -127,6 +127,9 @@ enum {
 
 /* Force a kernel family for A/B tests (B200_KERNEL_NONE restores automatic choice). Process-wide. */
 B200_API int b200_set_kernel_override(int kernel);
+/* Force the split count of the split-KV decode kernel (1..64, clamped to the number of 64-key tiles; 0 restores
+ * the automatic choice). For A/B tests and tuning. Process-wide. */
+B200_API int b200_set_decode_splits(int n_splits);
 
 B200_API const char* b200_strerror(int code);
 B200_API const char* b200_version(void);

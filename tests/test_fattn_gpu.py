@@ -221,6 +221,34 @@ def test_q8_0_decode_forms(b200, orc, kernel, hd, form):
         assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
 
 
+@pytest.mark.parametrize("n_splits", [1, 2, 3, 5, 8, 9, 64])
+@pytest.mark.parametrize("kv_kind", ["q8_0", "f16"])
+def test_decode_forced_split_counts(b200, orc, n_splits, kv_kind):
+    """Every way the partial results of the KV splits are merged: none (one split), inside a thread-block cluster
+    (Q8_0 cache, 2..8 splits), through the workspace and the merge kernel (the rest); ragged lengths leave some
+    splits without a key."""
+    rng = np.random.default_rng(700 + n_splits)
+    S, H, Hkv, hd, max_ctx = 3, 8, 2, 128, 640
+    lens = [600, 65, 330]
+    q = randn_f16(rng, (S, H, 1, hd)).astype(np.float32)
+    kw = dict(scale=hd ** -0.5, kv_len=lens)
+    if kv_kind == "q8_0":
+        kc, vc = _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx), _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx)
+        kw["kv_type"] = abi.Q8_0
+    else:
+        kc, vc = randn_f16(rng, (S, Hkv, max_ctx, hd)), randn_f16(rng, (S, Hkv, max_ctx, hd))
+    kv, vv = kc[:, :, :600], vc[:, :, :600]
+    ref = orc.flash_attn_ext(q, kv, vv, **kw)
+    assert b200.lib().b200_set_decode_splits(n_splits) == 0
+    try:
+        tq, tk, tv = (torch.from_numpy(np.ascontiguousarray(x)) for x in (q, kv, vv))
+        assert b200.plan(tq, tk, tv, **{k: v for k, v in kw.items() if k != "kv_len"})[1] == min(n_splits, 10)
+        got = gpu_op(b200, q, cuda_view(kv, kc), cuda_view(vv, vc), **kw)
+    finally:
+        assert b200.lib().b200_set_decode_splits(0) == 0
+    assert_close(got, ref, f"decode {kv_kind}, {n_splits} splits forced")
+
+
 def test_cfg4_decode_f16_cache_gqa(b200, orc, kernel):
     rng = np.random.default_rng(33)
     S, H, Hkv, hd, Lk = 4, 32, 8, 128, 535

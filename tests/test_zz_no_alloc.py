@@ -89,13 +89,19 @@ def test_static_scratch_matches_workspace_launch_twice(b200, orc):
 
 def test_static_scratch_rejects_what_it_cannot_hold(b200):
     L = b200.lib()
-    # 591 (stream, kv-head) units get 2 splits each: 1182 partials x 16 rows x 128 floats = 9.7 MB > 8 MiB
+    # 591 (stream, kv-head) units with 2 splits each: 1182 partials x 16 rows x 128 floats = 9.7 MB > 8 MiB.  The
+    # automatic choice keeps single-wave grids, whose partials always fit, so the split count is forced here.
     q = torch.zeros((3, 197, 1, 128), dtype=torch.float16, device="cuda")
     k = torch.zeros((3, 197, 128, 128), dtype=torch.float16, device="cuda")
-    need = b200.workspace_bytes(q, k, k, scale=1.0)
-    assert need > (8 << 20)
-    rc, _ = _launch_static(L, q, k, k, None, 1.0)
-    assert rc == abi.E_LIMIT and b"limit" in L.b200_strerror(rc)
+    assert L.b200_set_decode_splits(2) == 0
+    try:
+        need = b200.workspace_bytes(q, k, k, scale=1.0)
+        assert need > (8 << 20)
+        rc, _ = _launch_static(L, q, k, k, None, 1.0)
+        assert rc == abi.E_LIMIT and b"limit" in L.b200_strerror(rc)
+    finally:
+        assert L.b200_set_decode_splits(0) == 0
+    assert L.b200_set_decode_splits(65) == abi.E_LIMIT
     # a prefill-shaped call is not the decode kernel: refused, not silently rerouted
     qp = torch.zeros((1, 4, 300, 64), dtype=torch.float16, device="cuda")
     kp = torch.zeros((1, 4, 300, 64), dtype=torch.float16, device="cuda")
