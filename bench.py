@@ -266,6 +266,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernel", default="auto", choices=["auto", "tile"])
+    ap.add_argument("--decode-splits", type=int, default=0, help="force the split count of the split-KV decode kernel (A/B runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch each layer from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -292,6 +293,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     if args.kernel == "tile":
         b200.lib().b200_set_kernel_override(abi.KERNEL_TILE_MMA)
+    if args.decode_splits:
+        b200.lib().b200_set_decode_splits(args.decode_splits)
 
     units = args.units or w["units"]
     rng = np.random.default_rng(w["seed"] + 1000 * rank)
