@@ -1563,7 +1563,7 @@ static int decode_ctas_per_sm(const FattnArgs& a) {
 // Split count of the KV range for `B` batch entries of these operands.  A small cost model in units of one 64-key
 // tile of one CTA: a split costs its tiles plus 1.5 (set-up, epilogue) plus its share of the merge (1.0 through the
 // workspace and the merge kernel, 0.5 inside a cluster), the grid runs in whole waves while it is at most four waves
-// long, and a merge kernel adds its launch latency (1.5).  The candidates it separates were measured on the Q8_0
+// long, and a merge kernel adds its launch latency (1.5) and 0.2 per split it has to read (0.1 inside a cluster).  The candidates it separates were measured on the Q8_0
 // kernel (9 tiles): 16 streams 3 splits 47.3 k vs 5 splits 38.0 k stream-steps/s; 32 streams 2 vs 3 splits 58.3 k
 // vs 54.3 k; 64 streams 1 vs 2 splits 80.9 k vs 68.7 k.
 static int g_forced_splits = 0;
@@ -1591,7 +1591,7 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
         const double waves = w <= 4.0 ? ceil(w) : w + 0.5;
         const bool cluster = cluster_ok && n > 1 && n <= 8 && units * n <= 4.0 * 148;
         double cost = waves * (tps + 1.5 + (n == 1 ? 0.0 : (cluster ? 0.5 : 1.0)));
-        if (n > 1 && !cluster) cost += 1.5;
+        if (n > 1) cost += cluster ? 0.1 * n : 1.5 + 0.2 * n;   // the merge reads n partials per output row
         if (n == 1 || cost < best_cost - 1e-9) best = n, best_cost = cost;
     }
     return best;
