@@ -87,6 +87,8 @@ SYMBOLS = {
     "b200_fattn_static_scratch_bytes": (C.c_size_t, []),
     "b200_last_kernel": (C.c_int, []),
     "b200_device_status": (C.c_int, []),
+    "b200_device_status_reset": (C.c_int, []),
+    "b200_test_bounded_wait": (C.c_int, [C.c_int, C.c_void_p]),
     "b200_kv_create": (C.c_int, [C.POINTER(KvConfig), C.POINTER(C.c_void_p)]),
     "b200_kv_destroy": (None, [C.c_void_p]),
     "b200_kv_bytes": (C.c_size_t, [C.c_void_p]),

@@ -1,6 +1,7 @@
 """Builds libb200_fattn.so in-tree with nvcc for sm_100a (cross-compiles without a GPU)."""
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -9,6 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200_fattn.so")
+STAMP = LIB + ".srchash"   # hash of the sources and flags the library next to it was built from
 SOURCES = ["fattn_api.cu", "fattn_mma.cu", "fattn_tc5.cu", "kv_slab.cu", "segment_sched.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -27,20 +29,36 @@ def sources() -> list[str]:
     return [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
 
 
+def source_hash() -> str:
+    """SHA-256 over every file under csrc/, the public header and the compiler flags."""
+    h = hashlib.sha256()
+    files = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)) + [os.path.join(HERE, "..", "include", "b200_fattn.h")]
+    for path in files:
+        h.update(os.path.basename(path).encode() + b"\0")
+        h.update(open(path, "rb").read())
+    h.update(" ".join(NVCC_FLAGS + SOURCES).encode())
+    return h.hexdigest()
+
+
+def built_hash() -> str | None:
+    """The source hash recorded when the library in the tree was linked, or None."""
+    try:
+        return open(STAMP).read().strip() if os.path.exists(LIB) else None
+    except OSError:
+        return None
+
+
 def needs_build() -> bool:
-    if not os.path.exists(LIB):
-        return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "b200_fattn.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+    return built_hash() != source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
-    if not force and os.path.exists(LIB) and shutil.which(_nvcc()) is None and not os.path.exists(_nvcc()):
-        # a prebuilt library travelled here and there is no compiler to refresh it with: use it as it is
-        return LIB
+    if shutil.which(_nvcc()) is None and not os.path.exists(_nvcc()):
+        raise RuntimeError(
+            f"{LIB} is missing or was built from other sources (recorded {built_hash()}, tree {source_hash()}) "
+            "and there is no nvcc to rebuild it with")
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
@@ -61,6 +79,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed")
     link = [_nvcc(), "-shared", "-o", LIB, *objs, "-lcudart", "-Xcompiler", "-fPIC"]
     subprocess.run(link, check=True)
+    with open(STAMP, "w") as f:
+        f.write(source_hash() + "\n")
     return LIB
 
 

@@ -1,6 +1,7 @@
 // fattn_api.cu — the C-ABI of include/b200_fattn.h for the attention operator: operand
 // validation (ggml shape rules, returned as codes, never asserts), kernel choice, workspace
 // sizing, launch, and the host-buffer round trip.
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -16,7 +17,7 @@ namespace {
 
 thread_local char g_cuda_err[256] = "";
 thread_local int g_last_kernel = B200_KERNEL_NONE;
-int g_override = B200_KERNEL_NONE;
+std::atomic<int> g_override{B200_KERNEL_NONE};   // process-wide A/B knob, read once per plan
 
 int cuda_fail(cudaError_t e, const char* what) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
@@ -164,6 +165,9 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     if (dst->nb[1] != (uint64_t)hd * 4 || dst->nb[2] != (uint64_t)hd * H * 4 ||
         dst->nb[3] != (uint64_t)hd * H * Tq * 4)
         return B200_E_STRIDE;
+    // output rows are written with 128-bit stores where the row length allows it (head_dim 64 / 128 on the
+    // tensor-core kernels), so the base must be 16-byte aligned for those head dims
+    if ((hd == 64 || hd == 128) && (uintptr_t)dst->data % 16) return B200_E_ALIGN;
     if (hd > 128) return B200_E_UNSUPPORTED;
     if (Tq > INT32_MAX / 2 || Lk > INT32_MAX / 2 || H > 65535 || B > 65535) return B200_E_LIMIT;
     if (!std::isfinite(p->scale) || !std::isfinite(p->max_bias) || !std::isfinite(p->logit_softcap))
@@ -244,14 +248,15 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     int kernel = B200_KERNEL_TILE_MMA;
     const bool decode_ok = !a.relpos && Tq * (H / Hkv) <= 16;
     const bool tc5_ok = tc5_supported(a);
+    const int override_k = g_override.load(std::memory_order_relaxed);
     if (decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
     else if (tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
-    if (g_override == B200_KERNEL_TILE_MMA) kernel = B200_KERNEL_TILE_MMA;
-    if (g_override == B200_KERNEL_DECODE_SPLIT && decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
-    if (g_override == B200_KERNEL_PREFILL_TC5 && tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
+    if (override_k == B200_KERNEL_TILE_MMA) kernel = B200_KERNEL_TILE_MMA;
+    if (override_k == B200_KERNEL_DECODE_SPLIT && decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
+    if (override_k == B200_KERNEL_PREFILL_TC5 && tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
     plan->cast_kv = plan->cast_r = false;
     plan->cast_each = plan->cast_r_bytes = 0;
-    if (kernel == B200_KERNEL_TILE_MMA && g_override != B200_KERNEL_TILE_MMA && !decode_ok && (a.hd == 64 || a.hd == 128) &&
+    if (kernel == B200_KERNEL_TILE_MMA && override_k != B200_KERNEL_TILE_MMA && !decode_ok && (a.hd == 64 || a.hd == 128) &&
         !tc5_ok) {
         // F32 / Q8_0 / unaligned K/V: a conversion pre-pass into the workspace puts the call on the tcgen05 kernel
         FattnArgs c = kv_is_tma_ready(a) ? a : with_f16_kv(a, (const void*)256, (const void*)256);
@@ -269,7 +274,8 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     plan->ws_bytes = 2 * plan->cast_each + plan->cast_r_bytes;
     if (kernel == B200_KERNEL_DECODE_SPLIT) {
         a.n_splits = decode_split_choose(a, a.B, sm_count);
-        plan->ws_bytes = decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
+        // splits that merge inside thread-block clusters never touch a workspace
+        plan->ws_bytes = decode_uses_cluster_merge(a) ? 0 : decode_split_ws_bytes(a.B, a.Hkv, a.n_splits, a.hd);
     }
     return B200_OK;
 }
@@ -378,10 +384,28 @@ B200_API const char* b200_last_cuda_error(void) { return g_cuda_err; }
 B200_API int b200_last_kernel(void) { return g_last_kernel; }
 
 B200_API int b200_device_status(void) {
-    int st = 0;
-    const int e = tc5_read_status(&st);
+    int st_tc5 = 0, st_mma = 0;
+    int e = tc5_read_status(&st_tc5);
+    if (e == 0) e = mma_read_status(&st_mma);
     if (e != 0) return cuda_fail((cudaError_t)e, "cudaMemcpyFromSymbol(status)");
-    return st ? B200_E_DEVICE_WAIT : B200_OK;
+    return (st_tc5 | st_mma) ? B200_E_DEVICE_WAIT : B200_OK;
+}
+
+B200_API int b200_device_status_reset(void) {
+    int e = tc5_reset_status();
+    if (e == 0) e = mma_reset_status();
+    if (e != 0) return cuda_fail((cudaError_t)e, "cudaMemcpyToSymbol(status)");
+    return B200_OK;
+}
+
+B200_API int b200_test_bounded_wait(int polls, void* cuda_stream) {
+    if (polls < 1 || polls > (1 << 20)) return B200_E_LIMIT;
+    DeviceInfo di;
+    const int rc = device_info(&di);
+    if (rc != B200_OK) return rc;
+    const int e = launch_bounded_wait_probe(polls, (cudaStream_t)cuda_stream);
+    if (e != 0) return cuda_fail((cudaError_t)e, "bounded-wait probe launch");
+    return B200_OK;
 }
 
 B200_API int b200_set_decode_splits(int n_splits) {
@@ -392,7 +416,7 @@ B200_API int b200_set_decode_splits(int n_splits) {
 
 B200_API int b200_set_kernel_override(int kernel) {
     if (kernel < B200_KERNEL_NONE || kernel > B200_KERNEL_PREFILL_TC5) return B200_E_SHAPE;
-    g_override = kernel;
+    g_override.store(kernel, std::memory_order_relaxed);
     return B200_OK;
 }
 
@@ -530,77 +554,80 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
 
     cudaStream_t streams[2] = {ar.stream, ar.stream2};
 
-    // operands without a batch dimension (ne[3] == 1) are copied once, ahead of everything, on stream 0
+    // Everything below enqueues asynchronous work that reads and writes the caller's host buffers.  Whatever goes
+    // wrong, the call leaves through ONE exit that first waits for both streams, so the caller may free or reuse
+    // its buffers as soon as it has the return code, and the event is always destroyed.
     b200_tensor dt[NIN];
     cudaEvent_t shared_ready = nullptr;
-    for (int i = 0; i < NIN; i++) {
-        if (!in[i]) continue;
-        dt[i] = *in[i];
-        dt[i].data = ar.base + off[i];
-        if (n_chunks == 1 || in[i]->ne[3] == 1) {
-            if ((e = cudaMemcpyAsync(dt[i].data, in[i]->data, span_bytes(in[i]), cudaMemcpyHostToDevice, streams[0])) !=
-                cudaSuccess)
-                return cuda_fail(e, "cudaMemcpyAsync(H2D)");
-        }
-    }
-    if (ext && ext->kv_len &&
-        (e = cudaMemcpyAsync(ar.base + kvlen_off, ext->kv_len, (size_t)B * 4, cudaMemcpyHostToDevice, streams[0])) !=
-            cudaSuccess)
-        return cuda_fail(e, "cudaMemcpyAsync(kv_len)");
-    if (n_chunks > 1) {
-        if ((e = cudaEventCreateWithFlags(&shared_ready, cudaEventDisableTiming)) != cudaSuccess)
-            return cuda_fail(e, "cudaEventCreate");
-        cudaEventRecord(shared_ready, streams[0]);
-        cudaStreamWaitEvent(streams[1], shared_ready, 0);
-    }
-
-    int rc_chunks = B200_OK;
-    for (int c = 0; c < n_chunks && rc_chunks == B200_OK; c++) {
-        const int64_t b0 = B * c / n_chunks, b1 = B * (c + 1) / n_chunks, nb = b1 - b0;
-        cudaStream_t st = streams[c & 1];
-        b200_tensor ct[NIN];
+    auto enqueue_all = [&]() -> int {
+        cudaError_t e;
+        // operands without a batch dimension (ne[3] == 1) are copied once, ahead of everything, on stream 0
         for (int i = 0; i < NIN; i++) {
             if (!in[i]) continue;
-            ct[i] = dt[i];
-            if (n_chunks > 1 && in[i]->ne[3] != 1) {
-                ct[i].data = (uint8_t*)dt[i].data + (size_t)b0 * in[i]->nb[3];
-                ct[i].ne[3] = nb;
-                b200_tensor hview = *in[i];
-                hview.ne[3] = nb;
-                if ((e = cudaMemcpyAsync(ct[i].data, (const uint8_t*)in[i]->data + (size_t)b0 * in[i]->nb[3], span_bytes(&hview),
-                                         cudaMemcpyHostToDevice, st)) != cudaSuccess)
-                    return cuda_fail(e, "cudaMemcpyAsync(H2D chunk)");
+            dt[i] = *in[i];
+            dt[i].data = ar.base + off[i];
+            if (n_chunks == 1 || in[i]->ne[3] == 1) {
+                if ((e = cudaMemcpyAsync(dt[i].data, in[i]->data, span_bytes(in[i]), cudaMemcpyHostToDevice, streams[0])) !=
+                    cudaSuccess)
+                    return cuda_fail(e, "cudaMemcpyAsync(H2D)");
             }
         }
-        b200_fattn_ext dext;
-        memset(&dext, 0, sizeof(dext));
-        if (ext) {
-            dext = *ext;
-            dext.q_v = ext->q_v ? &ct[4] : nullptr;
-            dext.r = ext->r ? &ct[5] : nullptr;
-            dext.pos_bias_u = ext->pos_bias_u ? &ct[6] : nullptr;
-            dext.pos_bias_v = ext->pos_bias_v ? &ct[7] : nullptr;
-            dext.kv_len = ext->kv_len ? (const int32_t*)(ar.base + kvlen_off) + b0 : nullptr;
+        if (ext && ext->kv_len &&
+            (e = cudaMemcpyAsync(ar.base + kvlen_off, ext->kv_len, (size_t)B * 4, cudaMemcpyHostToDevice, streams[0])) !=
+                cudaSuccess)
+            return cuda_fail(e, "cudaMemcpyAsync(kv_len)");
+        if (n_chunks > 1) {
+            if ((e = cudaEventCreateWithFlags(&shared_ready, cudaEventDisableTiming)) != cudaSuccess)
+                return cuda_fail(e, "cudaEventCreate");
+            if ((e = cudaEventRecord(shared_ready, streams[0])) != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
+            if ((e = cudaStreamWaitEvent(streams[1], shared_ready, 0)) != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
         }
-        b200_tensor cdst = *dst;
-        cdst.ne[3] = nb;
-        cdst.data = ar.base + dst_off + (size_t)b0 * dst->nb[3];
-        Plan cplan;
-        rc_chunks = make_plan(&ct[0], &ct[1], &ct[2], mask ? &ct[3] : nullptr, &cdst, params, ext ? &dext : nullptr, false, &cplan);
-        if (rc_chunks != B200_OK) break;
-        if (cplan.ws_bytes > ws_each) {
-            rc_chunks = B200_E_WORKSPACE;
-            break;
+        for (int c = 0; c < n_chunks; c++) {
+            const int64_t b0 = B * c / n_chunks, b1 = B * (c + 1) / n_chunks, nb = b1 - b0;
+            cudaStream_t st = streams[c & 1];
+            b200_tensor ct[NIN];
+            for (int i = 0; i < NIN; i++) {
+                if (!in[i]) continue;
+                ct[i] = dt[i];
+                if (n_chunks > 1 && in[i]->ne[3] != 1) {
+                    ct[i].data = (uint8_t*)dt[i].data + (size_t)b0 * in[i]->nb[3];
+                    ct[i].ne[3] = nb;
+                    b200_tensor hview = *in[i];
+                    hview.ne[3] = nb;
+                    if ((e = cudaMemcpyAsync(ct[i].data, (const uint8_t*)in[i]->data + (size_t)b0 * in[i]->nb[3], span_bytes(&hview),
+                                             cudaMemcpyHostToDevice, st)) != cudaSuccess)
+                        return cuda_fail(e, "cudaMemcpyAsync(H2D chunk)");
+                }
+            }
+            b200_fattn_ext dext;
+            memset(&dext, 0, sizeof(dext));
+            if (ext) {
+                dext = *ext;
+                dext.q_v = ext->q_v ? &ct[4] : nullptr;
+                dext.r = ext->r ? &ct[5] : nullptr;
+                dext.pos_bias_u = ext->pos_bias_u ? &ct[6] : nullptr;
+                dext.pos_bias_v = ext->pos_bias_v ? &ct[7] : nullptr;
+                dext.kv_len = ext->kv_len ? (const int32_t*)(ar.base + kvlen_off) + b0 : nullptr;
+            }
+            b200_tensor cdst = *dst;
+            cdst.ne[3] = nb;
+            cdst.data = ar.base + dst_off + (size_t)b0 * dst->nb[3];
+            Plan cplan;
+            int rc_c = make_plan(&ct[0], &ct[1], &ct[2], mask ? &ct[3] : nullptr, &cdst, params, ext ? &dext : nullptr, false, &cplan);
+            if (rc_c != B200_OK) return rc_c;
+            if (cplan.ws_bytes > ws_each) return B200_E_WORKSPACE;
+            rc_c = do_launch(cplan, cplan.ws_bytes ? ar.base + ws_off + (size_t)(c & 1) * ws_each : nullptr, cplan.ws_bytes, st);
+            if (rc_c != B200_OK) return rc_c;
+            if ((e = cudaMemcpyAsync((uint8_t*)dst->data + (size_t)b0 * dst->nb[3], cdst.data, (size_t)nb * dst->nb[3],
+                                     cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+                return cuda_fail(e, "cudaMemcpyAsync(D2H)");
         }
-        rc_chunks = do_launch(cplan, cplan.ws_bytes ? ar.base + ws_off + (size_t)(c & 1) * ws_each : nullptr, cplan.ws_bytes, st);
-        if (rc_chunks != B200_OK) break;
-        if ((e = cudaMemcpyAsync((uint8_t*)dst->data + (size_t)b0 * dst->nb[3], cdst.data, (size_t)nb * dst->nb[3],
-                                 cudaMemcpyDeviceToHost, st)) != cudaSuccess)
-            return cuda_fail(e, "cudaMemcpyAsync(D2H)");
-    }
-    cudaError_t e0 = cudaStreamSynchronize(streams[0]), e1 = cudaStreamSynchronize(streams[1]);
+        return B200_OK;
+    };
+    const int rc_enqueue = enqueue_all();
+    const cudaError_t e0 = cudaStreamSynchronize(streams[0]), e1 = cudaStreamSynchronize(streams[1]);
     if (shared_ready) cudaEventDestroy(shared_ready);
-    if (rc_chunks != B200_OK) return rc_chunks;
+    if (rc_enqueue != B200_OK) return rc_enqueue;
     if (e0 != cudaSuccess) return cuda_fail(e0, "cudaStreamSynchronize");
     if (e1 != cudaSuccess) return cuda_fail(e1, "cudaStreamSynchronize");
     return B200_OK;
@@ -629,7 +656,10 @@ B200_API void b200_host_arena_release(void) { g_arena.release(); }
 // ------------------------------------------------------------------------------------------
 namespace b200 {
 namespace {
-constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: covers the split-KV partials of up to 8 decode streams x 8 KV heads x head_dim 128
+// 8 MiB.  A launch fits when B * Hkv * n_splits * (16 * hdp * 4 + 128) bytes <= 8 MiB (hdp = head_dim rounded up to
+// 32 / 64 / 128): e.g. 8 streams x 8 KV heads x head_dim 128 with up to 15 splits, or one Whisper segment
+// (20 heads, head_dim 64) with up to 64.
+constexpr size_t kStaticScratchBytes = 8u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address; the

@@ -117,5 +117,14 @@ size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd);
 int decode_split_choose(const FattnArgs& a, int B, int sm_count);
 void decode_split_force(int n_splits);  // 0 = automatic
 bool decode_cluster_merge_ok(const FattnArgs& a);
+// True when a launch with these arguments (n_splits set) merges its splits inside thread-block clusters: it then
+// neither reads nor writes a workspace.
+bool decode_uses_cluster_merge(const FattnArgs& a);
+// Status word of the mma.sync kernels' bounded waits (0 = no wait ever ran out). cudaError_t-compatible returns.
+int mma_read_status(int* status);
+int mma_reset_status();
+// Test hook: a one-warp kernel that waits, for at most `polls` polls, on an mbarrier nobody completes, then sets the
+// status word and returns.
+int launch_bounded_wait_probe(int polls, cudaStream_t st);
 
 }  // namespace b200

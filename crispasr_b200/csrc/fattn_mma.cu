@@ -13,10 +13,13 @@
 //    GQA, beams sharing a cross-attention cache): one (split, kv-head, batch) per CTA streams its
 //    share of the keys once, the four warps own 16-key slices of each tile, and partial
 //    (O, m, l) go to the workspace; fattn_merge_kernel combines splits with a log-sum-exp merge.
+#include <atomic>
 #include <cstdlib>
 #include "fattn_common.cuh"
 
 namespace b200 {
+
+__device__ int g_mma_status = 0;  // 0 ok, 1 = a bounded wait of a kernel in this file ran out
 
 namespace {
 
@@ -436,12 +439,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded: a copy that never lands ends the wait after about a second; the tile is then multiplied as it is.
-__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
-        if (mbar_try_wait(bar, parity)) return;
+// Bounded: a copy that never lands ends the wait after about a second.  Called by all lanes of a warp on the warp's
+// own barrier; the result is warp-uniform (a phase one lane saw complete is complete).  On expiry the device status
+// word is set (b200_device_status reports B200_E_DEVICE_WAIT) and the caller stops consuming tiles.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = 1u << 22) {
+    bool ok = false;
+    for (uint32_t it = 0; it < limit; ++it) {
+        if (mbar_try_wait(bar, parity)) {
+            ok = true;
+            break;
+        }
         if (it > 64) __nanosleep(64);
     }
+    ok = __any_sync(0xffffffffu, ok);
+    if (!ok && (threadIdx.x & 31) == 0) atomicExch(&g_mma_status, 1);
+    return ok;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
@@ -705,7 +717,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             // operands), so the key loop needs no CTA-wide barrier and the four warps drift apart freely - one
             // waits for its copy while another dequantises or multiplies.
             const int stage = (tile - tile_lo) % NS;
-            mbar_wait_bounded(smem_u32(&s_q8bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u);
+            if (!mbar_wait_bounded(smem_u32(&s_q8bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u)) break;
             __syncwarp();                // this warp's raw rows landed; its previous fp16 rows have been consumed
             dequant_tile_q8<HD>(sRaw + stage * 2 * RAW_BYTES, sKV, len_b - k0, warp, lane);
             __syncwarp();
@@ -1020,7 +1032,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     for (int tile = tile_lo; tile < tile_hi; tile++) {
         const int k0 = tile * kDecBN;
         const int stage = (tile - tile_lo) % NS;
-        mbar_wait_bounded(smem_u32(&s_bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u);
+        if (!mbar_wait_bounded(smem_u32(&s_bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u)) break;
         const uint8_t* rawK = sRaw + stage * 2 * RAW_BYTES + 16 * warp * RB;   // this warp's 16 keys
         const uint8_t* rawV = rawK + RAW_BYTES;
         const int rows_valid = len_b - (k0 + 16 * warp);   // keys at or beyond it hold stale bytes: their scale reads as 0
@@ -1535,7 +1547,40 @@ size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd) {
     return ((o + 255) / 256) * 256 + ((ml + 255) / 256) * 256;
 }
 
-// Enough CTAs to put about four on every SM, never more splits than 64-key tiles.
+bool decode_uses_cluster_merge(const FattnArgs& a) { return use_cluster_merge(a); }
+
+int mma_read_status(int* status) {
+    int v = 0;
+    const cudaError_t e = cudaMemcpyFromSymbol(&v, g_mma_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    *status = v;
+    return 0;
+}
+
+int mma_reset_status() {
+    const int zero = 0;
+    return (int)cudaMemcpyToSymbol(g_mma_status, &zero, sizeof(int));
+}
+
+namespace {
+// One warp arms nothing and waits on its own mbarrier for at most `polls` polls: the wait must run out, set the
+// status word and let the kernel return.  Exercises the failure path of mbar_wait_bounded without a fault.
+__global__ void bounded_wait_probe_kernel(uint32_t polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    mbar_wait_bounded(smem_u32(&bar), 0u, polls);
+}
+}  // namespace
+
+int launch_bounded_wait_probe(int polls, cudaStream_t st) {
+    bounded_wait_probe_kernel<<<1, 32, 0, st>>>((uint32_t)polls);
+    return (int)cudaGetLastError();
+}
+
 bool decode_cluster_merge_ok(const FattnArgs& a) {
     return cluster_merge_enabled() && a.k.type == B200_TYPE_Q8_0 && (a.hd == 64 || a.hd == 128);
 }
@@ -1566,11 +1611,11 @@ static int decode_ctas_per_sm(const FattnArgs& a) {
 // long, and a merge kernel adds its launch latency (1.5) and 0.2 per split it has to read (0.1 inside a cluster).  The candidates it separates were measured on the Q8_0
 // kernel (9 tiles): 16 streams 3 splits 47.3 k vs 5 splits 38.0 k stream-steps/s; 32 streams 2 vs 3 splits 58.3 k
 // vs 54.3 k; 64 streams 1 vs 2 splits 80.9 k vs 68.7 k.
-static int g_forced_splits = 0;
-void decode_split_force(int n_splits) { g_forced_splits = n_splits; }
+static std::atomic<int> g_forced_splits{0};
+void decode_split_force(int n_splits) { g_forced_splits.store(n_splits, std::memory_order_relaxed); }
 
 int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
-    const int forced = g_forced_splits;
+    const int forced = g_forced_splits.load(std::memory_order_relaxed);
     static const int per_sm_env = [] {  // B200_DECODE_CTAS_PER_SM=1..16 overrides the resident-CTA estimate
         const char* e = getenv("B200_DECODE_CTAS_PER_SM");
         const int n = e ? atoi(e) : 0;

@@ -1302,4 +1302,9 @@ int tc5_read_status(int* status) {
     return 0;
 }
 
+int tc5_reset_status() {
+    const int zero = 0;
+    return (int)cudaMemcpyToSymbol(g_tc5_status, &zero, sizeof(int));
+}
+
 }  // namespace b200

@@ -13,5 +13,6 @@ int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t
 
 // Reads the device status word set when a bounded device-side wait ran out (0 = never). Returns a cudaError_t value.
 int tc5_read_status(int* status);
+int tc5_reset_status();
 
 }  // namespace b200

@@ -19,7 +19,7 @@
  *   K    [hd,  Lk, Hkv, Bk] F16, F32 or Q8_0 (34-byte blocks of 32), H % Hkv == 0, B % Bk == 0
  *   V    [hdv, Lk, Hkv, Bk] same type as K (hdv == hd in this library)
  *   mask [Lk,  Tq, 1|H, 1|B] F16 or NULL; 0 = attend, -inf = masked, any finite value = additive bias
- *   dst  [hdv, H,  Tq,  B]  F32, contiguous
+ *   dst  [hdv, H,  Tq,  B]  F32, contiguous; 16-byte aligned base for head_dim 64 / 128 (else B200_E_ALIGN)
  *
  *   s[k]   = scale * sum_c Q[c,q,h,b] * K[c,k,h/(H/Hkv),b/(B/Bk)]
  *   s[k]   = softcap * tanh(s[k] / softcap)                (only when logit_softcap != 0)
@@ -125,10 +125,12 @@ enum {
     B200_KERNEL_PREFILL_TC5 = 3 /* TMA + tcgen05.mma + TMEM prefill kernel (F16 K/V) */
 };
 
-/* Force a kernel family for A/B tests (B200_KERNEL_NONE restores automatic choice). Process-wide. */
+/* Force a kernel family for A/B tests (B200_KERNEL_NONE restores automatic choice). Process-wide: an atomic that
+ * every plan reads once.  Do not change it between the b200_fattn_workspace_bytes and b200_fattn_launch calls
+ * of one operator call (the launch would find its workspace too small and return B200_E_WORKSPACE). */
 B200_API int b200_set_kernel_override(int kernel);
 /* Force the split count of the split-KV decode kernel (1..64, clamped to the number of 64-key tiles; 0 restores
- * the automatic choice). For A/B tests and tuning. Process-wide. */
+ * the automatic choice). For A/B tests and tuning. Process-wide atomic, same rule as above. */
 B200_API int b200_set_decode_splits(int n_splits);
 
 B200_API const char* b200_strerror(int code);
@@ -156,9 +158,11 @@ B200_API int b200_fattn_plan(const b200_tensor* q, const b200_tensor* k, const b
                              int* kernel, int* n_splits);
 
 /*
- * b200_fattn_workspace_bytes — scratch the launch needs (split-KV partial O/m/l).
+ * b200_fattn_workspace_bytes — scratch the launch needs (split-KV partial O/m/l, or the F16
+ * copies of K/V/R that the conversion pre-pass of the tensor-core prefill writes).
  * Mirrors ggml's per-op work buffer sizing (the reference sizes it inside
- * ggml_backend_sched_alloc_graph, src/voxtral.cpp:1196-1198). May return 0 bytes.
+ * ggml_backend_sched_alloc_graph, src/voxtral.cpp:1196-1198). May return 0 bytes: one split,
+ * or splits that merge inside thread-block clusters (small Q8_0 decode batches).
  */
 B200_API int b200_fattn_workspace_bytes(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
                                         const b200_tensor* mask, const b200_tensor* dst,
@@ -225,6 +229,15 @@ B200_API size_t b200_fattn_static_scratch_bytes(void);
  * after synchronising the stream(s) of interest.  No reference counterpart (ggml aborts instead).
  */
 B200_API int b200_device_status(void);
+/* Clears the status word of the current device (it is sticky otherwise).  Call with no launch in flight. */
+B200_API int b200_device_status_reset(void);
+/*
+ * b200_test_bounded_wait — test hook for the failure path above, in the only form that is safe on a shared
+ * GPU: launches a one-warp kernel that waits on an mbarrier which nothing ever completes, with a limit of
+ * `polls` polls (1 .. 2^20).  The wait runs out, the kernel sets the status word and returns normally; the
+ * context stays usable.  After synchronising, b200_device_status must report B200_E_DEVICE_WAIT.
+ */
+B200_API int b200_test_bounded_wait(int polls, void* cuda_stream);
 
 /* The kernel family the calling thread's most recent successful launch used. */
 B200_API int b200_last_kernel(void);

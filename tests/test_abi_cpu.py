@@ -29,6 +29,12 @@ def test_library_exports_every_declared_symbol(b200):
     assert b"sm_100a" in b200.lib().b200_version()
 
 
+def test_library_was_built_from_the_sources_in_the_tree(b200):
+    """The stamp written beside the library at link time equals the hash of the sources now in the tree."""
+    from crispasr_b200 import build
+    assert build.built_hash() == build.source_hash()
+
+
 def test_missing_library_fails_loudly(b200, monkeypatch):
     import crispasr_b200
     monkeypatch.setattr(crispasr_b200, "_LIB", None)
@@ -65,6 +71,10 @@ def test_validator_codes(b200):
     # dst must be contiguous [hd,H,Tq,B]
     bad_dst = torch.zeros((1, 10, 8, 128), dtype=torch.float32)[..., :64]
     assert _supports(b200, q, k, k, dst=bad_dst)[1] == abi.E_STRIDE
+    # dst rows are written with 128-bit stores by the tensor-core prefill: a base that is only 4-byte aligned is refused
+    buf = torch.zeros(1 * 10 * 8 * 64 + 4, dtype=torch.float32)
+    assert _supports(b200, q, k, k, dst=buf[1:1 + 10 * 8 * 64].view(1, 10, 8, 64))[1] == abi.E_ALIGN
+    assert _supports(b200, q, k, k, dst=buf[4:4 + 10 * 8 * 64].view(1, 10, 8, 64)) == (True, 0)
     # Q8_0 rows: nb0 must be one block and hd a multiple of 32
     kq = torch.zeros((1, 2, 20, 136), dtype=torch.uint8)
     q128 = _desc((1, 8, 1, 128), torch.float32)
@@ -99,8 +109,13 @@ def test_plan_choices(b200):
     assert b200.workspace_bytes(dq, enc_k, enc_k, scale=0.35) >= 20 * ns * 16 * 64 * 4
     # LLM decode, GQA 4, Q8_0
     kq = torch.zeros((8, 8, 663, 136), dtype=torch.uint8)
-    kern, _ = b200.plan(_desc((8, 32, 1, 128), torch.float32), kq, kq, scale=0.088, kv_type=abi.Q8_0)
-    assert kern == abi.KERNEL_DECODE_SPLIT
+    kern, ns = b200.plan(_desc((8, 32, 1, 128), torch.float32), kq, kq, scale=0.088, kv_type=abi.Q8_0)
+    assert kern == abi.KERNEL_DECODE_SPLIT and 1 < ns <= 8
+    # ... whose few splits merge inside thread-block clusters: no workspace is asked for
+    assert b200.workspace_bytes(_desc((8, 32, 1, 128), torch.float32), kq, kq, scale=0.088, kv_type=abi.Q8_0) == 0
+    # the same streams over an F16 cache merge through the workspace
+    kf = _desc((8, 8, 663, 128))
+    assert b200.workspace_bytes(_desc((8, 32, 1, 128), torch.float32), kf, kf, scale=0.088) > 0
     # explicit per-head mask or relpos -> general tile kernel unless the tcgen05 kernel takes it
     r = _desc((1, 20, 2999, 64))
     kern, _ = b200.plan(enc_q, enc_k, enc_k, scale=0.125, q_v=enc_q, r=r)

@@ -27,6 +27,33 @@ def test_extension_is_loaded_and_device_is_b200(b200):
     assert torch.cuda.is_available()
     assert torch.cuda.get_device_capability(0)[0] == 10
     assert os.path.exists(b200.LIB_PATH)
+    # the library under test was linked from the sources now in the tree (stamp written at link time)
+    from crispasr_b200 import build
+    assert build.built_hash() == build.source_hash()
+    loaded = [ln.split()[-1] for ln in open("/proc/self/maps") if "libb200_fattn.so" in ln]
+    assert loaded and os.path.realpath(loaded[0]) == os.path.realpath(b200.LIB_PATH)
+
+
+def test_bounded_wait_runs_out_sets_status_and_leaves_the_context_usable(b200, orc):
+    """Failure path of the device-side waits, without a fault: a one-warp probe kernel waits on an mbarrier that
+    nothing completes, gives up after a few thousand polls, sets the status word and returns.  The host then reads
+    B200_E_DEVICE_WAIT, clears it, and the next ordinary launch is green."""
+    L = b200.lib()
+    assert L.b200_device_status_reset() == 0 and L.b200_device_status() == 0
+    assert L.b200_test_bounded_wait(0, None) == abi.E_LIMIT
+    assert L.b200_test_bounded_wait(4096, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert L.b200_device_status() == abi.E_DEVICE_WAIT
+    assert L.b200_device_status() == abi.E_DEVICE_WAIT, "the word is sticky until it is reset"
+    assert L.b200_device_status_reset() == 0 and L.b200_device_status() == 0
+    rng = np.random.default_rng(3)
+    q, k, v = (randn_f16(rng, (1, 4, 200, 64)) for _ in range(3))
+    assert_close(gpu_op(b200, q, k, v, scale=0.125), orc.flash_attn_ext(q, k, v, scale=0.125), "launch after a run-out wait")
+    kq = orc.quantize_q8_0(rng.standard_normal((2, 2, 300, 128)).astype(np.float32))
+    qd = randn_f16(rng, (2, 8, 1, 128))
+    assert_close(gpu_op(b200, qd, kq, kq, scale=128 ** -0.5, kv_type=abi.Q8_0),
+                 orc.flash_attn_ext(qd, kq, kq, scale=128 ** -0.5, kv_type=abi.Q8_0), "Q8_0 decode after a run-out wait")
+    assert L.b200_device_status() == 0
 
 
 # ---- config 1: Whisper base.en encoder self-attention --------------------------------------------
@@ -502,7 +529,7 @@ def test_host_entry_point_chunked_decode_workspace(b200, orc):
 
 
 def test_full_size_properties_cfg3(b200, orc):
-    """BASELINE size of the encoder workload (64 segments x 20 heads x 1500 frames, one layer): two sampled
+    """Full size of the Whisper large-v3 encoder workload (64 segments x 20 heads x 1500 frames, one layer): two sampled
     segments against the oracle, batch invariance (a segment computed inside the batch equals the same segment
     computed alone, bit for bit), softmax weights summing to one (V = ones), and linearity in V."""
     gen = torch.Generator(device="cuda").manual_seed(2)

@@ -4,8 +4,8 @@ from __future__ import annotations
 
 import numpy as np
 
-MAX_ABS_TOL = 2e-3   # BASELINE north_star: max-abs error
-REL_L2_TOL = 1e-3    # BASELINE north_star: relative L2 error
+MAX_ABS_TOL = 2e-3   # the path's stated tolerance: max-abs error against the CPU operator
+REL_L2_TOL = 1e-3    # the path's stated tolerance: relative L2 error
 
 
 class XorShift:
