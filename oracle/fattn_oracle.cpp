@@ -140,10 +140,27 @@ inline float alibi_slope(float max_bias, int64_t n_head, int64_t h) {
     return (uint64_t)h < n2 ? std::pow(m0, (float)(h + 1)) : std::pow(m1, (float)(2 * (h - n2) + 1));
 }
 
+// Options of one oracle run.  The first three select the oracle of record (gold = fp64 accumulation).  q_as_q8_0
+// and acc_f16 are DIAGNOSTIC switches: they restate two things the upstream CPU kernel is believed to do
+// (unverifiable here, its source being absent) so that the distance they would move a result can be measured:
+//   q_as_q8_0: against a Q8_0 K the query row is itself quantised to Q8_0 blocks and every block's dot product is
+//              an integer sum times the two block scales (the vec-dot pairing of a quantised K);
+//   acc_f16:   with F16 V the output row is accumulated key by key in F16 by a streaming softmax
+//              (acc = f16(acc*ms); acc = f16(acc + v*vs)), instead of fp32 after a two-pass softmax.
+// rows/n_rows restrict the computation to a subset of query rows (others are left untouched in dst).
+struct OrcOptions {
+    int gold = 0, q_round_f16 = 1, n_threads = 0;
+    int q_as_q8_0 = 0, acc_f16 = 0;
+    const int32_t* rows = nullptr;
+    int n_rows = 0;
+};
+
 template <typename acc_t>
 int flash_attn_impl(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, const b200_tensor* mask,
-                    const b200_tensor* dst, const b200_fattn_params* p, const b200_fattn_ext* ext, int q_round_f16,
-                    int n_threads) {
+                    const b200_tensor* dst, const b200_fattn_params* p, const b200_fattn_ext* ext, const OrcOptions& opt) {
+    const int q_round_f16 = opt.q_round_f16, n_threads = opt.n_threads;
+    const bool q_q8 = opt.q_as_q8_0 && k->type == B200_TYPE_Q8_0;
+    const bool acc16 = opt.acc_f16 && v->type == B200_TYPE_F16;
     const int64_t hd = q->ne[0], Tq = q->ne[1], H = q->ne[2], B = q->ne[3];
     const int64_t Lk = k->ne[1], Hkv = k->ne[2], Bk = k->ne[3];
     const int64_t hdv = v->ne[0];
@@ -194,11 +211,26 @@ int flash_attn_impl(const b200_tensor* q, const b200_tensor* k, const b200_tenso
                 {
                     std::vector<float> qrow(hd), qvrow(hd), s(Lk);
                     std::vector<acc_t> o(hdv);
+                    std::vector<int8_t> qq(hd);          // q_as_q8_0: the query row as Q8_0 quants ...
+                    std::vector<float> qd(hd / 32 + 1);  // ... and block scales (rounded to F16 like stored blocks)
+                    std::vector<uint16_t> o16(hdv);      // acc_f16: the F16 accumulator
+                    const int64_t n_iter = opt.rows ? opt.n_rows : Tq;
 #pragma omp for schedule(dynamic, 4)
-                    for (int64_t iq = 0; iq < Tq; iq++) {
+                    for (int64_t it = 0; it < n_iter; it++) {
+                        const int64_t iq = opt.rows ? opt.rows[it] : it;
+                        if (iq < 0 || iq >= Tq) continue;
                         load_row(tptr(q, iq, h, b), q->type, hd, qrow.data());
                         if (q_round_f16)
                             for (int64_t c = 0; c < hd; c++) qrow[c] = round_f16(qrow[c]);
+                        if (q_q8) {
+                            for (int64_t blk = 0; blk < hd / 32; blk++) {
+                                float amax = 0.0f;
+                                for (int i = 0; i < 32; i++) amax = std::max(amax, std::fabs(qrow[blk * 32 + i]));
+                                const float d = amax / 127.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
+                                for (int i = 0; i < 32; i++) qq[blk * 32 + i] = (int8_t)std::round(qrow[blk * 32 + i] * id);
+                                qd[blk] = round_f16(d);
+                            }
+                        }
                         if (qv) {
                             load_row(tptr(qv, iq, h, b), qv->type, hd, qvrow.data());
                             if (q_round_f16)
@@ -212,8 +244,23 @@ int flash_attn_impl(const b200_tensor* q, const b200_tensor* k, const b200_tenso
                         for (int64_t ik = 0; ik < kend; ik++) {
                             const float* kr = &Kf[(size_t)ik * hd];
                             acc_t acc = 0;
+                            if (q_q8) {
+                                // per block: integer dot of the quants, times both block scales, summed in fp32
+                                const uint8_t* krow = tptr(k, ik, hk, b / bq);
+                                float sumf = 0.0f;
+                                for (int64_t blk = 0; blk < hd / 32; blk++) {
+                                    const uint8_t* kb = krow + 34 * blk;
+                                    uint16_t dk;
+                                    std::memcpy(&dk, kb, 2);
+                                    int sumi = 0;
+                                    for (int i = 0; i < 32; i++) sumi += (int)qq[blk * 32 + i] * (int)(int8_t)kb[2 + i];
+                                    sumf += (float)sumi * (qd[blk] * f16_to_f32(dk));
+                                }
+                                acc = (acc_t)sumf;
+                            } else {
 #pragma omp simd reduction(+ : acc)
-                            for (int64_t c = 0; c < hd; c++) acc += (acc_t)qrow[c] * (acc_t)kr[c];
+                                for (int64_t c = 0; c < hd; c++) acc += (acc_t)qrow[c] * (acc_t)kr[c];
+                            }
                             float sv = (float)acc * scale;
                             if (p->logit_softcap != 0.0f) sv = p->logit_softcap * std::tanh(sv);
                             if (r) {
@@ -236,6 +283,28 @@ int flash_attn_impl(const b200_tensor* q, const b200_tensor* k, const b200_tenso
                                               (uint64_t)iq * dst->nb[2] + (uint64_t)b * dst->nb[3]);
                         if (mx == ninf) {  // every key masked (or no key): zeros
                             for (int64_t c = 0; c < hdv; c++) out[c] = 0.0f;
+                            continue;
+                        }
+                        if (acc16) {
+                            // streaming softmax in key order with an F16 output accumulator
+                            std::fill(o16.begin(), o16.end(), (uint16_t)0);
+                            float M = ninf, S = 0.0f;
+                            for (int64_t ik = 0; ik < kend; ik++) {
+                                const float sv = s[ik];
+                                if (sv == ninf) continue;
+                                float ms = 1.0f, vs = 1.0f;
+                                if (sv > M) {
+                                    ms = std::exp(M - sv);   // exp(-inf) = 0 on the first key
+                                    M = sv;
+                                    for (int64_t c = 0; c < hdv; c++) o16[c] = f32_to_f16(f16_to_f32(o16[c]) * ms);
+                                } else {
+                                    vs = std::exp(sv - M);
+                                }
+                                const float* vr = &Vf[(size_t)ik * hdv];
+                                for (int64_t c = 0; c < hdv; c++) o16[c] = f32_to_f16(f16_to_f32(o16[c]) + vr[c] * vs);
+                                S = S * ms + vs;
+                            }
+                            for (int64_t c = 0; c < hdv; c++) out[c] = f16_to_f32(o16[c]) / S;
                             continue;
                         }
                         std::fill(o.begin(), o.end(), (acc_t)0);
@@ -268,8 +337,24 @@ B200_API int orc_flash_attn_ext(const b200_tensor* q, const b200_tensor* k, cons
                                 const b200_fattn_ext* ext, int gold, int q_round_f16, int n_threads) {
     if (!q || !k || !v || !dst || !params) return B200_E_NULL;
     if (k->type != v->type) return B200_E_TYPE;
-    if (gold) return flash_attn_impl<double>(q, k, v, mask, dst, params, ext, q_round_f16, n_threads);
-    return flash_attn_impl<float>(q, k, v, mask, dst, params, ext, q_round_f16, n_threads);
+    OrcOptions opt;
+    opt.gold = gold, opt.q_round_f16 = q_round_f16, opt.n_threads = n_threads;
+    if (gold) return flash_attn_impl<double>(q, k, v, mask, dst, params, ext, opt);
+    return flash_attn_impl<float>(q, k, v, mask, dst, params, ext, opt);
+}
+
+// The same with every option: `flags` bit 0 = gold, bit 1 = do NOT round Q to F16, bit 2 = q_as_q8_0 (diagnostic),
+// bit 3 = acc_f16 (diagnostic); `rows` (may be NULL) lists the query rows to compute, other rows of dst are left alone.
+B200_API int orc_flash_attn_ext_opt(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                                    const b200_tensor* mask, const b200_tensor* dst, const b200_fattn_params* params,
+                                    const b200_fattn_ext* ext, int flags, int n_threads, const int32_t* rows, int n_rows) {
+    if (!q || !k || !v || !dst || !params) return B200_E_NULL;
+    if (k->type != v->type) return B200_E_TYPE;
+    OrcOptions opt;
+    opt.gold = flags & 1, opt.q_round_f16 = !(flags & 2), opt.q_as_q8_0 = (flags >> 2) & 1, opt.acc_f16 = (flags >> 3) & 1;
+    opt.n_threads = n_threads, opt.rows = rows, opt.n_rows = rows ? n_rows : 0;
+    if (opt.gold) return flash_attn_impl<double>(q, k, v, mask, dst, params, ext, opt);
+    return flash_attn_impl<float>(q, k, v, mask, dst, params, ext, opt);
 }
 
 // Q8_0 row quantisation as gguf-py quants.Q8_0.quantize_blocks does it (the library the

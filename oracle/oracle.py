@@ -40,6 +40,9 @@ def lib() -> C.CDLL:
         L.orc_flash_attn_ext.restype = C.c_int
         L.orc_flash_attn_ext.argtypes = [abi.TP, abi.TP, abi.TP, abi.TP, abi.TP, C.POINTER(abi.Params),
                                          C.POINTER(abi.Ext), C.c_int, C.c_int, C.c_int]
+        L.orc_flash_attn_ext_opt.restype = C.c_int
+        L.orc_flash_attn_ext_opt.argtypes = [abi.TP, abi.TP, abi.TP, abi.TP, abi.TP, C.POINTER(abi.Params),
+                                             C.POINTER(abi.Ext), C.c_int, C.c_int, C.c_void_p, C.c_int]
         L.orc_relpos_mask.restype = C.c_int
         L.orc_relpos_mask.argtypes = [abi.TP, abi.TP, C.c_float, C.c_int, C.c_void_p]
         L.orc_max_threads.restype = C.c_int
@@ -52,16 +55,18 @@ def _ptr(a):
 
 def flash_attn_ext(q, k, v, mask=None, *, scale, max_bias=0.0, softcap=0.0, kv_type=None, causal=False, n_past=0,
                    kv_len=None, q_v=None, r=None, r_type=None, relpos_bias_f32=False, gold=False,
-                   q_round_f16=True, n_threads=0):
+                   q_round_f16=True, n_threads=0, q_as_q8_0=False, acc_f16=False, rows=None):
     """Run the oracle on numpy arrays in numpy order: q (B,H,Tq,hd) f32|f16; k,v (Bk,Hkv,Lk,hd)
     f32|f16, or uint8 block rows (Bk,Hkv,Lk,hd/32*34) with kv_type=abi.Q8_0; mask (Bm,Hm,Tq,Lk) f16.
-    Arrays may be strided views.  Returns (B,Tq,H,hd) float32 (= ggml dst [hd,H,Tq,B])."""
+    Arrays may be strided views.  Returns (B,Tq,H,hd) float32 (= ggml dst [hd,H,Tq,B]).
+    `rows`: only these query rows are computed (the result still has Tq rows; the others are zero).
+    `q_as_q8_0`, `acc_f16`: diagnostic switches (see OrcOptions in fattn_oracle.cpp), never the oracle of record."""
     L = lib()
     tq = abi.from_numpy(q)
     tk = abi.from_numpy(k, kv_type)
     tv = abi.from_numpy(v, kv_type)
     B, H, Tq, hd = q.shape
-    out = np.empty((B, Tq, H, hd), np.float32)
+    out = np.zeros((B, Tq, H, hd), np.float32) if rows is not None else np.empty((B, Tq, H, hd), np.float32)
     td = abi.from_numpy(out)
     tm = abi.from_numpy(mask) if mask is not None else None
     p = abi.Params(float(scale), float(max_bias), float(softcap), 0)
@@ -77,8 +82,12 @@ def flash_attn_ext(q, k, v, mask=None, *, scale, max_bias=0.0, softcap=0.0, kv_t
         keep.append(kl)
         e.kv_len = kl.ctypes.data
     e.relpos_bias_f32 = int(bool(relpos_bias_f32))
-    rc = L.orc_flash_attn_ext(C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tm) if tm is not None else None,
-                              C.byref(td), C.byref(p), C.byref(e), int(gold), int(q_round_f16), int(n_threads))
+    flags = int(bool(gold)) | (0 if q_round_f16 else 2) | (4 if q_as_q8_0 else 0) | (8 if acc_f16 else 0)
+    rows_arr = np.ascontiguousarray(rows, np.int32) if rows is not None else None
+    rc = L.orc_flash_attn_ext_opt(C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tm) if tm is not None else None,
+                                  C.byref(td), C.byref(p), C.byref(e), flags, int(n_threads),
+                                  rows_arr.ctypes.data if rows_arr is not None else None,
+                                  len(rows_arr) if rows_arr is not None else 0)
     if rc != 0:
         raise RuntimeError(f"oracle rejected the operands: code {rc}")
     return out

@@ -84,6 +84,80 @@ def test_decode_through_slab(b200, orc, type_):
     kv.close()
 
 
+def _launch_on_views(b200, q, tk, tv, dst, scale, kv_len=None, causal=False):
+    """b200_fattn_launch with K/V descriptors straight from the allocator."""
+    tq, td = abi.from_torch(q), abi.from_torch(dst)
+    p = abi.Params(scale, 0.0, 0.0, 0)
+    e = abi.Ext()
+    e.causal = int(causal)
+    if kv_len is not None:
+        e.kv_len = kv_len.data_ptr()
+    L_ = b200.lib()
+    n = C.c_size_t(0)
+    assert L_.b200_fattn_workspace_bytes(C.byref(tq), C.byref(tk), C.byref(tv), None, C.byref(td), C.byref(p), C.byref(e), C.byref(n)) == 0
+    ws = torch.empty(max(n.value, 256), dtype=torch.uint8, device="cuda")
+    rc = L_.b200_fattn_launch(C.byref(tq), C.byref(tk), C.byref(tv), None, C.byref(td), C.byref(p), C.byref(e),
+                              ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L_.b200_strerror(rc)
+    return ws   # kept alive by the caller until the stream has been synchronised
+
+
+def test_llm_decode_loop_on_one_slab(b200, orc):
+    """The whole decode loop of the LLM runtimes on one Q8_0 cache (src/voxtral.cpp:1176-1224 around
+    core_attn::kv_self_attn, src/core/attention.h:840-867): causal prefill of 375 audio + 32 text tokens into the
+    cache, then 256 steps of (quantise-on-append at a DEVICE position per stream, single-token attention with a
+    DEVICE kv_len per stream), 8 streams, GQA 32/8, head_dim 128, nothing synchronised between steps.  After the
+    prefill the streams are cut to ragged lengths, so appends overwrite rows and every stream grows from its own
+    length.  The prefill result and decode steps 1, 128 and 256 are compared with the oracle run on a cache that was
+    quantised on the host."""
+    rng = np.random.default_rng(3)
+    S, H, Hkv, hd, T0, steps = 8, 32, 8, 128, 407, 256
+    scale = hd ** -0.5
+    kv = b200.KvCache(abi.Q8_0, hd, Hkv, n_layers=1, max_ctx=T0 + steps, n_streams=S)
+    k_pre = rng.standard_normal((S, Hkv, T0, hd)).astype(np.float32)
+    v_pre = rng.standard_normal((S, Hkv, T0, hd)).astype(np.float32)
+    kv.append(0, torch.from_numpy(k_pre).cuda(), torch.from_numpy(v_pre).cuda(), pos0=0)
+    # ---- prefill: every stream attends causally to its own 407 rows ----
+    qp = torch.from_numpy(rng.standard_normal((S, H, T0, hd)).astype(np.float16).astype(np.float32)).cuda()
+    out_p = torch.empty((S, T0, H, hd), dtype=torch.float32, device="cuda")
+    tk, tv = kv.view(0, T0)
+    keep = [_launch_on_views(b200, qp, tk, tv, out_p, scale, causal=True)]
+    torch.cuda.synchronize()
+    kq_pre, vq_pre = orc.quantize_q8_0(k_pre), orc.quantize_q8_0(v_pre)
+    for s_ in (0, 5):
+        ref = orc.flash_attn_ext(qp[s_:s_ + 1].cpu().numpy(), kq_pre[s_:s_ + 1], vq_pre[s_:s_ + 1], scale=scale,
+                                 kv_type=abi.Q8_0, causal=True)
+        assert_close(out_p[s_:s_ + 1].cpu().numpy(), ref, f"prefill, stream {s_}")
+    # ---- decode: ragged starting lengths, device-side positions ----
+    len0 = np.array([T0 - 5 * s_ for s_ in range(S)], np.int32)
+    pos = torch.from_numpy(len0.copy()).cuda()            # row the next token of each stream is written to
+    kv_len = pos + 1
+    k_new = rng.standard_normal((steps, S, Hkv, 1, hd)).astype(np.float32)
+    v_new = rng.standard_normal((steps, S, Hkv, 1, hd)).astype(np.float32)
+    q_all = rng.standard_normal((steps, S, H, 1, hd)).astype(np.float16).astype(np.float32)
+    dk, dv, dq = torch.from_numpy(k_new).cuda(), torch.from_numpy(v_new).cuda(), torch.from_numpy(q_all).cuda()
+    outs = torch.empty((steps, S, 1, H, hd), dtype=torch.float32, device="cuda")
+    tk, tv = kv.view(0, T0 + steps)
+    for t in range(steps):
+        kv.append(0, dk[t], dv[t], pos=pos)
+        keep.append(_launch_on_views(b200, dq[t], tk, tv, outs[t], scale, kv_len=kv_len))
+        pos += 1
+        kv_len += 1
+    torch.cuda.synchronize()
+    assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT and b200.lib().b200_device_status() == 0
+    for t in (0, 127, 255):
+        kq = np.zeros((S, Hkv, T0 + steps, hd // 32 * 34), np.uint8)
+        vq = np.zeros_like(kq)
+        for s_ in range(S):
+            L0 = int(len0[s_])
+            kq[s_, :, :L0], vq[s_, :, :L0] = kq_pre[s_, :, :L0], vq_pre[s_, :, :L0]
+            kq[s_, :, L0:L0 + t + 1] = orc.quantize_q8_0(k_new[:t + 1, s_, :, 0].transpose(1, 0, 2))
+            vq[s_, :, L0:L0 + t + 1] = orc.quantize_q8_0(v_new[:t + 1, s_, :, 0].transpose(1, 0, 2))
+        ref = orc.flash_attn_ext(q_all[t], kq, vq, scale=scale, kv_type=abi.Q8_0, kv_len=len0 + t + 1)
+        assert_close(outs[t].cpu().numpy(), ref, f"decode step {t + 1}")
+    kv.close()
+
+
 def test_copy_stream_forks_a_beam(b200):
     """kv_snapshot_pool semantics: after the copy the destination stream reads the source's first n rows, other
     streams and rows beyond n are untouched."""
