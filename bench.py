@@ -10,14 +10,30 @@ segments/s (whole job, all GPUs).  Inputs are synthetic N(0,1) F16 tensors (seed
 (737 MB) is larger than L2, so successive launches never hit in cache.  Under torchrun every rank runs
 the same per-GPU batch (weak scaling, no data-path collective).
 
-Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference operator
-(oracle/) on the host cores instead; the reference's own ggml kernels are not in its tree.
+Prints ONE JSON line (rank 0).  Besides the headline keys it carries
+  * `workloads`: the other configurations of the path (decode over F16 and Q8_0 caches, causal prefill over
+    a Q8_0 cache, the fused relative-position encoder), each measured in the same process for a few steps
+    with its own roofline figure and clock record (1-GPU runs only; `--no-extra` skips it);
+  * `strong`: the fixed 64-segment batch partitioned over the N GPUs by the library's own scheduler
+    (`b200_sched_run_batched`, one host worker thread per GPU inside ONE process), timed by wall clock on the
+    host after a device synchronise — the strong-scaling counterpart of the weak-scaling headline.
+
+`--impl reference` times the CPU restatement of the reference operator (oracle/) on the host cores instead;
+the reference's own ggml kernels are not in its tree.
+
+`--record-traffic CSV [CSV ...]` is not a benchmark: it reads ncu exports made with
+    ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --print-units base --clock-control none \
+        -k regex:<kernel> -s <skip> -c 1 --csv --log-file traffic_<W>_u<U>.csv python bench.py --workload W --units U \
+        --steps 1 --warmup 1 --no-cpu-baseline --no-e2e --no-graph --no-extra
+and rewrites the table of measured DRAM traffic per launch that `roofline.traffic` is taken from.
 """
 from __future__ import annotations
 
 import argparse
+import csv
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -37,32 +53,84 @@ WORKLOADS = {
                                           kv="f16", seed=1, unit_name="segment-steps"),
     "voxtral_decode_q8_0": dict(kind="decode", layers=30, units=8, H=32, Hkv=8, Tq=1, Lk=535, hd=128, kv="q8_0",
                                 seed=3, unit_name="stream-steps"),
-    # config 2, self-attention half: 5 beams of one segment over the pooled cell cache (448 private cells each,
+    # decoder self-attention: 5 beams of one segment over the pooled cell cache (448 private cells each,
     # padded to 2304), beam membership only in the F16 mask [n_kv, 5]
     "whisper_large_v3_decode_self": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=2304, hd=64,
                                          kv="f16", seed=1, unit_name="segment-steps", beam_cells=448),
-    # config 4, prefill half: 375 audio + 32 text tokens, causal, GQA 32/8 over a Q8_0 cache, 8 streams
+    # LLM prefill: 375 audio + 32 text tokens, causal, GQA 32/8 over a Q8_0 cache, 8 streams
     "voxtral_prefill_q8_0": dict(kind="prefill", layers=30, units=8, H=32, Hkv=8, Tq=407, Lk=407, hd=128, kv="q8_0",
                                  seed=3, unit_name="streams", causal=True),
-    # roofline probe, not a BASELINE config: the FastConformer dims without the rel-pos bias (plain hd-128 prefill)
+    # roofline probe, not one of the path's model configurations: the FastConformer dims without the rel-pos bias
     "hd128_prefill_probe": dict(kind="prefill", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128, kv="f16",
                                 seed=4, unit_name="utterances"),
     "parakeet_relpos_encoder": dict(kind="relpos", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128,
                                     kv="f16", seed=4, unit_name="utterances"),
 }
 
+# (workload, units per GPU or None for the workload's own) measured into the `workloads` object of a 1-GPU run
+EXTRA = [("whisper_large_v3_decode_cross", None), ("whisper_large_v3_decode_self", None), ("voxtral_decode_q8_0", 8),
+         ("voxtral_decode_q8_0", 256), ("voxtral_prefill_q8_0", None), ("parakeet_relpos_encoder", None)]
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel for one launch, from the ncu captures summarised
-# under profiles/ (bytes, units per GPU of the captured launch).  Traffic grows in proportion to the units, so the
-# bench scales it to its own launch size.
-NCU_TRAFFIC = {
-    "whisper_large_v3_encoder": (120.89e6, 8),
-    "whisper_large_v3_decode_cross": (497.06e6, 64),
-    "whisper_large_v3_decode_self": (760.78e6, 64),
-    "voxtral_decode_q8_0": (310.18e6, 256),
-    "parakeet_relpos_encoder": (103.11e6, 1),
-    "hd128_prefill_probe": (48.61e6, 1),
-}
+TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "dram_traffic.md")
+
+
+def read_traffic():
+    """{workload: (dram bytes read + written per launch, units in that launch)} from the table of ncu captures."""
+    out = {}
+    if not os.path.exists(TRAFFIC_TABLE):
+        return out
+    for ln in open(TRAFFIC_TABLE):
+        f = [x.strip() for x in ln.strip().strip("|").split("|")]
+        if len(f) >= 5 and f[0] in WORKLOADS and f[1].isdigit():
+            try:
+                out[f[0]] = (float(f[3]) + float(f[4]), int(f[1]))
+            except ValueError:
+                pass
+    return out
+
+
+def record_traffic(paths):
+    """Rewrites the traffic table from ncu CSV exports (see the module docstring for the capture command)."""
+    rows = {}
+    for path in paths:
+        text = open(path, errors="replace").read()
+        m = re.match(r"traffic_(\w+?)_u(\d+)\.csv$", os.path.basename(path))   # traffic_<workload>_u<units>.csv
+        if not m or m.group(1) not in WORKLOADS:
+            print(f"{path}: name it traffic_<workload>_u<units>.csv", file=sys.stderr)
+            continue
+        workload, units = m.group(1), int(m.group(2))
+        start = text.find('"ID"')
+        if start < 0:
+            print(f"{path}: no ncu CSV table found", file=sys.stderr)
+            continue
+        vals, kernel = {}, ""
+        for r in csv.DictReader(text[start:].splitlines()):
+            name = r.get("Metric Name", "")
+            if name in ("dram__bytes_read.sum", "dram__bytes_write.sum") and name not in vals:
+                vals[name] = float(r["Metric Value"].replace(",", ""))
+                kernel = r.get("Kernel Name", "")
+        if len(vals) == 2:
+            rows[workload] = (units, kernel.split("(")[0], vals["dram__bytes_read.sum"], vals["dram__bytes_write.sum"], os.path.basename(path))
+    old = {}
+    if os.path.exists(TRAFFIC_TABLE):
+        for ln in open(TRAFFIC_TABLE):
+            f = [x.strip() for x in ln.strip().strip("|").split("|")]
+            if len(f) >= 6 and f[0] in WORKLOADS and f[1].isdigit():
+                old[f[0]] = (int(f[1]), f[2], float(f[3]), float(f[4]), f[5])
+    old.update(rows)
+    with open(TRAFFIC_TABLE, "w") as f:
+        f.write("# DRAM traffic per launch of each workload's dominant kernel\n\n"
+                "`dram__bytes_read.sum` and `dram__bytes_write.sum` of ONE launch, from ncu captures of the command\n\n"
+                "    ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --print-units base --clock-control none \\\n"
+                "        -k regex:<kernel> -s <launches before it> -c 1 --csv --log-file gpurun_out/traffic_<workload>_u<units>.csv \\\n"
+                "        python bench.py --workload <workload> --units <units> --steps 1 --warmup 1 --no-cpu-baseline --no-e2e --no-graph --no-extra\n\n"
+                "written by `python bench.py --record-traffic gpurun_out/traffic_*.csv`.  `bench.py` scales a row to the units of\n"
+                "its own launch (every unit reads its own operands once and writes its own output: traffic grows in proportion).\n\n"
+                "| workload | units in the captured launch | kernel | bytes read | bytes written | capture |\n|---|---|---|---|---|---|\n")
+        for name in sorted(old):
+            u, k, rd, wr, src = old[name]
+            f.write(f"| {name} | {u} | {k} | {rd:.0f} | {wr:.0f} | {src} |\n")
+    print(f"wrote {TRAFFIC_TABLE}: {sorted(old)}")
 
 
 def peaks():
@@ -79,13 +147,13 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index, period_ms=200):
+        self.index, self.proc, self.lines, self.period_ms = index, None, [], period_ms
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                          "-lms", str(self.period_ms), "-i", str(self.index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.t.start()
@@ -255,6 +323,143 @@ def config_of(args, w, units):
             "l2": "inputs of one launch exceed L2" if w["kind"] == "prefill" else "L2 flushed between steps"}
 
 
+class DeviceWorkload:
+    """One workload resident on one GPU: operands, output, workspace, and `step()` = one pass over the layers."""
+
+    def __init__(self, b200, abi, torch, dev, w, units, seed_offset=0):
+        self.b200, self.torch, self.w, self.units, self.dev = b200, torch, w, units, dev
+        rng = np.random.default_rng(w["seed"] + seed_offset)
+        # generate a few units' worth on the host and tile them: cheap and still random-like
+        gen_units = min(units, 4)
+        q_np, k_np, v_np, extra = make_inputs_np(w, gen_units, rng)
+        rep = -(-units // gen_units)
+        def up(a):
+            t = torch.from_numpy(a).to(dev)
+            return t.repeat((rep,) + (1,) * (t.dim() - 1))[:units].contiguous()
+        q, k, v = up(q_np), up(k_np), up(v_np)
+        if w["kind"] == "decode":
+            # K/V live in cache slabs as the allocator lays them out: head-major rows, the row count per head
+            # rounded up to 32 so every head starts 16-byte aligned; the op sees a view of the first Lk rows.
+            ctx_rows = -(-w["Lk"] // 32) * 32
+            def slab(t):
+                buf = torch.zeros(t.shape[:2] + (ctx_rows, t.shape[3]), dtype=t.dtype, device=dev)
+                buf[:, :, : w["Lk"]] = t
+                return buf[:, :, : w["Lk"]]
+            k, v = slab(k), slab(v)
+        kw = dict(scale=scale_of(w))
+        if w["kv"] == "q8_0":
+            kw["kv_type"] = abi.Q8_0
+        if w["kind"] == "relpos":
+            kw["q_v"], kw["r"] = up(extra["q_v"]), torch.from_numpy(extra["r"]).to(dev)
+        if w.get("causal"):
+            kw["causal"], kw["n_past"] = True, 0
+        mask = None
+        if "beam_cells" in w:
+            from oracle import oracle as orc_mask   # input generation only: the beam-membership mask rule
+            L, beams = w["beam_cells"], w["Tq"]
+            cell_pos = np.full(w["Lk"], 10 ** 6, np.int32)
+            bits = np.zeros(w["Lk"], np.uint32)
+            for jb in range(beams):
+                cell_pos[jb * L:(jb + 1) * L], bits[jb * L:(jb + 1) * L] = np.arange(L), 1 << jb
+            m = orc_mask.whisper_beam_mask(cell_pos, bits, tok_seq=np.arange(beams), tok_pos=np.full(beams, L - 1))
+            mask = torch.from_numpy(m[None, None]).to(dev)
+        self.q, self.k, self.v, self.kw, self.mask = q, k, v, kw, mask
+        self.out = torch.empty((units, w["Tq"], w["H"], w["hd"]), dtype=torch.float32, device=dev)
+        ws_bytes = b200.workspace_bytes(q, k, v, mask, **kw)
+        self.ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        self.kernel_id, self.n_splits = b200.plan(q, k, v, mask, **kw)
+        self.launches_per_layer = 1 + (1 if (self.kernel_id == abi.KERNEL_DECODE_SPLIT and self.n_splits > 1 and ws_bytes) else 0)
+        if self.kernel_id == abi.KERNEL_PREFILL_TC5 and ws_bytes:
+            self.launches_per_layer += 1   # K and V conversion pre-pass (one launch for both)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if w["kind"] != "prefill" else None
+
+    def step(self, stream=None):
+        for _ in range(self.w["layers"]):
+            self.b200.flash_attn_ext(self.q, self.k, self.v, self.mask, out=self.out, workspace=self.ws, stream=stream, **self.kw)
+
+    def measure(self, steps, warmup, graph, barrier=lambda: None):
+        """CUDA-event time of `steps` steps after `warmup`; returns the per-step times in ms."""
+        torch = self.torch
+        self.step()                 # first call outside any capture (function attributes, tensor maps, lazy init)
+        torch.cuda.synchronize()
+        run_step = self.step
+        if graph:
+            # the layer loop is launch-bound from Python for the small decode shapes: capture one step
+            # (all layers) into a CUDA graph and replay it, as a runtime would
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.step()
+            run_step = g.replay
+        for _ in range(max(warmup, 0)):
+            run_step()
+        barrier()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s in range(steps):
+            if self.flush is not None:
+                self.flush.fill_(s & 0xFF)        # evict L2 between steps (outside the event pair)
+            ev[s][0].record()
+            run_step()
+            ev[s][1].record()
+        barrier()
+        return [a.elapsed_time(b) for a, b in ev]
+
+
+def roofline_of(abi, w, name, units, dw, step_ms, pk, traffic):
+    work = algorithmic_work(w, units)
+    launch_s = statistics.fmean(step_ms) * 1e-3 / w["layers"]
+    achieved = work["amount"] / launch_s / work["div"]
+    peak = pk["tensor"] if work["bound"] == "tensor" else pk["hbm"]
+    t = traffic.get(name)
+    return {"bound": work["bound"], "achieved": achieved, "peak": peak, "unit": work["unit"], "frac": achieved / peak,
+            "traffic": (t[0] * units / t[1]) if t else None,
+            "traffic_source": "ncu capture of one launch, scaled by units" if t else None,
+            "peak_source": f"{pk['src']} ({'sustained bf16 GEMM' if work['bound'] == 'tensor' else 'copy'})",
+            "kernel": abi.KERNEL_NAMES[dw.kernel_id], "n_splits": dw.n_splits, "launch_ms": launch_s * 1e3,
+            "algorithmic_per_launch": work["amount"]}
+
+
+def strong_scaling(b200, abi, torch, w, total_units, n_dev, steps, warmup):
+    """The fixed batch (`total_units`) partitioned over `n_dev` GPUs by the library's scheduler inside this one
+    process: each worker thread gets its contiguous share as ONE batch (one launch per layer over the share).
+    Inputs are resident per device before the clock starts; value = batch / wall time of a whole pass."""
+    parts = [b200.SegmentScheduler.partition(total_units, n_dev, d) for d in range(n_dev)]
+    work, graphs = {}, {}
+    for d, (first, count) in enumerate(parts):
+        if count:
+            with torch.cuda.device(d):
+                work[d] = DeviceWorkload(b200, abi, torch, torch.device("cuda", d), w, count, seed_offset=first)
+                work[d].step()
+                torch.cuda.synchronize(d)
+                # one pass over the layers as a CUDA graph, replayed by the worker thread on the scheduler's stream
+                graphs[d] = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graphs[d]):
+                    work[d].step()
+                torch.cuda.synchronize(d)
+    sched = b200.SegmentScheduler(devices=list(range(n_dev)))
+
+    def batch(device, first, count, stream):
+        assert count == work[device].units, "a worker's share arrives as one batch"
+        with torch.cuda.device(device), torch.cuda.stream(torch.cuda.ExternalStream(stream, device=device)):
+            graphs[device].replay()
+        return 0
+    times, owners = [], None
+    for it in range(warmup + steps):
+        for d in work:
+            torch.cuda.synchronize(d)
+        t0 = time.perf_counter()
+        failed, owners = sched.run_batched(total_units, max(c for _, c in parts), batch, steal=False)   # returns after every worker synchronised its stream
+        dt = time.perf_counter() - t0
+        assert failed == 0
+        if it >= warmup:
+            times.append(dt)
+    sched.close()
+    dt = statistics.fmean(times)
+    return {"value": total_units / dt, "unit": f"{w['unit_name']}/s", "batch": total_units, "n_gpus": n_dev,
+            "ms_per_pass": dt * 1e3, "units_per_gpu": [c for _, c in parts], "workers_used": sorted(set(owners)),
+            "timing": "host wall clock around b200_sched_run_batched (every worker synchronises its stream before it returns)",
+            "api": "b200_sched_run_batched: one host thread per GPU in one process, contiguous shares, one launch per layer per share"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -265,10 +470,16 @@ def main():
     ap.add_argument("--units", type=int, default=0, help="units per GPU (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the `workloads` object (the other configurations)")
+    ap.add_argument("--no-strong", action="store_true", help="skip the scheduler-partitioned fixed batch")
     ap.add_argument("--kernel", default="auto", choices=["auto", "tile"])
     ap.add_argument("--decode-splits", type=int, default=0, help="force the split count of the split-KV decode kernel (A/B runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch each layer from Python instead of replaying a CUDA graph")
+    ap.add_argument("--record-traffic", nargs="+", metavar="CSV", help="rewrite the DRAM traffic table from ncu CSV exports and exit")
     args = ap.parse_args()
+    if args.record_traffic:
+        record_traffic(args.record_traffic)
+        return
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -288,96 +499,31 @@ def main():
     b200.lib()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    host_group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+        host_group = dist.new_group(backend="gloo")   # host-side barrier for the phase in which rank 0 drives every GPU
     if args.kernel == "tile":
         b200.lib().b200_set_kernel_override(abi.KERNEL_TILE_MMA)
     if args.decode_splits:
         b200.lib().b200_set_decode_splits(args.decode_splits)
 
     units = args.units or w["units"]
-    rng = np.random.default_rng(w["seed"] + 1000 * rank)
-    # generate one unit's worth on the host and tile it with per-unit sign flips/rolls: cheap and still random-like
-    gen_units = min(units, 4)
-    q_np, k_np, v_np, extra = make_inputs_np(w, gen_units, rng)
-    rep = -(-units // gen_units)
-    def up(a):
-        t = torch.from_numpy(a).to(dev)
-        t = t.repeat((rep,) + (1,) * (t.dim() - 1))[:units].contiguous()
-        return t
-    q, k, v = up(q_np), up(k_np), up(v_np)
-    if w["kind"] == "decode":
-        # K/V live in cache slabs as the allocator lays them out: head-major rows, the row count per head
-        # rounded up to 32 so every head starts 16-byte aligned; the op sees a view of the first Lk rows.
-        ctx_rows = -(-w["Lk"] // 32) * 32
-        def slab(t):
-            buf = torch.zeros(t.shape[:2] + (ctx_rows, t.shape[3]), dtype=t.dtype, device=dev)
-            buf[:, :, : w["Lk"]] = t
-            return buf[:, :, : w["Lk"]]
-        k, v = slab(k), slab(v)
-    kw = dict(scale=scale_of(w))
-    if w["kv"] == "q8_0":
-        kw["kv_type"] = abi.Q8_0
-    if w["kind"] == "relpos":
-        kw["q_v"], kw["r"] = up(extra["q_v"]), torch.from_numpy(extra["r"]).to(dev)
-    if w.get("causal"):
-        kw["causal"], kw["n_past"] = True, 0
-    mask = None
-    if "beam_cells" in w:
-        from oracle import oracle as orc_mask
-        L, beams = w["beam_cells"], w["Tq"]
-        cell_pos = np.full(w["Lk"], 10 ** 6, np.int32)
-        bits = np.zeros(w["Lk"], np.uint32)
-        for jb in range(beams):
-            cell_pos[jb * L:(jb + 1) * L], bits[jb * L:(jb + 1) * L] = np.arange(L), 1 << jb
-        m = orc_mask.whisper_beam_mask(cell_pos, bits, tok_seq=np.arange(beams), tok_pos=np.full(beams, L - 1))
-        mask = torch.from_numpy(m[None, None]).to(dev)
-    out = torch.empty((units, w["Tq"], w["H"], w["hd"]), dtype=torch.float32, device=dev)
-    ws_bytes = b200.workspace_bytes(q, k, v, mask, **kw)
-    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    kernel_id, n_splits = b200.plan(q, k, v, mask, **kw)
-    launches_per_layer = 1 + (1 if (kernel_id == abi.KERNEL_DECODE_SPLIT and n_splits > 1) else 0)
-    if kernel_id == abi.KERNEL_PREFILL_TC5 and ws_bytes:
-        launches_per_layer += 2   # K and V conversion pre-pass
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if w["kind"] != "prefill" else None
-
-    def step():
-        for _ in range(w["layers"]):
-            b200.flash_attn_ext(q, k, v, mask, out=out, workspace=ws, **kw)
+    dw = DeviceWorkload(b200, abi, torch, dev, w, units, seed_offset=1000 * rank)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    step()                      # first call outside any capture (function attributes, tensor maps, lazy init)
+    sampler = ClockSampler(local, period_ms=50)
+    dw.step()
     torch.cuda.synchronize()
-    run_step = step
-    if not args.no_graph:
-        # the layer loop is launch-bound from Python for the small decode shapes: capture one step
-        # (all layers) into a CUDA graph and replay it, as a runtime would
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        run_step = graph.replay
-    for _ in range(max(args.warmup, 0)):
-        run_step()
-    barrier()
-    sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    for s in range(args.steps):
-        if flush is not None:
-            flush.fill_(s & 0xFF)        # evict L2 between steps (outside the event pair)
-        ev[s][0].record()
-        run_step()
-        ev[s][1].record()
-    barrier()
+    step_ms = dw.measure(args.steps, args.warmup, not args.no_graph, barrier)
     clocks = sampler.stop() if rank == 0 else None
-    step_ms = [a.elapsed_time(b) for a, b in ev]
     total_ms = float(sum(step_ms))
     if world > 1:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
@@ -389,16 +535,16 @@ def main():
     # ---- end to end: host buffers through the C-ABI host entry point, H2D + D2H inside the timed region ----
     e2e = None
     if not args.no_e2e:
-        e2e_units = min(units, 16 if w["kind"] == "prefill" else units)
+        e2e_units = units
         affinity0 = os.sched_getaffinity(0)
         near_cpus = gpu_local_cpus(dev.index if dev.index is not None else 0)
         if near_cpus:
             os.sched_setaffinity(0, near_cpus)   # staging buffers next to the GPU; restored after the measurement
-        hq, hk, hv = (x[:e2e_units].contiguous().cpu().pin_memory() for x in (q, k, v))
-        hkw = dict(kw)
+        hq, hk, hv = (x[:e2e_units].contiguous().cpu().pin_memory() for x in (dw.q, dw.k, dw.v))
+        hkw = dict(dw.kw)
         if w["kind"] == "relpos":
-            hkw["q_v"], hkw["r"] = kw["q_v"][:e2e_units].cpu().pin_memory(), kw["r"].cpu().pin_memory()
-        hmask = mask.cpu().pin_memory() if mask is not None else None
+            hkw["q_v"], hkw["r"] = dw.kw["q_v"][:e2e_units].cpu().pin_memory(), dw.kw["r"].cpu().pin_memory()
+        hmask = dw.mask.cpu().pin_memory() if dw.mask is not None else None
         hout = torch.empty((e2e_units, w["Tq"], w["H"], w["hd"]), dtype=torch.float32).pin_memory()
         e2e_layers = w["layers"]
         def e2e_step():
@@ -424,6 +570,17 @@ def main():
         e2e["host_cpus"] = f"{len(near_cpus)} of {len(affinity0)} (NUMA-local to the GPU)" if near_cpus else f"{len(affinity0)} (topology unknown)"
         os.sched_setaffinity(0, affinity0)
         b200.lib().b200_host_arena_release()
+        del hq, hk, hv, hout
+
+    # ---- strong scaling: the fixed batch over all N GPUs, driven by the library's scheduler from rank 0 alone ----
+    strong = None
+    if not args.no_strong and w["kind"] in ("prefill", "relpos") and not args.units:
+        barrier()
+        if rank == 0:
+            strong = strong_scaling(b200, abi, torch, w, w["units"] if w["kind"] == "prefill" else 16, world,
+                                    steps=max(1, min(args.steps, 5)), warmup=2)
+        if world > 1:
+            dist.barrier(group=host_group)   # the other ranks wait on the host: no kernel of theirs occupies a GPU meanwhile
 
     if rank != 0:
         if world > 1:
@@ -431,26 +588,51 @@ def main():
         return
 
     pk = peaks()
-    work = algorithmic_work(w, units)
-    launch_s = (sum(step_ms) / args.steps) * 1e-3 / w["layers"]
-    achieved = work["amount"] / launch_s / work["div"]
-    peak = pk["tensor"] if work["bound"] == "tensor" else pk["hbm"]
-    roofline = {"bound": work["bound"], "achieved": achieved, "peak": peak, "unit": work["unit"],
-                "frac": achieved / peak,
-                "traffic": (NCU_TRAFFIC[args.workload][0] * units / NCU_TRAFFIC[args.workload][1]
-                            if args.workload in NCU_TRAFFIC else None),
-                "traffic_source": "ncu capture under profiles/, scaled by units" if args.workload in NCU_TRAFFIC else None,
-                "peak_source": f"{pk['src']} ({'sustained bf16 GEMM' if work['bound'] == 'tensor' else 'copy'})",
-                "kernel": abi.KERNEL_NAMES[kernel_id], "launch_ms": launch_s * 1e3,
-                "algorithmic_per_launch": work["amount"]}
+    traffic = read_traffic()
+    roofline = roofline_of(abi, w, args.workload, units, dw, step_ms, pk, traffic)
     line = {
         "metric": f"attention {w['unit_name']}/s ({args.workload})", "value": value, "unit": f"{w['unit_name']}/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 operands, f32 softmax/accumulate" if w["kv"] == "f16" else "q8_0 KV dequantised in-kernel, f32 softmax/accumulate",
         "data": "synthetic", "config": config_of(args, w, units), "roofline": roofline, "clocks": clocks,
-        "gpu_launches": launches_per_layer * w["layers"] * args.steps, "e2e": e2e,
+        "gpu_launches": dw.launches_per_layer * w["layers"] * args.steps, "e2e": e2e,
     }
+    if strong is not None:
+        line["strong"] = strong
+
+    # ---- the other configurations of the path, a few steps each (single-GPU runs) ----
+    if not args.no_extra and world == 1 and not args.units and args.workload == "whisper_large_v3_encoder":
+        del dw
+        torch.cuda.empty_cache()
+        extra = {}
+        for name, u in EXTRA:
+            xw = WORKLOADS[name]
+            xu = u or xw["units"]
+            key = name if u is None else f"{name}@{xu}"
+            try:
+                xdw = DeviceWorkload(b200, abi, torch, dev, xw, xu)
+                xs = ClockSampler(local, period_ms=50)
+                xdw.step()
+                torch.cuda.synchronize()
+                xs.start()
+                xms = xdw.measure(5, 3, True, torch.cuda.synchronize)
+                # short workloads: keep the device busy long enough for a few clock samples
+                t_end = time.perf_counter() + 0.4
+                while time.perf_counter() < t_end:
+                    xdw.step()
+                    torch.cuda.synchronize()
+                xc = xs.stop()
+                xms_mean = statistics.fmean(xms)
+                extra[key] = {"value": xu / (xms_mean * 1e-3), "unit": f"{xw['unit_name']}/s", "units_per_gpu": xu,
+                              "ms_per_step": xms_mean, "steps": 5, "warmup": 3,
+                              "roofline": roofline_of(abi, xw, name, xu, xdw, xms, pk, traffic), "clocks": xc,
+                              "gpu_launches": xdw.launches_per_layer * xw["layers"] * 5}
+                del xdw
+                torch.cuda.empty_cache()
+            except Exception as exc:   # one failing configuration must not take the headline line with it
+                extra[key] = {"error": f"{type(exc).__name__}: {exc}"}
+        line["workloads"] = extra
     if not args.no_cpu_baseline:
         val, sample, cores = cpu_sample(w, budget_s=12.0)
         line["cpu_baseline"] = {"value": val, "unit": f"{w['unit_name']}/s", "cores": cores, "kind": "port", "sample": sample}

@@ -66,6 +66,7 @@ class KvConfig(C.Structure):
 
 
 UNIT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p)
+BATCH_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p)
 
 TP = C.POINTER(Tensor)
 
@@ -98,6 +99,7 @@ SYMBOLS = {
     "b200_sched_create": (C.c_int, [C.POINTER(C.c_int), C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "b200_sched_destroy": (None, [C.c_void_p]),
     "b200_sched_run": (C.c_int, [C.c_void_p, C.c_int, UNIT_FN, C.c_void_p, C.POINTER(C.c_int)]),
+    "b200_sched_run_batched": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, BATCH_FN, C.c_void_p, C.POINTER(C.c_int)]),
     "b200_sched_partition": (None, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
 }
 

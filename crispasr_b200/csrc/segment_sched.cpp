@@ -101,9 +101,28 @@ B200_API void b200_sched_destroy(b200_sched* s) {
     delete s;
 }
 
+namespace {
+struct UnitAsBatch {
+    b200_unit_fn fn;
+    void* user;
+};
+int unit_as_batch(void* user, int device, int first_unit, int n_units, void* cuda_stream) {
+    (void)n_units;   // always 1: b200_sched_run hands out single units
+    UnitAsBatch* u = (UnitAsBatch*)user;
+    return u->fn(u->user, device, first_unit, cuda_stream);
+}
+}  // namespace
+
 B200_API int b200_sched_run(b200_sched* s, int n_units, b200_unit_fn fn, void* user, int* unit_device) {
     if (!s || !fn) return B200_E_NULL;
-    if (n_units < 0) return B200_E_SHAPE;
+    UnitAsBatch u{fn, user};
+    return b200_sched_run_batched(s, n_units, 1, 1, unit_as_batch, &u, unit_device);
+}
+
+B200_API int b200_sched_run_batched(b200_sched* s, int n_units, int max_batch, int steal, b200_batch_fn fn, void* user,
+                                    int* unit_device) {
+    if (!s || !fn) return B200_E_NULL;
+    if (n_units < 0 || max_batch < 1) return B200_E_SHAPE;
     const int W = s->n_workers;
     std::vector<std::atomic<int>> cursor(W);
     std::vector<int> range_end(W);
@@ -116,14 +135,26 @@ B200_API int b200_sched_run(b200_sched* s, int n_units, b200_unit_fn fn, void* u
     std::vector<int> done_by(n_units, -1);
     std::atomic<int> outstanding(n_units), failed(0), cuda_error(0), alive(W);
     std::mutex mu;
-    std::deque<std::pair<int, int>> retry;  // (unit, worker that failed it)
+    struct Run {
+        int first, count, failed_by;
+    };
+    std::deque<Run> retry;  // runs whose callback failed once, with the worker that failed them
+    std::vector<std::atomic<int>> dead(W);   // workers that could not bind their device
+    for (int w = 0; w < W; w++) dead[w].store(0);
 
-    auto next_fresh = [&](int w) -> int {
-        for (int k = 0; k < W; k++) {  // own range first, then victims in ring order
+    // A run of up to max_batch consecutive units: from the worker's own range first, then (if stealing is on) from
+    // the other ranges in ring order.  A run never crosses a range border, so what a worker is handed is always a
+    // contiguous slice of one static share.
+    auto next_fresh = [&](int w, int* count) -> int {
+        for (int k = 0; k < W; k++) {
             const int v = (w + k) % W;
+            if (k > 0 && !steal && !dead[v].load(std::memory_order_relaxed)) continue;   // a dead worker's share is always up for grabs
             if (cursor[v].load(std::memory_order_relaxed) >= range_end[v]) continue;
-            const int u = cursor[v].fetch_add(1);
-            if (u < range_end[v]) return u;
+            const int u = cursor[v].fetch_add(max_batch);
+            if (u < range_end[v]) {
+                *count = range_end[v] - u < max_batch ? range_end[v] - u : max_batch;
+                return u;
+            }
         }
         return -1;
     };
@@ -134,17 +165,19 @@ B200_API int b200_sched_run(b200_sched* s, int n_units, b200_unit_fn fn, void* u
             // this worker cannot run; the others steal its range
             cuda_error.store(1);
             cudaGetLastError();
+            dead[w].store(1);
             alive.fetch_sub(1);
             return;
         }
         while (outstanding.load() > 0) {
-            int unit = next_fresh(w);
+            int count = 0;
+            int unit = next_fresh(w, &count);
             bool is_retry = false;
             if (unit < 0) {
                 std::lock_guard<std::mutex> lk(mu);
                 for (auto it = retry.begin(); it != retry.end(); ++it) {
-                    if (it->second != w || alive.load() == 1) {
-                        unit = it->first;
+                    if (it->failed_by != w || alive.load() == 1) {
+                        unit = it->first, count = it->count;
                         retry.erase(it);
                         is_retry = true;
                         break;
@@ -155,16 +188,16 @@ B200_API int b200_sched_run(b200_sched* s, int n_units, b200_unit_fn fn, void* u
                 std::this_thread::sleep_for(std::chrono::microseconds(50));
                 continue;
             }
-            const int rc = fn(user, dev, unit, (void*)s->streams[w]);
+            const int rc = fn(user, dev, unit, count, (void*)s->streams[w]);
             if (rc == 0) {
-                done_by[unit] = w;
-                outstanding.fetch_sub(1);
+                for (int u = unit; u < unit + count; u++) done_by[u] = w;
+                outstanding.fetch_sub(count);
             } else if (!is_retry) {
                 std::lock_guard<std::mutex> lk(mu);
-                retry.emplace_back(unit, w);
+                retry.push_back(Run{unit, count, w});
             } else {
-                failed.fetch_add(1);
-                outstanding.fetch_sub(1);
+                failed.fetch_add(count);
+                outstanding.fetch_sub(count);
             }
         }
         if (!s->host_only && cudaStreamSynchronize(s->streams[w]) != cudaSuccess) {

@@ -220,6 +220,21 @@ class SegmentScheduler:
             raise _err(rc, "b200_sched_run")
         return rc, list(owners)[:n_units]
 
+    def run_batched(self, n_units, max_batch, fn, steal=True):
+        """fn(device, first_unit, n_units, stream) -> int (0 ok): runs of up to `max_batch` consecutive units per call.
+        Returns (n_failed, worker-per-unit list)."""
+        def tramp(_user, device, first, count, stream):
+            try:
+                return int(fn(device, first, count, stream) or 0)
+            except Exception:  # a raising batch is a failed batch, never an abort
+                return 1
+        cb = abi.BATCH_FN(tramp)
+        owners = (C.c_int * max(n_units, 1))()
+        rc = _lib().b200_sched_run_batched(self._h, n_units, int(max_batch), int(bool(steal)), cb, None, owners)
+        if rc < 0:
+            raise _err(rc, "b200_sched_run_batched")
+        return rc, list(owners)[:n_units]
+
     @staticmethod
     def partition(n_units, n_workers, w):
         f, c = C.c_int(0), C.c_int(0)

@@ -308,6 +308,20 @@ B200_API void b200_sched_destroy(b200_sched* s);
  * else [n_units]) receives the worker index that completed each unit, -1 for a failed unit.
  * Returns the number of failed units (>= 0) or a negative code. */
 B200_API int b200_sched_run(b200_sched* s, int n_units, b200_unit_fn fn, void* user, int* unit_device);
+/*
+ * b200_sched_run_batched — the same scheduler for callers that batch: the callback receives a RUN of up to
+ * `max_batch` consecutive units (never crossing the border of a worker's static share) and processes it as one
+ * batch, i.e. one kernel launch per layer over all units of the run (units concatenated on ne[3], ragged lengths
+ * through ext->kv_len / ext->q_len; see b200_batch_* below).  This is what lets several slices of
+ * CrispasrBackend::encode_slice / decode_slice (examples/cli/crispasr_backend.h:181-230) share a launch per GPU
+ * instead of one launch each.  max_batch >= the share size hands each worker its whole share at once;
+ * `steal` = 0 keeps every unit on the worker that owns it statically (resident per-device inputs), non-zero lets
+ * idle workers take runs from the others.  A run whose callback fails is retried once, whole, on another worker.
+ * Every worker synchronises its stream before the call returns.  Returns the number of failed units.
+ */
+typedef int (*b200_batch_fn)(void* user, int device, int first_unit, int n_units, void* cuda_stream);
+B200_API int b200_sched_run_batched(b200_sched* s, int n_units, int max_batch, int steal, b200_batch_fn fn, void* user,
+                                    int* unit_device);
 /* Static part of the partition: first unit and count owned by worker `w` of `n_workers`. */
 B200_API void b200_sched_partition(int n_units, int n_workers, int w, int* first, int* count);
 

@@ -203,3 +203,41 @@ def test_scheduler_steals_from_slow_worker(b200):
     assert failed == 0
     assert any(o == 1 for o in owners[:8]), "the idle worker never stole from the busy one"
     s.close()
+
+
+def test_batched_scheduler_hands_out_contiguous_runs(b200):
+    """b200_sched_run_batched: runs of consecutive units, never across the border of a worker's static share;
+    max_batch >= share size gives each worker its share as one batch; without stealing every unit stays with its
+    owner; a failing run is retried whole on another worker."""
+    s = b200.SegmentScheduler(n_host_workers=4)
+    calls = []
+    lock = threading.Lock()
+
+    def batch(dev, first, count, stream):
+        with lock:
+            calls.append((first, count))
+        return 0
+    failed, owners = s.run_batched(64, 64, batch, steal=False)
+    assert failed == 0 and sorted(calls) == [(0, 16), (16, 16), (32, 16), (48, 16)]
+    assert owners == [u // 16 for u in range(64)]
+    calls.clear()
+    failed, owners = s.run_batched(23, 4, batch, steal=True)
+    assert failed == 0 and sorted(u for f, c in calls for u in range(f, f + c)) == list(range(23))
+    borders = {b200.SegmentScheduler.partition(23, 4, w)[0] for w in range(4)}
+    for f, c in calls:
+        assert 1 <= c <= 4 and not any(f < b < f + c for b in borders), "a run crossed a share border"
+    # a run that fails once is retried as a whole somewhere else; one that always fails is reported per unit
+    tried = {}
+
+    def flaky(dev, first, count, stream):
+        me = threading.get_ident()
+        with lock:
+            tried.setdefault(first, []).append(me)
+            n = len(tried[first])
+        if first == 8 and n == 1:
+            return 3
+        return 7 if first == 12 else 0
+    failed, owners = s.run_batched(16, 4, flaky, steal=True)
+    assert failed == 4 and owners[12:16] == [-1] * 4 and all(o >= 0 for o in owners[:12])
+    assert len(tried[8]) == 2 and tried[8][0] != tried[8][1]
+    s.close()
