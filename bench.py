@@ -57,18 +57,30 @@ WORKLOADS = {
     # padded to 2304), beam membership only in the F16 mask [n_kv, 5]
     "whisper_large_v3_decode_self": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=2304, hd=64,
                                          kv="f16", seed=1, unit_name="segment-steps", beam_cells=448),
+    # the same step over a pool as a running beam search leaves it: 3584 cells, the 5 beams share a 224-token prefix
+    # and own 224 private cells each, scattered over the pool.  "dense" is the reference's form (every beam row scans
+    # every pooled cell through the F16 membership mask), "index" makes each beam a batch entry that gathers its own
+    # 448 cells through ext->kv_index.  Algorithmic bytes of both: the 1344 live cells, read once.
+    "whisper_large_v3_decode_self_pool_dense": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=3584, hd=64,
+                                                    kv="f16", seed=1, unit_name="segment-steps", pool=(224, 224, "dense")),
+    "whisper_large_v3_decode_self_pool_index": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=3584, hd=64,
+                                                    kv="f16", seed=1, unit_name="segment-steps", pool=(224, 224, "index")),
     # LLM prefill: 375 audio + 32 text tokens, causal, GQA 32/8 over a Q8_0 cache, 8 streams
     "voxtral_prefill_q8_0": dict(kind="prefill", layers=30, units=8, H=32, Hkv=8, Tq=407, Lk=407, hd=128, kv="q8_0",
                                  seed=3, unit_name="streams", causal=True),
     # roofline probe, not one of the path's model configurations: the FastConformer dims without the rel-pos bias
     "hd128_prefill_probe": dict(kind="prefill", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128, kv="f16",
                                 seed=4, unit_name="utterances"),
+    # the same for head_dim 64: the encoder kernel with 48 KV tiles per CTA instead of 12 (set-up amortised)
+    "hd64_prefill_probe": dict(kind="prefill", layers=8, units=4, H=20, Hkv=20, Tq=6000, Lk=6000, hd=64, kv="f16",
+                               seed=2, unit_name="utterances"),
     "parakeet_relpos_encoder": dict(kind="relpos", layers=24, units=2, H=8, Hkv=8, Tq=7500, Lk=7500, hd=128,
                                     kv="f16", seed=4, unit_name="utterances"),
 }
 
 # (workload, units per GPU or None for the workload's own) measured into the `workloads` object of a 1-GPU run
-EXTRA = [("whisper_large_v3_decode_cross", None), ("whisper_large_v3_decode_self", None), ("voxtral_decode_q8_0", 8),
+EXTRA = [("whisper_large_v3_decode_cross", None), ("whisper_large_v3_decode_self", None),
+         ("whisper_large_v3_decode_self_pool_dense", None), ("whisper_large_v3_decode_self_pool_index", None), ("voxtral_decode_q8_0", 8),
          ("voxtral_decode_q8_0", 256), ("voxtral_prefill_q8_0", None), ("parakeet_relpos_encoder", None)]
 
 TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "dram_traffic.md")
@@ -218,6 +230,8 @@ def algorithmic_work(w, units):
         return dict(bound="tensor", amount=flops, unit="TFLOP/s", div=1e12)
     row = w["hd"] * 2 if w["kv"] == "f16" else w["hd"] // 32 * 34
     rows = w["Tq"] * w["beam_cells"] if "beam_cells" in w else w["Lk"]    # valid cells only
+    if "pool" in w:
+        rows = w["pool"][0] + w["Tq"] * w["pool"][1]                      # live cells: the shared prefix once, every private suffix
     kv_bytes = 2.0 * rows * w["Hkv"] * row * units
     qo_bytes = units * w["H"] * w["Tq"] * w["hd"] * (2 + 4)
     return dict(bound="hbm", amount=kv_bytes + qo_bytes, unit="GB/s", div=1e9)
@@ -363,8 +377,32 @@ class DeviceWorkload:
                 cell_pos[jb * L:(jb + 1) * L], bits[jb * L:(jb + 1) * L] = np.arange(L), 1 << jb
             m = orc_mask.whisper_beam_mask(cell_pos, bits, tok_seq=np.arange(beams), tok_pos=np.full(beams, L - 1))
             mask = torch.from_numpy(m[None, None]).to(dev)
+        if "pool" in w:
+            prefix, suffix, form = w["pool"]
+            beams, n_cells = w["Tq"], w["Lk"]
+            prng = np.random.default_rng(12345)
+            slots = prng.permutation(n_cells)[:prefix + beams * suffix]
+            cell_pos, bits = np.full(n_cells, -1, np.int32), np.zeros(n_cells, np.uint32)
+            cell_pos[slots[:prefix]], bits[slots[:prefix]] = np.arange(prefix), (1 << beams) - 1
+            for jb in range(beams):
+                sl = slots[prefix + jb * suffix: prefix + (jb + 1) * suffix]
+                cell_pos[sl], bits[sl] = prefix + np.arange(suffix), 1 << jb
+            tok_seq, tok_pos = np.arange(beams, dtype=np.int32), np.full(beams, prefix + suffix - 1, np.int32)
+            if form == "dense":
+                from oracle import oracle as orc_mask   # input generation only: the beam-membership mask rule
+                mask = torch.from_numpy(orc_mask.whisper_beam_mask(cell_pos, bits, tok_seq, tok_pos)[None, None]).to(dev)
+            else:
+                stride = prefix + suffix
+                idx, lens = np.zeros((beams, stride), np.int32), np.zeros(beams, np.int32)
+                rc = b200.lib().b200_beam_cells_to_index(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data,
+                                                         tok_pos.ctypes.data, beams, idx.ctypes.data, stride, lens.ctypes.data)
+                assert rc == 0
+                # every beam of every segment is a batch entry; the beams of a segment share its pool (B / Bk = beams)
+                q = q.permute(0, 2, 1, 3).reshape(units * beams, w["H"], 1, w["hd"]).contiguous()
+                kw["kv_index"] = torch.from_numpy(np.tile(idx, (units, 1))).to(dev)
+                kw["kv_len"] = torch.from_numpy(np.tile(lens, units)).to(dev)
         self.q, self.k, self.v, self.kw, self.mask = q, k, v, kw, mask
-        self.out = torch.empty((units, w["Tq"], w["H"], w["hd"]), dtype=torch.float32, device=dev)
+        self.out = torch.empty((q.shape[0], q.shape[2], w["H"], w["hd"]), dtype=torch.float32, device=dev)
         ws_bytes = b200.workspace_bytes(q, k, v, mask, **kw)
         self.ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
         self.kernel_id, self.n_splits = b200.plan(q, k, v, mask, **kw)

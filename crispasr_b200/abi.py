@@ -50,7 +50,9 @@ class Ext(C.Structure):
         ("n_past", C.c_int32),
         ("kv_len", C.c_void_p),
         ("relpos_bias_f32", C.c_int32),
-        ("reserved", C.c_int32),
+        ("kv_index_stride", C.c_int32),
+        ("kv_index", C.c_void_p),
+        ("q_len", C.c_void_p),
     ]
 
 
@@ -63,6 +65,12 @@ class KvConfig(C.Structure):
         ("max_ctx", C.c_int32),
         ("n_streams", C.c_int32),
     ]
+
+
+class TraceRecord(C.Structure):
+    _fields_ = [("kernel", C.c_int32), ("n_splits", C.c_int32), ("head_dim", C.c_int32), ("q_len", C.c_int32),
+                ("kv_len", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("n_batch", C.c_int32),
+                ("kv_type", C.c_int32), ("ms", C.c_float)]
 
 
 UNIT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p)
@@ -89,6 +97,8 @@ SYMBOLS = {
     "b200_last_kernel": (C.c_int, []),
     "b200_device_status": (C.c_int, []),
     "b200_device_status_reset": (C.c_int, []),
+    "b200_trace_enable": (C.c_int, [C.c_int]),
+    "b200_trace_read": (C.c_int, [C.POINTER(TraceRecord), C.c_int, C.POINTER(C.c_int)]),
     "b200_test_bounded_wait": (C.c_int, [C.c_int, C.c_void_p]),
     "b200_kv_create": (C.c_int, [C.POINTER(KvConfig), C.POINTER(C.c_void_p)]),
     "b200_kv_destroy": (None, [C.c_void_p]),
@@ -96,6 +106,23 @@ SYMBOLS = {
     "b200_kv_view": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, TP, TP]),
     "b200_kv_append": (C.c_int, [C.c_void_p, C.c_int, TP, TP, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200_kv_copy_stream": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p]),
+    "b200_beam_cells_to_index": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "b200_relpos_table": (C.c_int, [TP, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200_relpos_cache_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "b200_relpos_cache_destroy": (None, [C.c_void_p]),
+    "b200_relpos_cache_bytes": (C.c_size_t, [C.c_void_p]),
+    "b200_relpos_cache_get": (C.c_int, [C.c_void_p, C.c_int, C.c_int, TP, C.c_int, C.c_void_p, TP, C.POINTER(C.c_int)]),
+    "b200_batch_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "b200_batch_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "b200_batch_destroy": (None, [C.c_void_p]),
+    "b200_batch_add": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "b200_batch_set": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "b200_batch_advance": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200_batch_remove": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200_batch_span": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "b200_batch_unit": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200_batch_lengths": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "b200_batch_tables": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "b200_sched_create": (C.c_int, [C.POINTER(C.c_int), C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "b200_sched_destroy": (None, [C.c_void_p]),
     "b200_sched_run": (C.c_int, [C.c_void_p, C.c_int, UNIT_FN, C.c_void_p, C.POINTER(C.c_int)]),

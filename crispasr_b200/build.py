@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200_fattn.so")
 STAMP = LIB + ".srchash"   # hash of the sources and flags the library next to it was built from
-SOURCES = ["fattn_api.cu", "fattn_mma.cu", "fattn_tc5.cu", "kv_slab.cu", "segment_sched.cpp"]
+SOURCES = ["fattn_api.cu", "fattn_mma.cu", "fattn_tc5.cu", "kv_slab.cu", "relpos_table.cu", "segment_sched.cpp", "slice_batch.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr",

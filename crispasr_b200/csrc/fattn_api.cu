@@ -7,6 +7,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "fattn_common.cuh"
 #include "fattn_tc5.cuh"
@@ -235,6 +238,14 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
         a.causal = ext->causal ? 1 : 0;
         a.n_past = ext->n_past;
         a.kv_len = ext->kv_len;
+        a.q_len = ext->q_len;
+        if (ext->kv_index) {
+            if (!ext->kv_len) return B200_E_NULL;   // the lists' lengths
+            if (ext->kv_index_stride <= 0 || ext->kv_index_stride > INT32_MAX / 2) return B200_E_SHAPE;
+            if ((uintptr_t)ext->kv_index % 4) return B200_E_ALIGN;
+            a.kv_index = ext->kv_index;
+            a.kv_index_stride = ext->kv_index_stride;
+        }
     }
 
     int sm_count = 148;
@@ -247,11 +258,12 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     // kernel choice
     int kernel = B200_KERNEL_TILE_MMA;
     const bool decode_ok = !a.relpos && Tq * (H / Hkv) <= 16;
+    if (a.kv_index && (!decode_ok || a.has_mask || a.causal || a.softcap != 0.0f || a.q_len)) return B200_E_UNSUPPORTED;
     const bool tc5_ok = tc5_supported(a);
     const int override_k = g_override.load(std::memory_order_relaxed);
     if (decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
     else if (tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
-    if (override_k == B200_KERNEL_TILE_MMA) kernel = B200_KERNEL_TILE_MMA;
+    if (override_k == B200_KERNEL_TILE_MMA && !a.kv_index) kernel = B200_KERNEL_TILE_MMA;   // index lists exist in the decode kernel only
     if (override_k == B200_KERNEL_DECODE_SPLIT && decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
     if (override_k == B200_KERNEL_PREFILL_TC5 && tc5_ok) kernel = B200_KERNEL_PREFILL_TC5;
     plan->cast_kv = plan->cast_r = false;
@@ -280,7 +292,62 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     return B200_OK;
 }
 
+// ---- per-launch tracing: an NVTX range around the enqueue and a CUDA event pair around the kernels ----
+// Off by default.  b200_trace_enable(n) creates a ring of n event pairs on the current device up front, so a traced
+// launch allocates nothing; launches on other devices, and launches made while a stream is being captured into a
+// CUDA graph, are not traced (an event record of this kind cannot be captured with timing).
+struct TraceSlot {
+    cudaEvent_t begin = nullptr, end = nullptr;
+    b200_trace_record rec;
+    bool used = false;
+};
+struct Trace {
+    std::mutex mu;
+    std::vector<TraceSlot> ring;
+    size_t next = 0, count = 0;   // count = slots holding unread records (oldest at next - count)
+    int device = -1;
+    std::atomic<int> on{0};
+} g_trace;
+
+const char* kernel_label(int k) {
+    switch (k) {
+        case B200_KERNEL_TILE_MMA: return "b200_fattn:tile_mma";
+        case B200_KERNEL_DECODE_SPLIT: return "b200_fattn:decode_split";
+        case B200_KERNEL_PREFILL_TC5: return "b200_fattn:prefill_tc5";
+        default: return "b200_fattn";
+    }
+}
+
+int do_launch_untraced(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st);
+
 int do_launch(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st) {
+    if (!g_trace.on.load(std::memory_order_relaxed)) return do_launch_untraced(plan, workspace, ws_bytes, st);
+    int dev = -1;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != g_trace.device || cudaStreamIsCapturing(st, &cap) != cudaSuccess ||
+        cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return do_launch_untraced(plan, workspace, ws_bytes, st);
+    }
+    std::lock_guard<std::mutex> lk(g_trace.mu);
+    if (g_trace.ring.empty()) return do_launch_untraced(plan, workspace, ws_bytes, st);
+    TraceSlot& slot = g_trace.ring[g_trace.next];
+    const FattnArgs& a = plan.args;
+    nvtxRangePushA(kernel_label(plan.kernel));
+    cudaEventRecord(slot.begin, st);
+    const int rc = do_launch_untraced(plan, workspace, ws_bytes, st);
+    cudaEventRecord(slot.end, st);
+    nvtxRangePop();
+    if (rc == B200_OK) {
+        slot.rec = b200_trace_record{plan.kernel, a.n_splits, a.hd, a.Tq, a.Lk, a.H, a.Hkv, a.B, a.k.type, -1.0f};
+        slot.used = true;
+        g_trace.next = (g_trace.next + 1) % g_trace.ring.size();
+        if (g_trace.count < g_trace.ring.size()) g_trace.count++;   // a full ring drops its oldest record
+    }
+    return rc;
+}
+
+int do_launch_untraced(Plan& plan, void* workspace, size_t ws_bytes, cudaStream_t st) {
     FattnArgs& a = plan.args;
     if (plan.cast_kv || plan.cast_r) {
         if (!workspace || ws_bytes < plan.ws_bytes || (uintptr_t)workspace % 256) return B200_E_WORKSPACE;
@@ -398,6 +465,62 @@ B200_API int b200_device_status_reset(void) {
     return B200_OK;
 }
 
+B200_API int b200_trace_enable(int capacity) {
+    if (capacity < 0 || capacity > (1 << 16)) return B200_E_LIMIT;
+    std::lock_guard<std::mutex> lk(g_trace.mu);
+    g_trace.on.store(0);
+    for (TraceSlot& sl : g_trace.ring) {
+        if (sl.begin) cudaEventDestroy(sl.begin);
+        if (sl.end) cudaEventDestroy(sl.end);
+    }
+    g_trace.ring.clear();
+    g_trace.next = g_trace.count = 0;
+    g_trace.device = -1;
+    if (capacity == 0) return B200_OK;
+    DeviceInfo di;
+    const int rc = device_info(&di);
+    if (rc != B200_OK) return rc;
+    cudaGetDevice(&g_trace.device);
+    g_trace.ring.resize((size_t)capacity);
+    for (TraceSlot& sl : g_trace.ring) {
+        cudaError_t e = cudaEventCreate(&sl.begin);
+        if (e == cudaSuccess) e = cudaEventCreate(&sl.end);
+        if (e != cudaSuccess) {
+            for (TraceSlot& x : g_trace.ring) {
+                if (x.begin) cudaEventDestroy(x.begin);
+                if (x.end) cudaEventDestroy(x.end);
+            }
+            g_trace.ring.clear();
+            return cuda_fail(e, "cudaEventCreate(trace)");
+        }
+    }
+    g_trace.on.store(1);
+    return B200_OK;
+}
+
+B200_API int b200_trace_read(b200_trace_record* out, int max_records, int* n_out) {
+    if (!n_out || (max_records > 0 && !out)) return B200_E_NULL;
+    *n_out = 0;
+    std::lock_guard<std::mutex> lk(g_trace.mu);
+    const size_t n = g_trace.ring.size();
+    if (n == 0) return B200_OK;
+    size_t idx = (g_trace.next + n - g_trace.count) % n;   // oldest unread
+    while (g_trace.count > 0 && *n_out < max_records) {
+        TraceSlot& sl = g_trace.ring[idx];
+        cudaError_t e = cudaEventSynchronize(sl.end);
+        float ms = -1.0f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, sl.begin, sl.end);
+        if (e != cudaSuccess) return cuda_fail(e, "trace event");
+        out[*n_out] = sl.rec;
+        out[*n_out].ms = ms;
+        (*n_out)++;
+        sl.used = false;
+        idx = (idx + 1) % n;
+        g_trace.count--;
+    }
+    return B200_OK;
+}
+
 B200_API int b200_test_bounded_wait(int polls, void* cuda_stream) {
     if (polls < 1 || polls > (1 << 20)) return B200_E_LIMIT;
     DeviceInfo di;
@@ -417,6 +540,28 @@ B200_API int b200_set_decode_splits(int n_splits) {
 B200_API int b200_set_kernel_override(int kernel) {
     if (kernel < B200_KERNEL_NONE || kernel > B200_KERNEL_PREFILL_TC5) return B200_E_SHAPE;
     g_override.store(kernel, std::memory_order_relaxed);
+    return B200_OK;
+}
+
+B200_API int b200_beam_cells_to_index(const int32_t* cell_pos, const uint32_t* cell_seq_bits, int n_cells,
+                                      const int32_t* tok_seq, const int32_t* tok_pos, int n_tokens,
+                                      int32_t* index_out, int stride, int32_t* len_out) {
+    if (!cell_pos || !cell_seq_bits || !tok_seq || !tok_pos || !index_out || !len_out) return B200_E_NULL;
+    if (n_cells < 0 || n_tokens < 0 || stride <= 0) return B200_E_SHAPE;
+    for (int j = 0; j < n_tokens; j++) {
+        if (tok_seq[j] < 0 || tok_seq[j] >= 32) return B200_E_SHAPE;
+        int32_t* row = index_out + (size_t)j * stride;
+        int n = 0;
+        for (int i = 0; i < n_cells; i++) {
+            // visible iff the cell carries the token's sequence id and is not ahead of the token
+            if (((cell_seq_bits[i] >> tok_seq[j]) & 1u) && cell_pos[i] <= tok_pos[j]) {
+                if (n == stride) return B200_E_LIMIT;
+                row[n++] = i;
+            }
+        }
+        len_out[j] = n;
+        for (int i = n; i < stride; i++) row[i] = 0;   // never read (beyond kv_len), kept in range all the same
+    }
     return B200_OK;
 }
 
@@ -471,6 +616,7 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     Plan plan;
     int rc = make_plan(q, k, v, mask, dst, params, ext, false, &plan);
     if (rc != B200_OK) return rc;
+    if (ext && ext->kv_index) return B200_E_UNSUPPORTED;   // index lists address a device-resident pool; nothing to stage
     DeviceInfo di;
     if ((rc = device_info(&di))) return rc;
     int dev = 0;
@@ -488,6 +634,7 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
     };
     for (int i = 0; i < NIN; i++) off[i] = in[i] ? bump(span_bytes(in[i])) : 0;
     const size_t kvlen_off = (ext && ext->kv_len) ? bump((size_t)q->ne[3] * 4) : 0;
+    const size_t qlen_off = (ext && ext->q_len) ? bump((size_t)q->ne[3] * 4) : 0;
     const size_t dst_bytes = (size_t)dst->ne[0] * dst->ne[1] * dst->ne[2] * dst->ne[3] * 4;
     const size_t dst_off = bump(dst_bytes);
 
@@ -576,6 +723,10 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
             (e = cudaMemcpyAsync(ar.base + kvlen_off, ext->kv_len, (size_t)B * 4, cudaMemcpyHostToDevice, streams[0])) !=
                 cudaSuccess)
             return cuda_fail(e, "cudaMemcpyAsync(kv_len)");
+        if (ext && ext->q_len &&
+            (e = cudaMemcpyAsync(ar.base + qlen_off, ext->q_len, (size_t)B * 4, cudaMemcpyHostToDevice, streams[0])) !=
+                cudaSuccess)
+            return cuda_fail(e, "cudaMemcpyAsync(q_len)");
         if (n_chunks > 1) {
             if ((e = cudaEventCreateWithFlags(&shared_ready, cudaEventDisableTiming)) != cudaSuccess)
                 return cuda_fail(e, "cudaEventCreate");
@@ -608,6 +759,7 @@ B200_API int b200_fattn_forward_host(const b200_tensor* q, const b200_tensor* k,
                 dext.pos_bias_u = ext->pos_bias_u ? &ct[6] : nullptr;
                 dext.pos_bias_v = ext->pos_bias_v ? &ct[7] : nullptr;
                 dext.kv_len = ext->kv_len ? (const int32_t*)(ar.base + kvlen_off) + b0 : nullptr;
+                dext.q_len = ext->q_len ? (const int32_t*)(ar.base + qlen_off) + b0 : nullptr;
             }
             b200_tensor cdst = *dst;
             cdst.ne[3] = nb;

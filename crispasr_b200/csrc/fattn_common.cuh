@@ -30,6 +30,9 @@ struct FattnArgs {
     int32_t n2;       // ALiBi head split; 0 = max_bias off
     int32_t causal, n_past;
     const int32_t* kv_len;
+    const int32_t* q_len;      // [B] valid query rows per batch entry; nullptr = Tq
+    const int32_t* kv_index;   // [B][kv_index_stride] cache row of each logical key; nullptr = identity
+    int32_t kv_index_stride;
     int32_t relpos, relpos_f32;
     int32_t cluster_merge;  // split-KV: the splits of one (batch, kv-head) form a thread-block cluster and merge through distributed shared memory
     const float* bias_u;  // [hd, H] fp32 added to Q on load (content scores); nullptr = off
@@ -45,6 +48,19 @@ constexpr float kLog2e = 1.4426950408889634f;
 __device__ __forceinline__ float alibi_slope(const FattnArgs& a, int h) {
     if (a.n2 == 0) return 1.0f;
     return h < a.n2 ? powf(a.m0, (float)(h + 1)) : powf(a.m1, (float)(2 * (h - a.n2) + 1));
+}
+
+// Valid query rows of batch entry b (ext->q_len clamped to [0, Tq]; Tq without the table).
+__device__ __forceinline__ int q_rows_of(const FattnArgs& a, int b) {
+    if (!a.q_len) return a.Tq;
+    const int v = a.q_len[b];
+    return v < 0 ? 0 : (v > a.Tq ? a.Tq : v);
+}
+
+// n_past of the implicit causal rule (key k visible to query q iff k <= n_past + q).  A batched launch that gives
+// both per-entry tables places an entry's q_len new tokens at the end of its kv_len keys; otherwise the scalar applies.
+__device__ __forceinline__ int n_past_of(const FattnArgs& a, int len_b, int tq_b) {
+    return (a.q_len && a.kv_len) ? len_b - tq_b : a.n_past;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

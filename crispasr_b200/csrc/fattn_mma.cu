@@ -117,15 +117,20 @@ __device__ __forceinline__ uint4 load8_as_half(const uint8_t* rowp, int type, in
 
 // Rows [row0, row0+NROWS) of a strided 2-D slice -> swizzled fp16 tile; rows outside
 // [row_lo, row_hi) are zero-filled.
+// `index` (may be null) maps a logical row to the row of `base` that holds it, clamped to [0, pool_rows).
 template <int HD, int NROWS>
 __device__ __forceinline__ void load_tile(__half* sm, const uint8_t* base, int64_t nb1, int type, bool vec16,
-                                          int row0, int row_lo, int row_hi, int hd, int tid) {
+                                          int row0, int row_lo, int row_hi, int hd, int tid, const int32_t* index = nullptr,
+                                          int pool_rows = 0) {
     constexpr int CPR = HD / 8;
     for (int idx = tid; idx < NROWS * CPR; idx += kThreads) {
         const int row = idx / CPR, ch = idx % CPR;
         const int grow = row0 + row;
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (grow >= row_lo && grow < row_hi) val = load8_as_half(base + (int64_t)grow * nb1, type, ch * 8, hd, vec16);
+        if (grow >= row_lo && grow < row_hi) {
+            const int src = index ? min(max(__ldg(index + grow), 0), pool_rows - 1) : grow;
+            val = load8_as_half(base + (int64_t)src * nb1, type, ch * 8, hd, vec16);
+        }
         *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sm) + (row * CPR + swz<HD>(row, ch)) * 16) = val;
     }
 }
@@ -174,10 +179,13 @@ __device__ __forceinline__ float quad_sum(float v) {
     return v;
 }
 
+// Valid keys of batch entry b: kv_len[b] clamped to the number of logical keys (the rows of K, or the width of the
+// index lists when keys are addressed through ext->kv_index).
 __device__ __forceinline__ int clamp_len(const FattnArgs& a, int b) {
-    if (!a.kv_len) return a.Lk;
+    const int cap = a.kv_index ? a.kv_index_stride : a.Lk;
+    if (!a.kv_len) return cap;
     const int v = a.kv_len[b];
-    return v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
+    return v < 0 ? 0 : (v > cap ? cap : v);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -200,6 +208,14 @@ __global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArg
     const int q0 = blockIdx.x * BM, h = blockIdx.y, b = blockIdx.z;
     const int hk = h / a.gqa, bk = b / a.bq;
     const float ninf = -INFINITY;
+    const int tq_b = q_rows_of(a, b);   // rows at or beyond it are padding of a batched launch: zeros, no work
+    if (q0 >= tq_b) {
+        for (int idx = tid; idx < BM * a.hd; idx += kThreads) {
+            const int iq = q0 + idx / a.hd;
+            if (iq < a.Tq) a.dst[(((int64_t)b * a.Tq + iq) * a.H + h) * a.hd + idx % a.hd] = 0.0f;
+        }
+        return;
+    }
 
     if (RELPOS && a.bias_u != nullptr) {
         // untied position biases folded into the load: Q_u = Q + bias_u, Q_v = Q + bias_v (q_v aliases q)
@@ -223,9 +239,12 @@ __global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArg
 
     const int len_b = clamp_len(a, b);
     int kmax = len_b;
+    // causal bound: key k is visible to query q iff k <= n_past + q; in a batched launch with per-entry lengths the
+    // new tokens are the last q_len rows of the entry's kv_len keys
+    const int n_past = n_past_of(a, len_b, tq_b);
     if (a.causal) {
-        const int last_q = min(q0 + BM, a.Tq) - 1;
-        kmax = min(kmax, a.n_past + last_q + 1);
+        const int last_q = min(q0 + BM, tq_b) - 1;
+        kmax = min(kmax, n_past + last_q + 1);
     }
     const float slope = alibi_slope(a, h);
 
@@ -304,7 +323,7 @@ __global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArg
                 float val = s[nt][e] * a.scale;
                 if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
                 if (RELPOS) val += xw[i * kXStride + j + 15 - i];
-                const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + iq);
+                const bool valid = ik < len_b && (!a.causal || ik <= n_past + iq);
                 if (mbase && valid && iq < a.Tq)
                     val += slope * __half2float(*reinterpret_cast<const __half*>(mbase + (int64_t)iq * a.mask.nb1 +
                                                                                  (int64_t)ik * 2));
@@ -362,11 +381,12 @@ __global__ void __launch_bounds__(kThreads) fattn_tile_mma_kernel(const FattnArg
         if (iq >= a.Tq) continue;
         float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * a.hd;
         const float inv = rI ? inv1 : inv0;
+        const bool live = iq < tq_b;   // padding rows get literal zeros, whatever their Q rows held
 #pragma unroll
         for (int nt = 0; nt < HD / 8; nt++) {
             const int c = nt * 8 + 2 * t;
-            if (c < a.hd) out[c] = o[nt][2 * rI] * inv;
-            if (c + 1 < a.hd) out[c + 1] = o[nt][2 * rI + 1] * inv;
+            if (c < a.hd) out[c] = live ? o[nt][2 * rI] * inv : 0.0f;
+            if (c + 1 < a.hd) out[c + 1] = live ? o[nt][2 * rI + 1] * inv : 0.0f;
         }
     }
 }
@@ -410,8 +430,10 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 // cp.async copy of rows [row0, row0+64) x HD halves into a swizzled fp16 tile; rows >= row_hi are zero-filled.
-template <int HD>
-__device__ __forceinline__ void issue_tile_f16(__half* sm, const uint8_t* base, int64_t nb1, int row0, int row_hi, int tid) {
+// IDX: logical row `grow` lives in cache row index[grow] (clamped to the pool): the gather of ext->kv_index.
+template <int HD, bool IDX = false>
+__device__ __forceinline__ void issue_tile_f16(__half* sm, const uint8_t* base, int64_t nb1, int row0, int row_hi, int tid,
+                                               const int32_t* index = nullptr, int pool_rows = 0) {
     constexpr int CPR = HD / 8;
 #pragma unroll
     for (int it = 0; it < kDecBN * CPR / kThreads; it++) {
@@ -419,7 +441,9 @@ __device__ __forceinline__ void issue_tile_f16(__half* sm, const uint8_t* base, 
         const int row = idx / CPR, ch = idx % CPR;
         const int grow = row0 + row;
         const bool valid = grow < row_hi;
-        cp_async16(tile_addr<HD>(sm, row, ch), base + (valid ? (int64_t)grow * nb1 + ch * 16 : 0), valid);
+        int src = grow;
+        if (IDX && valid) src = min(max(__ldg(index + grow), 0), pool_rows - 1);
+        cp_async16(tile_addr<HD>(sm, row, ch), base + (valid ? (int64_t)src * nb1 + ch * 16 : 0), valid);
     }
 }
 
@@ -578,12 +602,13 @@ __device__ __forceinline__ void cluster_merge_store(const FattnArgs& a, const fl
             L = fmaf(w, l[s], L), acc = fmaf(w, o[s], acc);
         }
         const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
-        a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? acc / L : 0.0f;
+        a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = (L > 0.0f && iq < q_rows_of(a, b)) ? acc / L : 0.0f;
     }
     cluster_sync_all();
 }
 
-template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false, bool LOW = false>
+// IDX (F16 ring, PLAIN): keys are gathered through ext->kv_index (one list per batch entry).
+template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false, bool LOW = false, bool IDX = false>
 __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int NR = LOW ? 1 : 2, NE = 2 * NR;   // live row halves / accumulator elements per n-tile
     constexpr int TILE_HALVES = kDecBN * HD;              // one fp16 K or V tile
@@ -610,13 +635,16 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     const float ninf = -INFINITY;
 
     const int len_b = clamp_len(a, b);
-    int kmax = len_b;
-    if (a.causal) kmax = min(kmax, a.n_past + a.Tq);
+    const int tq_b = q_rows_of(a, b);   // query rows at or beyond it give zeros
+    int kmax = tq_b > 0 ? len_b : 0;    // an entry without live rows reads no keys
+    const int n_past = n_past_of(a, len_b, tq_b);
+    if (a.causal) kmax = min(kmax, n_past + tq_b);
     const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
     const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
     const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
     const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
     const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
+    const int32_t* index = a.kv_index ? a.kv_index + (int64_t)b * a.kv_index_stride : nullptr;   // this entry's key list
 
     __shared__ __align__(8) uint64_t s_q8bar[4][kDecQ8Stages];   // Q8_0: one barrier per (warp, raw stage)
     if (MODE == kDecAsyncQ8) {
@@ -639,8 +667,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         }
         if (tile < tile_hi) {
             const int stage = (tile - tile_lo) % NS;
-            issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid);
-            issue_tile_f16<HD>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid);
+            issue_tile_f16<HD, IDX>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid, index, a.Lk);
+            issue_tile_f16<HD, IDX>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid, index, a.Lk);
             if (stage_mask && tid < R * 8) {
                 const int rr = tid >> 3, ch = tid & 7;
                 const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
@@ -702,8 +730,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         const __half *sK, *sV;
         if (MODE == kDecSync) {
             __syncthreads();
-            load_tile<HD, kDecBN>(sKV, kbase, a.k.nb1, a.k.type, a.k.vec16, k0, 0, len_b, a.hd, tid);
-            load_tile<HD, kDecBN>(sKV + TILE_HALVES, vbase, a.v.nb1, a.v.type, a.v.vec16, k0, 0, len_b, a.hd, tid);
+            load_tile<HD, kDecBN>(sKV, kbase, a.k.nb1, a.k.type, a.k.vec16, k0, 0, len_b, a.hd, tid, index, a.Lk);
+            load_tile<HD, kDecBN>(sKV + TILE_HALVES, vbase, a.v.nb1, a.v.type, a.v.vec16, k0, 0, len_b, a.hd, tid, index, a.Lk);
             __syncthreads();
             sK = sKV, sV = sKV + TILE_HALVES;
         } else if (MODE == kDecAsyncF16) {
@@ -743,7 +771,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         float rmax[2] = {ninf, ninf};
         // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
         const bool plain_tile = STAGE_MASK ? false : PLAIN ? (k0 + kDecBN <= len_b)
-                                      : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1));
+                                      : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= n_past + 1));
         if (plain_tile) {
             const float c = a.scale * kLog2e;
 #pragma unroll
@@ -788,7 +816,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
                 const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
                 float val = s[nt][e] * a.scale;
                 if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
-                const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + row_iq[rI]);
+                const bool valid = ik < len_b && (!a.causal || ik <= n_past + row_iq[rI]);
                 if (row_mask[rI] && valid)
                     val += row_slope[rI] * __half2float(*reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2));
                 val = valid ? val * kLog2e : ninf;
@@ -890,7 +918,7 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             if (c >= a.hd) continue;
             const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
             const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? merged(rr, c) / L : 0.0f;
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = (L > 0.0f && iq < tq_b) ? merged(rr, c) / L : 0.0f;
         }
     } else if (a.cluster_merge) {
         for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
@@ -948,8 +976,10 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     const float ninf = -INFINITY;
 
     const int len_b = clamp_len(a, b);
-    int kmax = len_b;
-    if (a.causal) kmax = min(kmax, a.n_past + a.Tq);
+    const int tq_b = q_rows_of(a, b);   // query rows at or beyond it give zeros
+    int kmax = tq_b > 0 ? len_b : 0;    // an entry without live rows reads no keys
+    const int n_past = n_past_of(a, len_b, tq_b);
+    if (a.causal) kmax = min(kmax, n_past + tq_b);
     const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
     const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
     const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
@@ -1070,7 +1100,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         float rmax[2] = {ninf, ninf};
         // common case (no mask, no softcap, every key of the tile visible to every row): one multiply per score
         const bool plain_tile = PLAIN ? (k0 + kDecBN <= len_b)
-                                      : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= a.n_past + 1));
+                                      : (!a.has_mask && a.softcap == 0.0f && k0 + kDecBN <= len_b && (!a.causal || k0 + kDecBN <= n_past + 1));
         if (plain_tile) {
             const float c = a.scale * kLog2e;
 #pragma unroll
@@ -1099,7 +1129,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
                     const int ik = k0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
                     float val = s[nt][e] * a.scale;
                     if (a.softcap != 0.0f) val = a.softcap * tanhf(val);
-                    const bool valid = ik < len_b && (!a.causal || ik <= a.n_past + row_iq[rI]);
+                    const bool valid = ik < len_b && (!a.causal || ik <= n_past + row_iq[rI]);
                     if (row_mask[rI] && valid)
                         val += row_slope[rI] * __half2float(*reinterpret_cast<const __half*>(row_mask[rI] + (int64_t)ik * 2));
                     val = valid ? val * kLog2e : ninf;
@@ -1232,7 +1262,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
             if (c >= a.hd) continue;
             const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
             const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = L > 0.0f ? merged(rr, c) / L : 0.0f;
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = (L > 0.0f && iq < tq_b) ? merged(rr, c) / L : 0.0f;
         }
     } else if (a.cluster_merge) {
         for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
@@ -1305,7 +1335,7 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
     }
     const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
     float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd;
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    const float inv = (L > 0.0f && iq < q_rows_of(a, b)) ? 1.0f / L : 0.0f;
 #pragma unroll
     for (int i = 0; i < HD / 32; i++) {
         const int c = lane + 32 * i;
@@ -1397,6 +1427,18 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
         e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
+    } else if (MODE == kDecAsyncF16 && a.kv_index && low) {   // index lists come without mask / softcap / causal bound
+        auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        launch_split(kern, grid, smem, st, a);
+    } else if (MODE == kDecAsyncF16 && a.kv_index) {
+        auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, false, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        launch_split(kern, grid, smem, st, a);
     } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal && low) {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
@@ -1436,7 +1478,7 @@ int decode_mode(const FattnArgs& a, int hdp) {
         // start at or beyond row kv_len are zero-filled, so reads stay inside rows [0, Lk) when Lk*rb % 16 == 0
         // or the head slab continues behind row Lk-1 (nb2 > Lk*rb).
         const bool tail_ok = ((int64_t)a.Lk * rb) % 16 == 0 || a.k.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16;
-        if (contiguous_rows && aligned && tail_ok && a.v.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16)
+        if (!a.kv_index && contiguous_rows && aligned && tail_ok && a.v.nb2 >= ((int64_t)a.Lk * rb + 15) / 16 * 16)   // gathered rows are not contiguous: element path
             return (a.hd == 64 || a.hd == 128) ? kDecRegQ8 : kDecAsyncQ8;
     }
     return kDecSync;
@@ -1621,7 +1663,7 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
         const int n = e ? atoi(e) : 0;
         return n >= 1 && n <= 16 ? n : 0;
     }();
-    const int tiles = (a.Lk + kDecBN - 1) / kDecBN;
+    const int tiles = ((a.kv_index ? a.kv_index_stride : a.Lk) + kDecBN - 1) / kDecBN;
     if (tiles <= 1) return 1;
     if (forced) return forced < tiles ? forced : tiles;
     const double units = (double)B * a.Hkv;

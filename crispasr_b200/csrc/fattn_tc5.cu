@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "fattn_tc5.cuh"
@@ -286,16 +287,15 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
     lsum_io += l0 + l1;
 }
 
-// Explicit F16 mask: turns 64 raw scores into log2-domain logits t = s*c + mask*log2(e) in place (mask -inf stays
-// -inf).  `mptr` points at the mask value of the first of the 64 columns, `avail` is how many mask columns exist
-// from there to the end of the mask row (loads never go past it).  Eight 16-byte loads are in flight at once.
-__device__ __forceinline__ void apply_mask64(uint32_t (&sreg)[2][32], const uint8_t* mptr, int avail, float c) {
-    uint4 mv[8];
+// 64 consecutive F16 mask values starting at `mptr` as eight 16-byte loads, all in flight at once (2-byte loads
+// where the address is not 16-byte aligned); values at or beyond `avail` (the end of the mask row) read as 0 and
+// are never touched in memory.
+__device__ __forceinline__ void load_mask64(uint4 (&mv)[8], const uint8_t* mptr, int avail) {
 #pragma unroll
     for (int q = 0; q < 8; q++) {
-        if (q * 8 + 8 <= avail) {
+        if (q * 8 + 8 <= avail && ((reinterpret_cast<uintptr_t>(mptr) & 15) == 0)) {
             mv[q] = __ldg(reinterpret_cast<const uint4*>(mptr + q * 16));
-        } else {
+        } else {   // the end of the row, or a row that does not start on a 16-byte boundary (mask rows hold exactly Lk values)
             uint16_t hv[8];
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -304,16 +304,26 @@ __device__ __forceinline__ void apply_mask64(uint32_t (&sreg)[2][32], const uint
                                hv[6] | ((uint32_t)hv[7] << 16));
         }
     }
+}
+// Mask value pair (columns i, i+1 of the 64, i even) of a block loaded by load_mask64.
+__device__ __forceinline__ float2 mask_pair(const uint4 (&mv)[8], int i) {
+    const uint4& v = mv[i >> 3];
+    const int u = (i & 7) >> 1;
+    const uint32_t w = u == 0 ? v.x : (u == 1 ? v.y : (u == 2 ? v.z : v.w));
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+// Explicit F16 mask: turns 64 raw scores into log2-domain logits t = s*c + mask*log2(e) in place (mask -inf stays
+// -inf).  `mptr` points at the mask value of the first of the 64 columns, `avail` is how many mask columns exist
+// from there to the end of the mask row (loads never go past it).
+__device__ __forceinline__ void apply_mask64(uint32_t (&sreg)[2][32], const uint8_t* mptr, int avail, float c) {
+    uint4 mv[8];
+    load_mask64(mv, mptr, avail);
 #pragma unroll
-    for (int q = 0; q < 8; q++) {
-        const uint32_t w[4] = {mv[q].x, mv[q].y, mv[q].z, mv[q].w};
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const float2 m2 = __half22float2(*reinterpret_cast<const __half2*>(&w[u]));
-            const int i = q * 8 + 2 * u;
-            sreg[i >> 5][i & 31] = __float_as_uint(fmaf(__uint_as_float(sreg[i >> 5][i & 31]), c, m2.x * kLog2e));
-            sreg[i >> 5][(i + 1) & 31] = __float_as_uint(fmaf(__uint_as_float(sreg[i >> 5][(i + 1) & 31]), c, m2.y * kLog2e));
-        }
+    for (int i = 0; i < 64; i += 2) {
+        const float2 m2 = mask_pair(mv, i);
+        sreg[i >> 5][i & 31] = __float_as_uint(fmaf(__uint_as_float(sreg[i >> 5][i & 31]), c, m2.x * kLog2e));
+        sreg[i >> 5][(i + 1) & 31] = __float_as_uint(fmaf(__uint_as_float(sreg[i >> 5][(i + 1) & 31]), c, m2.y * kLog2e));
     }
 }
 
@@ -400,14 +410,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     }
     const int bk = b / a.bq;
     const int rows_total = a.Tq * a.gqa;   // packed rows of this (kv head, batch entry)
+    const int tq_b = q_rows_of(a, b);      // query rows at or beyond it are padding of a batched launch: zeros
+    const int rows_live = tq_b * a.gqa;
 
     int len_b = a.Lk;
     if (a.kv_len) {
         const int v = a.kv_len[b];
         len_b = v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
     }
-    int kmax = len_b;
-    if (a.causal) kmax = min(kmax, a.n_past + min((q0 + kTile - 1) / a.gqa + 1, a.Tq));
+    const int n_past = n_past_of(a, len_b, tq_b);
+    int kmax = q0 < rows_live ? len_b : 0;   // a tile of padding rows reads no keys
+    if (a.causal) kmax = min(kmax, n_past + min((q0 + kTile - 1) / a.gqa + 1, tq_b));
     const int n_tiles = kmax > 0 ? (kmax + kTile - 1) / kTile : 0;
 
     if (n_tiles == 0) {  // nothing to attend to: zeros
@@ -582,15 +595,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     } else {
         // ================= softmax / correction / epilogue =================
         const int r = tid;
-        const bool row_live = q0 + r < rows_total;
-        const int iq = row_live ? (q0 + r) / a.gqa : a.Tq, h = hk * a.gqa + (q0 + r) % a.gqa;   // dead rows: iq = Tq
+        const bool row_live = q0 + r < rows_live;
+        const bool row_zero = !row_live && q0 + r < rows_total;   // a padding row inside the tensor: its dst row is zero-filled
+        const int iq_dst = (q0 + r) / a.gqa;
+        const int iq = row_live ? iq_dst : a.Tq, h = hk * a.gqa + (q0 + r) % a.gqa;   // dead rows: iq = Tq
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         const float c = a.scale * kLog2e;
         int kend = len_b;
-        if (a.causal) kend = min(kend, a.n_past + iq + 1);
+        if (a.causal) kend = min(kend, n_past + iq + 1);
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
-        // explicit mask row of this query ([Lk, Tq, 1|H, 1|B] F16, 16-byte aligned strides); rows past Tq reuse row 0
+        // explicit mask row of this query ([Lk, Tq, 1|H, 1|B] F16); rows past Tq reuse row 0
         const uint8_t* mrow = HASMASK ? a.mask.p + (int64_t)(iq < a.Tq ? iq : 0) * a.mask.nb1 +
                                             (int64_t)(h % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
                                       : nullptr;
@@ -701,18 +716,21 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + h) * HD;
+            float* out = a.dst + (((int64_t)b * a.Tq + iq_dst) * a.H + h) * HD;
 #pragma unroll
             for (int q4 = 0; q4 < HD / 32; q4++) {
                 uint32_t oreg[32];
                 tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
                 tmem_wait_ld();
-                if (iq < a.Tq) {
+                if (row_live) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
                         *reinterpret_cast<float4*>(out + q4 * 32 + i) =
                             make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
                                         __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
+                } else if (row_zero) {   // literal zeros: whatever the padding row of Q held never reaches dst
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out + q4 * 32 + i) = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
         }
@@ -747,6 +765,7 @@ constexpr int kBncStride = 128;  // bytes per bounce row: a ring of 64 f16 value
 
 constexpr int kThreadsRelpos = 320;  // 8 softmax warps (two threads per query row), TMA warp, MMA warp
 
+template <bool HASMASK>
 __global__ void __launch_bounds__(kThreadsRelpos, 1)
 fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
                                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmR) {
@@ -780,7 +799,8 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         const int v = a.kv_len[b];
         len_b = v < 0 ? 0 : (v > a.Lk ? a.Lk : v);
     }
-    const int n_tiles = len_b > 0 ? (len_b + kTile - 1) / kTile : 0;
+    const int tq_b = q_rows_of(a, b);   // query rows at or beyond it are padding of a batched launch: zeros
+    const int n_tiles = (len_b > 0 && q0 < tq_b) ? (len_b + kTile - 1) / kTile : 0;
     if (n_tiles == 0) {
         if (tid < kTile && q0 + tid < a.Tq) {
             float4* out = reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + q0 + tid) * a.H + h) * HD);
@@ -972,6 +992,12 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
         const uint32_t x_col0 = 96 - 32 * (warp & 3) + 64 * ch;   // first X column this thread's warp can need
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
+        // Explicit F16 mask added on top of the bias (bucket padding of src/canary_ctc.cpp:370-382, the local-attention
+        // window of src/core/fastconformer.h:887-895): this thread's row of [Lk, Tq, 1|H, 1|B];
+        // rows past Tq (the padding rows of the last query tile) read row 0.
+        const uint8_t* mrow = HASMASK ? a.mask.p + (int64_t)(iq < a.Tq ? iq : 0) * a.mask.nb1 +
+                                            (int64_t)(h % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
+                                      : nullptr;
         // Publish a value, meet the partner warp at the pair barrier (bounded wait), read the partner's value.
         // One slot per thread is enough: the partner's next write comes after its wait for the next S tile, which the
         // tensor pipe only produces after the P*V product that needed this thread's later arrival on bar_p_ready.
@@ -1031,6 +1057,8 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_x_free);
             if (tid == 0) TC5_TRACE(0, j, 1);
+            uint4 mv[8];
+            if (HASMASK) load_mask64(mv, mrow + (int64_t)(j * kTile + ch * 64) * 2, a.Lk - (j * kTile + ch * 64));   // in flight during the wait for S
 
             // ---- phase B: u = S*scale + bias (natural units), row maximum ----
             ok = mbar_wait(bar_s_full, j & 1, s_abort);
@@ -1052,6 +1080,10 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                         float u0, u1;
                         unpack2(fma2(pack2(__uint_as_float(sreg[q2][i]), __uint_as_float(sreg[q2][i + 1])), bscale2,
                                      pack2(u[q2][i], u[q2][i + 1])), u0, u1);
+                        if (HASMASK) {
+                            const float2 m2 = mask_pair(mv, q2 * 32 + i);
+                            u0 += m2.x, u1 += m2.y;
+                        }
                         if (!full_tile) {
                             if (ch * 64 + q2 * 32 + i >= n_valid) u0 = -INFINITY;
                             if (ch * 64 + q2 * 32 + i + 1 >= n_valid) u1 = -INFINITY;
@@ -1123,12 +1155,15 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 uint32_t oreg[32];
                 tmem_ld32(tmem_O + lane_base + ch * 64 + q4 * 32, oreg);
                 tmem_wait_ld();
-                if (iq < a.Tq) {
+                if (iq < tq_b) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
                         *reinterpret_cast<float4*>(out + q4 * 32 + i) =
                             make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
                                         __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
+                } else if (iq < a.Tq) {   // padding row of a batched launch: literal zeros
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out + q4 * 32 + i) = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
         }
@@ -1196,13 +1231,24 @@ int launch_relpos(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errl
         return B200_E_CUDA;
     }
     const size_t smem = 1024 + (size_t)6 * 2 * kPanelBytes + (size_t)2 * kTile * kBncStride + 136 + 8 + 2 * 128 * sizeof(float) + 16;
-    auto kern = fattn_prefill_tc5_relpos_kernel;
-    static bool smem_set[64] = {false};
-    cudaError_t e = set_smem_once(kern, smem, smem_set);
-    if (e == cudaSuccess) {
-        dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
-        kern<<<grid, kThreadsRelpos, smem, st>>>(a, tmK, tmV, tmR);
-        e = cudaGetLastError();
+    cudaError_t e;
+    dim3 grid((a.Tq + kTile - 1) / kTile, a.H, a.B);
+    if (a.has_mask) {
+        auto kern = fattn_prefill_tc5_relpos_kernel<true>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            kern<<<grid, kThreadsRelpos, smem, st>>>(a, tmK, tmV, tmR);
+            e = cudaGetLastError();
+        }
+    } else {
+        auto kern = fattn_prefill_tc5_relpos_kernel<false>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            kern<<<grid, kThreadsRelpos, smem, st>>>(a, tmK, tmV, tmR);
+            e = cudaGetLastError();
+        }
     }
     if (e != cudaSuccess) {
         snprintf(errbuf, errlen, "tcgen05 rel-pos prefill launch: %s", cudaGetErrorString(e));
@@ -1227,6 +1273,60 @@ cudaError_t launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStrea
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+#include "fattn_tc5_pair.cuh"
+
+// The paired-tile persistent kernel takes head_dim 64 without explicit mask and without causal bound.
+// B200_PREFILL_PAIR=1 selects it (the one-tile kernel is the default); B200_PREFILL_POLY=n (2..16) moves every n-th pair of
+// exponentials of the paired kernel to the FMA pipe (0 = none).
+int pair_mode() {
+    static const int mode = [] {
+        const char* e = getenv("B200_PREFILL_PAIR");
+        if (!(e && e[0] == '1')) return -1;   // opt-in while it measures slower than the one-tile kernel
+        const char* p = getenv("B200_PREFILL_POLY");
+        const int n = p ? atoi(p) : 0;
+        return (n == 2 || n == 3 || n == 4 || n == 8) ? n : 0;
+    }();
+    return mode;
+}
+
+bool pair_supported(const FattnArgs& a) {
+    return pair_mode() >= 0 && a.hd == 64 && !a.has_mask && !a.causal && !a.relpos;
+}
+
+int launch_pair(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+    CUtensorMap tmK, tmV;
+    if (!encode_kv_map(&tmK, a.k, a.hd, a.Lk, a.Hkv, a.B / a.bq) || !encode_kv_map(&tmV, a.v, a.hd, a.Lk, a.Hkv, a.B / a.bq)) {
+        snprintf(errbuf, errlen, "cuTensorMapEncodeTiled failed for K/V");
+        return B200_E_CUDA;
+    }
+    const int n_pairs = (a.Tq * a.gqa + 2 * kTile - 1) / (2 * kTile);
+    const int64_t n_items64 = (int64_t)n_pairs * a.Hkv * a.B;
+    if (n_items64 > INT32_MAX) return B200_E_LIMIT;
+    const int n_items = (int)n_items64;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    dim3 grid(n_items < sms ? n_items : sms);
+    cudaError_t e;
+    auto go = [&](auto kern) {
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, kPairSmem, smem_set);
+        if (e == cudaSuccess) e = launch_pdl(kern, grid, kPairThreads, kPairSmem, st, a, tmK, tmV, n_pairs, n_items);
+    };
+    switch (pair_mode()) {
+        case 2: go(fattn_prefill_tc5_pair_kernel<2>); break;
+        case 3: go(fattn_prefill_tc5_pair_kernel<3>); break;
+        case 4: go(fattn_prefill_tc5_pair_kernel<4>); break;
+        case 8: go(fattn_prefill_tc5_pair_kernel<8>); break;
+        default: go(fattn_prefill_tc5_pair_kernel<0>); break;
+    }
+    if (e != cudaSuccess) {
+        snprintf(errbuf, errlen, "tcgen05 paired prefill launch: %s", cudaGetErrorString(e));
+        return B200_E_CUDA;
+    }
+    return B200_OK;
 }
 
 template <int HD, int NSTG>
@@ -1270,7 +1370,7 @@ bool tc5_supported(const FattnArgs& a) {
     if (!a.k.vec16 || !a.v.vec16) return false;
     if (a.softcap != 0.0f || a.n2 != 0) return false;
     if (!(a.scale > 0.0f)) return false;
-    if (a.has_mask && (a.relpos || !a.mask.vec16)) return false;  // explicit masks: plain kernel, 16-byte aligned rows
+    // explicit masks: any 2-byte aligned layout (rows that are not 16-byte aligned are read with 2-byte loads)
     if (a.relpos) {
         // fused bias: head_dim 128, F16 R with TMA-legal strides, no causal mask, bias rounded to F16
         if (a.hd != 128 || a.causal || a.relpos_f32) return false;
@@ -1284,6 +1384,7 @@ bool tc5_supported(const FattnArgs& a) {
 
 int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     if (a.relpos) return launch_relpos(a, st, errbuf, errlen);
+    if (pair_supported(a)) return launch_pair(a, st, errbuf, errlen);
     if (a.hd == 64) return launch_t<64, 2>(a, st, errbuf, errlen);
     return launch_t<128, 1>(a, st, errbuf, errlen);
 }

@@ -4,8 +4,9 @@
 
 namespace b200 {
 
-// True when the operands fit the tcgen05 kernel: F16 K/V with 16-byte aligned strides, head_dim 64 or
-// 128, no explicit mask, no softcap/ALiBi (implicit causal mask and kv_len are handled in-kernel).
+// True when the operands fit the tcgen05 kernels: F16 K/V with 16-byte aligned strides, head_dim 64 or 128 (128
+// for the fused rel-pos form), no softcap/ALiBi; explicit F16 masks, the implicit causal mask and kv_len are
+// handled in-kernel.
 bool tc5_supported(const FattnArgs& a);
 
 // Encodes the tensor maps and launches. Returns a B200_* code; on CUDA failure writes the text to errbuf.

@@ -26,7 +26,7 @@ class _Call:
     """Descriptors of one op call; keeps every ctypes object alive for the duration of the call."""
 
     def __init__(self, q, k, v, mask, dst, scale, max_bias, softcap, kv_type, causal, n_past, kv_len, q_v, r,
-                 relpos_bias_f32, conv, pos_bias_u=None, pos_bias_v=None):
+                 relpos_bias_f32, conv, pos_bias_u=None, pos_bias_v=None, kv_index=None, q_len=None):
         self.q, self.k, self.v = conv(q), conv(k, kv_type), conv(v, kv_type)
         self.mask = conv(mask) if mask is not None else None
         self.dst = conv(dst)
@@ -49,6 +49,12 @@ class _Call:
         if kv_len is not None:
             self.ext.kv_len = kv_len.data_ptr() if hasattr(kv_len, "data_ptr") else kv_len.ctypes.data
         self.ext.relpos_bias_f32 = int(bool(relpos_bias_f32))
+        self.kv_index, self.q_len = kv_index, q_len
+        if kv_index is not None:   # int32 (B, stride): cache row of each logical key
+            self.ext.kv_index = kv_index.data_ptr() if hasattr(kv_index, "data_ptr") else kv_index.ctypes.data
+            self.ext.kv_index_stride = int(kv_index.shape[-1])
+        if q_len is not None:      # int32 (B,): valid query rows per batch entry
+            self.ext.q_len = q_len.data_ptr() if hasattr(q_len, "data_ptr") else q_len.ctypes.data
 
     def args(self):
         return (C.byref(self.q), C.byref(self.k), C.byref(self.v),
@@ -65,7 +71,8 @@ def _dst_like(q, device=None):
 def _make(q, k, v, mask, dst, kw, conv):
     return _Call(q, k, v, mask, dst, kw["scale"], kw.get("max_bias", 0.0), kw.get("softcap", 0.0),
                  kw.get("kv_type"), kw.get("causal", False), kw.get("n_past", 0), kw.get("kv_len"), kw.get("q_v"),
-                 kw.get("r"), kw.get("relpos_bias_f32", False), conv, kw.get("pos_bias_u"), kw.get("pos_bias_v"))
+                 kw.get("r"), kw.get("relpos_bias_f32", False), conv, kw.get("pos_bias_u"), kw.get("pos_bias_v"),
+                 kw.get("kv_index"), kw.get("q_len"))
 
 
 def supports(q, k, v, mask=None, **kw) -> bool:

@@ -97,7 +97,21 @@ typedef struct b200_fattn_ext {
     const int32_t* kv_len;
     /* If non-zero the relative-position bias is NOT rounded to F16 (diagnostic; the reference rounds). */
     int32_t relpos_bias_f32;
-    int32_t reserved;
+    /* Index lists instead of a dense membership mask.  Replaces, for the decoder self-attention over whisper's
+     * unified cell pool, the F16 mask that src/crispasr.cpp:3467-3499 fills (cell i visible to token j iff the cell
+     * carries j's sequence id and cell.pos <= pos_j) and with it the scan of every pooled cell by every beam:
+     * kv_index is a device array [B][kv_index_stride]; logical key i of batch entry b is row kv_index[b][i] of
+     * K and V (rows of batch entry b / (B/Bk), so the beams of one segment are batch entries that share its pool),
+     * for i < kv_len[b] (kv_len is then required; kv_len[b] <= kv_index_stride).  Entries are clamped to
+     * [0, Lk).  Only for launches that b200_fattn_plan maps to B200_KERNEL_DECODE_SPLIT, without mask and without
+     * the causal flag (a list already says which keys a row sees); otherwise B200_E_UNSUPPORTED.
+     * b200_beam_cells_to_index builds the lists from whisper's cells. */
+    int32_t kv_index_stride;
+    const int32_t* kv_index;
+    /* Device array [B] of valid query rows per batch entry (rows >= q_len[b] are not computed; their dst rows are
+     * zero-filled); NULL = Tq.  With kv_len this is the per-unit (q_len, kv_len) table of a batched launch over
+     * independent units of different lengths (b200_batch_*): no padding mask, no work for the padding. */
+    const int32_t* q_len;
 } b200_fattn_ext;
 
 /* Error codes (negative). 0 is success. Nothing in this library aborts or throws. */
@@ -239,6 +253,26 @@ B200_API int b200_device_status_reset(void);
  */
 B200_API int b200_test_bounded_wait(int polls, void* cuda_stream);
 
+/*
+ * Per-launch tracing, off by default.  The reference's counterparts are its debug taps and per-op timing buckets
+ * (src/core/attention.h:786-806 dumps tensors around the FA call; src/qwen3_tts.cpp:196-273 accumulates wall time
+ * per op class).  b200_trace_enable(n > 0) creates a ring of n CUDA event pairs on the current device; from then on
+ * every b200_fattn_launch / b200_fattn_launch_static / chunk of b200_fattn_forward_host on that device is wrapped
+ * in an NVTX range named after its kernel family and bracketed by an event pair on its stream.  b200_trace_read
+ * waits for the recorded launches and returns their records oldest first (a full ring overwrites its oldest
+ * record).  Launches made while the stream is being captured into a CUDA graph are not traced.
+ * b200_trace_enable(0) turns tracing off and frees the events.  Tracing serialises concurrent launches on a lock.
+ */
+typedef struct b200_trace_record {
+    int32_t kernel;   /* B200_KERNEL_* */
+    int32_t n_splits;
+    int32_t head_dim, q_len, kv_len, n_heads, n_kv_heads, n_batch;
+    int32_t kv_type;  /* b200_type */
+    float ms;         /* device time between the two events: all kernels of the launch (pre-pass, merge) included */
+} b200_trace_record;
+B200_API int b200_trace_enable(int capacity);
+B200_API int b200_trace_read(b200_trace_record* out, int max_records, int* n_out);
+
 /* The kernel family the calling thread's most recent successful launch used. */
 B200_API int b200_last_kernel(void);
 
@@ -286,6 +320,43 @@ B200_API int b200_kv_append(b200_kv_cache* kv, int layer, const b200_tensor* k_n
  */
 B200_API int b200_kv_copy_stream(b200_kv_cache* kv, int dst_stream, int src_stream, int64_t n_rows, void* cuda_stream);
 
+/*
+ * b200_beam_cells_to_index — host helper for ext->kv_index: turns whisper's cell pool
+ * (src/crispasr.cpp:1194-1217: per cell a position and a set of sequence ids; find_slot :1517-1564 hands cells
+ * out, beam reshuffles are seq-id edits :8193-8235) into one index list per token.  cell_pos[n_cells] and
+ * cell_seq_bits[n_cells] (bit s set = the cell carries sequence id s; an empty cell has no bit set) describe the
+ * pool; token j belongs to sequence tok_seq[j] at position tok_pos[j] and sees exactly the cells
+ * {i : bit tok_seq[j] of cell_seq_bits[i] set and cell_pos[i] <= tok_pos[j]} — the complement of the reference's
+ * -inf rule (:3480-3488).  index_out is [n_tokens][stride] (host), filled in ascending cell order; len_out[j]
+ * receives the count.  Returns B200_E_LIMIT if a list does not fit `stride`.  Pure host function.
+ */
+B200_API int b200_beam_cells_to_index(const int32_t* cell_pos, const uint32_t* cell_seq_bits, int n_cells,
+                                      const int32_t* tok_seq, const int32_t* tok_pos, int n_tokens,
+                                      int32_t* index_out, int stride, int32_t* len_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Relative-position table of the FastConformer attention block.  Replaces make_pos_enc
+ * (src/core/fastconformer.h:118-130), its upload, and R = MUL_MAT(attn_pos_w, pos_enc) with the
+ * reshape/permute that follows (:843, :851): R depends on the layer's weight and on T only, so it is built
+ * once per (layer, T) on the device, in the F16 [hd, 2T-1, H] layout that ext->r of the fused attention
+ * takes, and reused for every utterance of that length bucket.
+ * ------------------------------------------------------------------------------------------ */
+/* Builds R for one weight: attn_pos_w is the device tensor [d_in, d_out] (ggml order: ne[0] = input
+ * feature, contiguous) F32 or F16 with d_in == d_out == n_heads * hd.  Writes (2T-1) * d F16 values,
+ * head-major ([hd, 2T-1, H] contiguous), to r_out (device, 16-byte aligned, r_bytes >= that).  Asynchronous. */
+B200_API int b200_relpos_table(const b200_tensor* attn_pos_w, int n_heads, int T, void* r_out, size_t r_bytes,
+                               void* cuda_stream);
+typedef struct b200_relpos_cache b200_relpos_cache; /* opaque; tables live on the device current at creation */
+B200_API int b200_relpos_cache_create(int n_layers, int max_entries_per_layer, b200_relpos_cache** out);
+B200_API void b200_relpos_cache_destroy(b200_relpos_cache* c);
+B200_API size_t b200_relpos_cache_bytes(const b200_relpos_cache* c);
+/* Fills `r` with the descriptor of the table for (layer, T, this weight pointer), building it on a miss (one
+ * device allocation and one launch on `cuda_stream`; a hit does no device work).  Each layer keeps at most
+ * max_entries_per_layer tables and evicts the least recently used one.  Use the table on the stream it was
+ * built on, or order the streams yourself.  `was_hit` may be NULL. */
+B200_API int b200_relpos_cache_get(b200_relpos_cache* c, int layer, int T, const b200_tensor* attn_pos_w, int n_heads,
+                                   void* cuda_stream, b200_tensor* r, int* was_hit);
+
 /* ------------------------------------------------------------------------------------------
  * Segment scheduler.  Replaces the `-p N` worker instances with an atomic next-slice cursor
  * (examples/cli/crispasr_run.cpp:1882-1930) and whisper_full_parallel (src/crispasr.cpp:8755-8880)
@@ -324,6 +395,42 @@ B200_API int b200_sched_run_batched(b200_sched* s, int n_units, int max_batch, i
                                     int* unit_device);
 /* Static part of the partition: first unit and count owned by worker `w` of `n_workers`. */
 B200_API void b200_sched_partition(int n_units, int n_workers, int w, int* first, int* count);
+
+/* ------------------------------------------------------------------------------------------
+ * Slice batcher.  The reference runs one slice per operator call (CrispasrBackend::encode_slice /
+ * decode_slice, examples/cli/crispasr_backend.h:181-230; the encode/decode pipeline of
+ * examples/cli/crispasr_run.cpp:1765-1881 holds at most two slices) and pads different lengths to a bucket
+ * with a -inf mask (src/canary_ctc.cpp:370-382).  Here the units of one GPU share launches: they are
+ * concatenated on ne[3] and a per-unit (q_len, kv_len) table (ext->q_len / ext->kv_len) replaces the padding
+ * mask, so padding costs no arithmetic and no memory traffic.
+ * ------------------------------------------------------------------------------------------ */
+/* Orders `n_units` pending units by length (longest first) and cuts them into launches of at most `max_units`
+ * in which no unit's kv_len (q_len) is below (1 - max_pad) of the launch's longest: the padded operand buffers
+ * of a launch are then at most 1 / (1 - max_pad) times the sum of its units.  order[n_units] receives unit
+ * indices in launch order, group_end[g] the end (exclusive) of launch g in `order` (n_units entries suffice),
+ * n_groups the launch count.  Pure host function. */
+B200_API int b200_batch_pack(const int32_t* q_len, const int32_t* kv_len, int n_units, int max_units, float max_pad,
+                             int32_t* order, int32_t* group_end, int* n_groups);
+/* Slot table of a resident batch on the current device (decode streams join and leave, caches grow by a row per
+ * step).  Slot s is batch entry s of the launch: ne[3] of Q/K/V/dst = the span returned by b200_batch_span. */
+typedef struct b200_batch b200_batch; /* opaque */
+B200_API int b200_batch_create(int capacity, b200_batch** out);
+B200_API void b200_batch_destroy(b200_batch* b);
+/* Places unit `unit_id` (>= 0) in the lowest free slot; returns the slot or B200_E_LIMIT. */
+B200_API int b200_batch_add(b200_batch* b, int unit_id, int q_len, int kv_len);
+B200_API int b200_batch_set(b200_batch* b, int slot, int q_len, int kv_len);
+/* kv_len += kv_delta for every occupied slot: one decode step of all resident streams. */
+B200_API int b200_batch_advance(b200_batch* b, int kv_delta);
+/* Frees a slot; inside the span it stays in the launch with zero rows and zero keys (no work, zero output). */
+B200_API int b200_batch_remove(b200_batch* b, int slot);
+/* Span (highest occupied slot + 1), occupied slots, and the longest q_len / kv_len among them (any may be NULL). */
+B200_API int b200_batch_span(const b200_batch* b, int* n_slots, int* n_active, int* max_q_len, int* max_kv_len);
+B200_API int b200_batch_unit(const b200_batch* b, int slot); /* unit id, or -1 for a free slot */
+B200_API int b200_batch_lengths(const b200_batch* b, int slot, int* q_len, int* kv_len);
+/* Device arrays [capacity] for ext->q_len and ext->kv_len; uploads the tables with one asynchronous copy on
+ * `cuda_stream` if they changed since the last call.  Edit the table again only after work enqueued behind that
+ * copy no longer needs the old values in the pinned source (i.e. after the copy itself has run). */
+B200_API int b200_batch_tables(b200_batch* b, void* cuda_stream, const int32_t** q_len_dev, const int32_t** kv_len_dev);
 
 #ifdef __cplusplus
 }

@@ -241,3 +241,75 @@ def test_batched_scheduler_hands_out_contiguous_runs(b200):
     assert failed == 4 and owners[12:16] == [-1] * 4 and all(o >= 0 for o in owners[:12])
     assert len(tried[8]) == 2 and tried[8][0] != tried[8][1]
     s.close()
+
+
+def test_slice_packer_groups_units_of_similar_length(b200):
+    """b200_batch_pack: every unit exactly once, launches of at most max_units, longest first, and inside a launch no
+    unit below (1 - max_pad) of the longest, so padded buffers stay within 1 / (1 - max_pad) of the payload."""
+    L = b200.lib()
+    rng = np.random.default_rng(9)
+    n = 57
+    q = rng.integers(1, 1500, n).astype(np.int32)
+    kv = (q + rng.integers(0, 200, n)).astype(np.int32)
+    order, ends, ng = np.zeros(n, np.int32), np.zeros(n, np.int32), C.c_int(0)
+    for max_units, max_pad in ((8, 0.25), (64, 0.1), (4, 1.0)):
+        assert L.b200_batch_pack(q.ctypes.data, kv.ctypes.data, n, max_units, max_pad, order.ctypes.data, ends.ctypes.data, C.byref(ng)) == 0
+        assert sorted(order.tolist()) == list(range(n))
+        assert ends[ng.value - 1] == n and (np.diff(np.r_[0, ends[:ng.value]]) <= max_units).all()
+        assert (np.diff(kv[order]) <= 0).all(), "longest first"
+        start = 0
+        for e in ends[:ng.value]:
+            g = order[start:e]
+            assert kv[g].min() >= (1 - max_pad) * kv[g].max() - 1e-6 and q[g].min() >= (1 - max_pad) * q[g].max() - 1e-6
+            start = e
+        if max_pad == 1.0:
+            assert ng.value == -(-n // max_units)   # no length constraint: full launches
+    assert L.b200_batch_pack(q.ctypes.data, kv.ctypes.data, 0, 4, 0.5, order.ctypes.data, ends.ctypes.data, C.byref(ng)) == 0 and ng.value == 0
+    assert L.b200_batch_pack(q.ctypes.data, kv.ctypes.data, n, 0, 0.5, order.ctypes.data, ends.ctypes.data, C.byref(ng)) == abi.E_SHAPE
+
+
+def test_slot_table_of_a_resident_batch(b200):
+    """b200_batch: units take the lowest free slot, a freed slot inside the span stays in the launch with zero
+    lengths, one decode step advances every resident stream."""
+    L = b200.lib()
+    h = C.c_void_p()
+    assert L.b200_batch_create(4, C.byref(h)) == 0
+    assert [L.b200_batch_add(h, 100 + i, 1, 400 + i) for i in range(4)] == [0, 1, 2, 3]
+    assert L.b200_batch_add(h, 200, 1, 1) == abi.E_LIMIT
+    span, act, mq, mk = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    assert L.b200_batch_span(h, C.byref(span), C.byref(act), C.byref(mq), C.byref(mk)) == 0
+    assert (span.value, act.value, mq.value, mk.value) == (4, 4, 1, 403)
+    assert L.b200_batch_remove(h, 1) == 0 and L.b200_batch_remove(h, 1) == abi.E_STATE
+    assert L.b200_batch_advance(h, 1) == 0
+    ql, kl = C.c_int(), C.c_int()
+    assert L.b200_batch_lengths(h, 1, C.byref(ql), C.byref(kl)) == 0 and (ql.value, kl.value) == (0, 0)
+    assert L.b200_batch_lengths(h, 2, C.byref(ql), C.byref(kl)) == 0 and (ql.value, kl.value) == (1, 403)
+    assert L.b200_batch_unit(h, 1) == -1 and L.b200_batch_unit(h, 3) == 103
+    assert L.b200_batch_add(h, 300, 1, 7) == 1                      # the hole is reused first
+    assert L.b200_batch_remove(h, 3) == 0
+    L.b200_batch_span(h, C.byref(span), C.byref(act), None, None)
+    assert (span.value, act.value) == (3, 3)
+    assert L.b200_batch_set(h, 3, 1, 1) == abi.E_STATE and L.b200_batch_set(h, 9, 1, 1) == abi.E_SHAPE
+    if not torch.cuda.is_available():
+        a, b_ = C.c_void_p(), C.c_void_p()
+        assert L.b200_batch_tables(h, None, C.byref(a), C.byref(b_)) == abi.E_NO_DEVICE
+    L.b200_batch_destroy(h)
+
+
+def test_beam_cells_to_index_is_the_complement_of_the_mask_rule(b200, orc):
+    """The index lists hold exactly the cells the reference's mask leaves at 0 (src/crispasr.cpp:3480-3488)."""
+    L = b200.lib()
+    rng = np.random.default_rng(10)
+    n_cells, n_tok, stride = 300, 5, 256
+    cell_pos = rng.integers(0, 60, n_cells).astype(np.int32)
+    bits = rng.integers(0, 32, n_cells).astype(np.uint32)           # random subsets of 5 sequence ids; 0 = empty cell
+    tok_seq, tok_pos = np.arange(n_tok, dtype=np.int32), rng.integers(20, 60, n_tok).astype(np.int32)
+    idx, lens = np.full((n_tok, stride), -1, np.int32), np.zeros(n_tok, np.int32)
+    rc = L.b200_beam_cells_to_index(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data, tok_pos.ctypes.data,
+                                    n_tok, idx.ctypes.data, stride, lens.ctypes.data)
+    assert rc == 0
+    mask = orc.whisper_beam_mask(cell_pos, bits, tok_seq, tok_pos)   # (n_tok, n_cells) f16: 0 or -inf
+    for j in range(n_tok):
+        assert idx[j, :lens[j]].tolist() == np.flatnonzero(mask[j] == 0).tolist()
+    assert L.b200_beam_cells_to_index(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data, tok_pos.ctypes.data,
+                                      n_tok, idx.ctypes.data, 8, lens.ctypes.data) == abi.E_LIMIT

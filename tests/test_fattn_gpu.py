@@ -574,3 +574,114 @@ def test_full_size_properties_cfg5(b200, orc, capsys):
     ones = np.ones_like(v)
     got1 = gpu_op(b200, q_u, k, ones, scale=scale, q_v=q_v, r=r)
     assert np.abs(got1 - 1.0).max() < 2e-3
+
+
+@pytest.mark.parametrize("T", [200, 611])
+def test_cfg5_relpos_with_explicit_masks_on_the_tensor_core_path(b200, orc, T):
+    """The fused bias combined with an explicit F16 mask stays on the tcgen05 kernel: the bucket padding mask of
+    src/canary_ctc.cpp:370-382 (pad keys -inf), the local-attention window of src/core/fastconformer.h:887-895
+    (a band of width 2*64+1, -inf outside), and a per-head finite mask; a query row whose window is empty of valid
+    keys gives zeros."""
+    rng = np.random.default_rng(45)
+    q_u, q_v, k, v, r = _relpos_case(orc, rng, T)
+    scale = 128 ** -0.5
+    valid = T - 29
+    pad = np.zeros((1, 1, T, T), np.float16)
+    pad[..., valid:] = -np.inf
+    qi, ki = np.arange(T)[:, None], np.arange(T)[None, :]
+    band = np.where(np.abs(qi - ki) <= 64, 0.0, -np.inf).astype(np.float16)[None, None]
+    per_head = (rng.standard_normal((1, 8, T, T)) * 0.5).astype(np.float16)
+    per_head[0, 3, 17, :] = -np.inf                      # one fully masked row
+    for name, mask in (("padding", pad), ("local window", band), ("padding + window", (pad.astype(np.float32) + band).astype(np.float16)),
+                       ("per-head", per_head)):
+        ref = orc.flash_attn_ext(q_u, k, v, mask, scale=scale, q_v=q_v, r=r)
+        got = gpu_op(b200, q_u, k, v, mask, scale=scale, q_v=q_v, r=r)
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5, name
+        rows = slice(0, valid) if "padding" in name else slice(0, T)
+        assert_close(got[:, rows], ref[:, rows], f"cfg5 fused bias + {name} mask, T={T}")
+    assert not gpu_op(b200, q_u, k, v, per_head, scale=scale, q_v=q_v, r=r)[0, 17, 3].any()
+    assert b200.lib().b200_device_status() == 0
+
+
+def test_relpos_table_built_on_the_device_and_cached(b200, orc):
+    """R = attn_pos_w . pos_enc (src/core/fastconformer.h:118-130, :843, :851) built by the library for a (layer, T)
+    equals the oracle's make_pos_enc @ W to within one F16 rounding, attention with the library's table meets the
+    parity tolerance against the oracle with the host-built table, and the cache returns the same table for the
+    same key, builds per T, and evicts the least recently used entry."""
+    import ctypes as C
+    rng = np.random.default_rng(47)
+    T, H, hd = 333, 8, 128
+    d = H * hd
+    w = (rng.standard_normal((d, d)) / 32.0).astype(np.float32)          # numpy (d_out, d_in) == ggml [d_in, d_out]
+    r_host = (orc.make_pos_enc(d, T) @ w.T).reshape(2 * T - 1, H, hd).transpose(1, 0, 2)   # (H, 2T-1, hd)
+    L = b200.lib()
+    cache = C.c_void_p()
+    assert L.b200_relpos_cache_create(2, 2, C.byref(cache)) == 0
+    st = torch.cuda.current_stream().cuda_stream
+    for wt, tol in ((torch.from_numpy(w).cuda(), 1.0), (torch.from_numpy(w).cuda().half(), 1.0)):
+        tw, tr, hit = abi.from_torch(wt), abi.Tensor(), C.c_int(-1)
+        assert L.b200_relpos_cache_get(cache, 0, T, C.byref(tw), H, st, C.byref(tr), C.byref(hit)) == 0 and hit.value == 0
+        assert (tr.ne[0], tr.ne[1], tr.ne[2], tr.type) == (hd, 2 * T - 1, H, abi.F16) and tr.data % 16 == 0
+        torch.cuda.synchronize()
+        got = torch.empty((H, 2 * T - 1, hd), dtype=torch.float16, device="cuda")
+        C.cdll.LoadLibrary("libcudart.so").cudaMemcpy(C.c_void_p(got.data_ptr()), C.c_void_p(tr.data), C.c_size_t(got.numel() * 2), 3)
+        want = (orc.make_pos_enc(d, T) @ wt.float().cpu().numpy().T).reshape(2 * T - 1, H, hd).transpose(1, 0, 2)
+        diff = np.abs(got.float().cpu().numpy() - want)
+        ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(want), 2.0 ** -14))) - 10)      # one F16 ulp at each value
+        # one F16 rounding, plus the fp32 summation-order noise of a 1024-term dot product (and, for the F16 weight,
+        # nothing more: the weight is widened exactly)
+        assert (diff <= tol * ulp + 4e-6).all(), f"table differs by {float(((diff - 4e-6) / ulp).max()):.2f} F16 ulp"
+        tr2 = abi.Tensor()
+        assert L.b200_relpos_cache_get(cache, 0, T, C.byref(tw), H, st, C.byref(tr2), C.byref(hit)) == 0 and hit.value == 1
+        assert tr2.data == tr.data
+    # attention with the library-built table (F32 weight entry was evicted? no: two entries per layer, both alive)
+    q_u = rng.standard_normal((1, H, T, hd)).astype(np.float16).astype(np.float32)
+    q_v = rng.standard_normal((1, H, T, hd)).astype(np.float16).astype(np.float32)
+    k, v = randn_f16(rng, (1, H, T, hd)), randn_f16(rng, (1, H, T, hd))
+    ref = orc.flash_attn_ext(q_u, k, v, scale=hd ** -0.5, q_v=q_v, r=np.ascontiguousarray(r_host[None]).astype(np.float16))
+    wt = torch.from_numpy(w).cuda()
+    tw, tr, hit = abi.from_torch(wt), abi.Tensor(), C.c_int(-1)
+    assert L.b200_relpos_cache_get(cache, 1, T, C.byref(tw), H, st, C.byref(tr), C.byref(hit)) == 0 and hit.value == 0
+    r_dev = torch.empty((1, H, 2 * T - 1, hd), dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    C.cdll.LoadLibrary("libcudart.so").cudaMemcpy(C.c_void_p(r_dev.data_ptr()), C.c_void_p(tr.data), C.c_size_t(r_dev.numel() * 2), 3)
+    got = gpu_op(b200, q_u, k, v, scale=hd ** -0.5, q_v=q_v, r=r_dev)
+    assert_close(got, ref, "attention with the device-built table")
+    # eviction: a third and fourth T on layer 1 push out the oldest entries; bytes follow
+    for T2 in (40, 50, 60):
+        assert L.b200_relpos_cache_get(cache, 1, T2, C.byref(tw), H, st, C.byref(tr), C.byref(hit)) == 0 and hit.value == 0
+    assert L.b200_relpos_cache_get(cache, 1, T, C.byref(tw), H, st, C.byref(tr), C.byref(hit)) == 0 and hit.value == 0   # was evicted
+    assert L.b200_relpos_cache_get(cache, 1, 60, C.byref(tw), H, st, C.byref(tr), C.byref(hit)) == 0 and hit.value == 1
+    assert L.b200_relpos_cache_bytes(cache) == 2 * d * (2 * T - 1) * 2 + d * (2 * T - 1) * 2 + d * (2 * 60 - 1) * 2
+    assert L.b200_relpos_cache_get(cache, 5, T, C.byref(tw), H, st, C.byref(tr), None) == abi.E_SHAPE
+    torch.cuda.synchronize()
+    L.b200_relpos_cache_destroy(cache)
+
+
+def test_launch_tracing_records_one_event_pair_per_launch(b200, orc):
+    """b200_trace_enable / b200_trace_read: every launch is bracketed by an event pair (and an NVTX range); records
+    come back oldest first with the launch's geometry and a positive device time; a full ring keeps the newest."""
+    import ctypes as C
+    L = b200.lib()
+    rng = np.random.default_rng(60)
+    assert L.b200_trace_enable(4) == 0
+    try:
+        qp, kp = randn_f16(rng, (1, 4, 300, 64)), randn_f16(rng, (1, 4, 300, 64))
+        qd, kd = randn_f16(rng, (2, 8, 1, 128)), randn_f16(rng, (2, 2, 700, 128))
+        got = gpu_op(b200, qp, kp, kp, scale=0.125)
+        gpu_op(b200, qd, kd, kd, scale=0.1)
+        recs, n = (abi.TraceRecord * 8)(), C.c_int(0)
+        assert L.b200_trace_read(recs, 8, C.byref(n)) == 0 and n.value == 2
+        assert (recs[0].kernel, recs[0].head_dim, recs[0].q_len, recs[0].kv_len, recs[0].n_heads, recs[0].n_batch) == (abi.KERNEL_PREFILL_TC5, 64, 300, 300, 4, 1)
+        assert (recs[1].kernel, recs[1].head_dim, recs[1].q_len, recs[1].kv_len, recs[1].n_kv_heads, recs[1].n_batch) == (abi.KERNEL_DECODE_SPLIT, 128, 1, 700, 2, 2)
+        assert recs[1].n_splits >= 1 and 0.0 < recs[0].ms < 50.0 and 0.0 < recs[1].ms < 50.0
+        assert L.b200_trace_read(recs, 8, C.byref(n)) == 0 and n.value == 0       # read clears
+        for _ in range(6):                                                        # ring of 4: the two oldest are dropped
+            gpu_op(b200, qd, kd, kd, scale=0.1)
+        assert L.b200_trace_read(recs, 8, C.byref(n)) == 0 and n.value == 4
+        assert_close(got, orc.flash_attn_ext(qp, kp, kp, scale=0.125), "traced launch")   # tracing does not change results
+    finally:
+        assert L.b200_trace_enable(0) == 0
+    gpu_op(b200, qd, kd, kd, scale=0.1)
+    n = C.c_int(5)
+    assert L.b200_trace_read(None, 0, C.byref(n)) == 0 and n.value == 0

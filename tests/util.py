@@ -74,8 +74,9 @@ def gpu_op(b200, q, k, v, mask=None, **kw):
     for name in ("q_v", "r", "pos_bias_u", "pos_bias_v"):
         if kw.get(name) is not None:
             kw[name] = dev(kw[name])
-    if kw.get("kv_len") is not None:
-        kw["kv_len"] = torch.as_tensor(np.asarray(kw["kv_len"], np.int32)).cuda()
+    for name in ("kv_len", "q_len", "kv_index"):
+        if kw.get(name) is not None and not isinstance(kw[name], torch.Tensor):
+            kw[name] = torch.as_tensor(np.ascontiguousarray(kw[name], np.int32)).cuda()
     out = b200.flash_attn_ext(dev(q), dev(k), dev(v), dev(mask), **kw)
     torch.cuda.synchronize()
     return out.cpu().numpy()
