@@ -178,7 +178,7 @@ class ClockSampler:
         time.sleep(0.25)
         self.proc.terminate()
         self.t.join(timeout=2)
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
@@ -186,13 +186,18 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                pw.append(float(f[3]))
             except ValueError:
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        # "under load" = samples drawing at least half of the highest power seen: the sampler also runs through the
+        # idle moments around the timed region, which would otherwise hide a clock that drops under the power cap
+        load = [c for c, p in zip(sm, pw) if pw and p >= 0.5 * max(pw)]
+        return {"sm_mhz": statistics.median(load or sm) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(pw) if pw else None,
+                "reasons": sorted(reasons), "samples": len(sm), "samples_under_load": len(load)}
 
 
 def make_inputs_np(w, units, rng):

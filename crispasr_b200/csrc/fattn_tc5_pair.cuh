@@ -11,8 +11,8 @@
 //   * an item is a PAIR of 128-row query tiles of one (KV head, batch entry); the two tiles ("slots") share every K/V
 //     tile in shared memory, so K/V travel from L2 once per 256 query rows;
 //   * 384 threads: warps 0-3 softmax of slot 0, warps 4-7 softmax of slot 1 (thread r of a slot owns query row r, all
-//     128 score columns of a tile live in its registers), warp 8 TMA producer, warp 9 MMA issuer, warps 10-11 convert
-//     the NEXT item's Q tiles into the second Q buffer while the current item runs.  Register budgets are moved with
+//     128 score columns of a tile live in its registers), warp 8 TMA producer, warp 9 issues the score MMAs, warp 11
+//     the P.V MMAs, warp 10 converts the NEXT item's Q tiles into the second Q buffer while the current item runs.  Register budgets are moved with
 //     setmaxnreg: 200 per softmax thread, 96 for the rest;
 //   * tensor memory, all 512 columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).
 //     A softmax thread pulls its whole score row into registers at the start of a tile and says so (s_read); P has its
@@ -121,13 +121,21 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     asm volatile("griddepcontrol.wait;" ::: "memory");   // programmatic launch: the previous kernel of the stream has completed
+#ifdef B200_TC5_TRACE
+    if (tid == 0 && blockIdx.x < 192) {
+        long long tnow;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tnow));
+        (&g_tc5_trace[2][0][0])[blockIdx.x * 2] = tnow;
+        if (blockIdx.x < 8) (&g_tc5_trace[1][40][0])[blockIdx.x * 2] = clock64();
+    }
+#endif
 
     // ---- set-up, once per SM ----
     if (tid == 8 * 32) {
         for (int i = 0; i < kPairBars; i++) {
             const uint32_t bar = sBar + 8 * i;
             uint32_t count = 1;
-            if (bar >= bar_q_full && bar < bar_q_empty) count = 2;      // one arrival per Q-loader warp
+            // q_full: one arrival (the Q-loader warp)
             if (bar >= bar_p_ready && bar < bar_pv_done) count = 4;     // one arrival per softmax warp of the slot
             if (bar >= bar_s_read) count = 4;
             mbar_init(bar, count);
@@ -150,20 +158,22 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
 
     if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 96;" ::: "memory");
-        if (warp >= 10) {
-            // ================= Q loaders: the next item's two query tiles -> the free Q buffer =================
-            const int lt = tid - 10 * 32;   // 0..63, four rows each
+        if (warp == 10) {
+            // ================= Q loader: the next item's two query tiles -> the free Q buffer =================
+            const int lt = lane;   // eight rows each
             bool ok = true;
             int ka = 0;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const PairItem it = pair_item(a, item, n_pairs);
                 if (!it.active) continue;
                 const int buf = ka & 1, use = ka >> 1;
+                if (lane == 0) PAIR_TRACE(1, 16 + ka, 0);
                 if (use > 0) ok = mbar_wait(bar_q_empty + 8 * buf, (use - 1) & 1, s_abort);
                 if (!ok) break;
+                if (lane == 0) PAIR_TRACE(1, 16 + ka, 1);
 #pragma unroll 1
-                for (int rr = 0; rr < 4; rr++) {
-                    const int r = lt + 64 * rr, slot = r >> 7, row = r & 127;
+                for (int rr = 0; rr < 8; rr++) {
+                    const int r = lt + 32 * rr, slot = r >> 7, row = r & 127;
                     const int pr = it.q0 + r;                       // packed (query, head-of-group) row
                     const int iq = pr / a.gqa, h = it.hk * a.gqa + pr % a.gqa;
                     load_q_row<HD>(smem_gen + (buf * 2 + slot) * kPairTile, row,
@@ -173,6 +183,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_q_full + 8 * buf);
+                if (lane == 0) PAIR_TRACE(1, 16 + ka, 2);
                 ka++;
             }
         } else if (warp == 8) {
@@ -199,15 +210,17 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     for (uint32_t itn = 0; itn < 16384; ++itn) __nanosleep(64);
                 }
             }
-        } else {
-            // ================= MMA issuer =================
+        } else if (warp == 9) {
+            // ================= score issuer: S_t[j] = Q_t . K[j]^T =================
+            // Two threads issue the tensor-core work, this one the score tiles and warp 11 the P.V products: one
+            // thread doing both took 4 k clocks per pair of tiles (about 65 per MMA or commit, twice that per barrier
+            // test) and was what the softmax warps waited for.
             if (lane == 0) {
                 constexpr uint32_t desc_hi = smem_desc_hi(1024);
-                const uint32_t tS[2] = {tmem_base, tmem_base + 128}, tO[2] = {tmem_base + 256, tmem_base + 320},
-                               tP[2] = {tmem_base + 384, tmem_base + 448};
+                const uint32_t tS[2] = {tmem_base, tmem_base + 128};
                 bool ok = true;
                 int g = 0, ka = 0;
-                int cnt[2] = {0, 0};     // score tiles handed to each slot so far (phases of s_full / p_ready / pv_done)
+                int cnt[2] = {0, 0};     // score tiles each slot has taken into registers so far (phase of s_read)
                 bool any_mma = false;
                 auto issue_s = [&](int t, uint32_t q_addr, int kslot) {
                     const uint32_t qd = smem_desc_lo(q_addr, 16), kd = smem_desc_lo(sK + kslot * kPairTile, 16);
@@ -222,39 +235,53 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     const int buf = ka & 1, n = it.n_tiles;
                     const uint32_t q_addr[2] = {sQ + (buf * 2) * kPairTile, sQ + (buf * 2 + 1) * kPairTile};
                     ok = mbar_wait(bar_q_full + 8 * buf, (ka >> 1) & 1, s_abort);
-                    if (ok) ok = mbar_wait(bar_k_full + 8 * (g % NS), (g / NS) & 1, s_abort);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_s(0, q_addr[0], g % NS);
-                    if (it.live1) issue_s(1, q_addr[1], g % NS);
-                    any_mma = true;
-                    tc_commit(bar_k_empty + 8 * (g % NS));
-                    if (n == 1) tc_commit(bar_q_empty + 8 * buf);
                     for (int j = 0; j < n && ok; j++, g++) {
-                        const int slot = g % NS, nslot = (g + 1) % NS;
-                        const bool more = j + 1 < n;
+                        // tile j of the item: the slot's score columns are free once its four warps hold tile j-1 in
+                        // registers (s_read), long before its P is ready - so the next score tile is computed under
+                        // the slot's exponentials and a softmax warp never waits for the tensor pipe between tiles
+                        const int slot = g % NS;
+                        ok = mbar_wait(bar_k_full + 8 * slot, (g / NS) & 1, s_abort);
                         if (ka == 0) PAIR_TRACE(1, j, 0);
-                        // A slot's score columns are free as soon as its four warps hold the tile in registers (s_read),
-                        // long before its P is ready: the NEXT score tile is issued then and is computed under the
-                        // slot's exponentials, so a softmax warp never waits for the tensor pipe between two tiles.
-                        if (more) ok = mbar_wait(bar_k_full + 8 * nslot, ((g + 1) / NS) & 1, s_abort);
 #pragma unroll
                         for (int t = 0; t < 2; t++) {
                             if (!ok || (t == 1 && !it.live1)) continue;
-                            ok = mbar_wait(bar_s_read + 8 * t, cnt[t] & 1, s_abort);
+                            if (cnt[t] > 0) ok = mbar_wait(bar_s_read + 8 * t, (cnt[t] - 1) & 1, s_abort);   // the slot's previous tile (of this or the last item)
                             if (!ok) continue;
+                            cnt[t]++;
                             tc_fence_after();
-                            if (more) issue_s(t, q_addr[t], nslot);
+                            issue_s(t, q_addr[t], slot);
+                            any_mma = true;
+                            if (ka == 0) PAIR_TRACE(1, j, 1 + t);
                         }
                         if (!ok) break;
-                        if (more) {
-                            tc_commit(bar_k_empty + 8 * nslot);
-                            if (j + 2 == n) tc_commit(bar_q_empty + 8 * buf);   // the item's last score tiles have been issued
-                        }
-                        if (ka == 0) PAIR_TRACE(1, j, 1);
+                        tc_commit(bar_k_empty + 8 * slot);
+                        if (j + 1 == n) tc_commit(bar_q_empty + 8 * buf);   // the item's last score tiles have been issued
+                    }
+                    ka++;
+                }
+                if (!ok && any_mma) {
+                    tc_commit(bar_q_empty);
+                    for (uint32_t itn = 0; itn < 65536; ++itn) __nanosleep(64);   // no MMA of this CTA may still run when tensor memory is released
+                }
+            }
+        } else {
+            // ================= P.V issuer: O_t += P_t[j] . V[j] =================
+            if (lane == 0) {
+                constexpr uint32_t desc_hi = smem_desc_hi(1024);
+                const uint32_t tO[2] = {tmem_base + 256, tmem_base + 320}, tP[2] = {tmem_base + 384, tmem_base + 448};
+                bool ok = true;
+                int g = 0, ka = 0;
+                int cnt[2] = {0, 0};     // P tiles consumed per slot (phase of p_ready)
+                bool any_mma = false;
+                for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                    const PairItem it = pair_item(a, item, n_pairs);
+                    if (!it.active) continue;
+                    const int n = it.n_tiles;
+                    for (int j = 0; j < n && ok; j++, g++) {
+                        const int slot = g % NS;
+                        const bool more = j + 1 < n;
                         ok = mbar_wait(bar_v_full + 8 * slot, (g / NS) & 1, s_abort);
                         if (!ok) break;
-                        if (ka == 0) PAIR_TRACE(1, j, 2);
                         const uint32_t vd = smem_desc_lo(sV + slot * kPairTile, kPanelBytes);
 #pragma unroll
                         for (int t = 0; t < 2; t++) {
@@ -267,6 +294,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
 #pragma unroll
                             for (int ks = 0; ks < kTile / 16; ks++)
                                 mma_ts(tO[t], tP[t] + ks * 8, desc64(vd + ks * (2048 >> 4), desc_hi), IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);
+                            any_mma = true;
                             tc_commit(bar_pv_done + 8 * t);
                             if (!more) tc_commit(bar_o_done + 8 * t);
                             if (ka == 0) PAIR_TRACE(1, j, 4 + 2 * t);
@@ -277,8 +305,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     ka++;
                 }
                 if (!ok && any_mma) {
-                    // make sure no MMA of this CTA is still running before tensor memory is released
-                    tc_commit(bar_q_empty);
+                    tc_commit(bar_v_empty);
                     for (uint32_t itn = 0; itn < 65536; ++itn) __nanosleep(64);
                 }
             }
@@ -309,12 +336,13 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
             }
             const bool row_live = pr < it.rows_live, row_zero = !row_live && pr < it.rows_total;
             float m_ref = -INFINITY, l_run = 0.0f;
+            if (tid == 0) PAIR_TRACE(0, 16 + items_done, 0);
             for (int j = 0; j < it.n_tiles; j++, cnt++) {
                 const bool tr = (r == 0) && items_done == 0;
-                if (tr) PAIR_TRACE(2 * t, j, 7);
+                if (tr && t == 0) PAIR_TRACE(0, j, 7);
                 ok = mbar_wait(bar_s_full + 8 * t, cnt & 1, s_abort);
                 if (!ok) break;
-                if (tr) PAIR_TRACE(2 * t, j, 0);
+                if (tr && t == 0) PAIR_TRACE(0, j, 0);
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
@@ -323,39 +351,89 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_s_read + 8 * t);   // the tile is in registers: its columns may be overwritten
-                if (tr) PAIR_TRACE(2 * t, j, 1);
+                if (tr && t == 0) PAIR_TRACE(0, j, 1);
                 const int n_valid = it.len_b - j * kTile;   // the same for every row: columns >= n_valid are beyond the last key
                 const bool full = n_valid >= kTile;
-                // ---- row maximum, from registers ----
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    if (!full && q4 * 32 >= n_valid) continue;
+                if (j == 0) {
+                    // first tile of an item: a first reference maximum from the row's first 32 scores - rarely more than
+                    // 2^8 below the row's real maximum, and when it is the check below raises it and redoes the tile
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float s0 = __uint_as_float(s[q4][i]), s1 = __uint_as_float(s[q4][i + 1]);
-                        if (!full) {
-                            if (q4 * 32 + i >= n_valid) s0 = -INFINITY;
-                            if (q4 * 32 + i + 1 >= n_valid) s1 = -INFINITY;
-                        }
-                        mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], s0, s1);
+                        const float x0 = (i < n_valid) ? __uint_as_float(s[0][i]) : -INFINITY;
+                        const float x1 = (i + 1 < n_valid) ? __uint_as_float(s[0][i + 1]) : -INFINITY;
+                        m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], x0, x1);
                     }
+                    m_ref = max3(fmaxf(m4[0], m4[1]), m4[2], m4[3]) * c;
                 }
-                const float m_tile = max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]) * c;   // c > 0
-                bool pv_waited = false;
-                if (__any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold)) {
-                    // some row of the warp outgrew its reference maximum (always true on an item's first tile): raise
-                    // it and rescale l and O.  O must be at rest: the slot's previous P.V has completed.
-                    if (j > 0) {
-                        ok = mbar_wait(bar_pv_done + 8 * t, (cnt - 1) & 1, s_abort);
-                        if (!ok) break;
-                        tc_fence_after();
-                        pv_waited = true;
+                if (tr && t == 0) PAIR_TRACE(0, j, 2);
+                if (j > 0) {   // the slot's previous P.V has completed: its P columns are free and O is at rest
+                    ok = mbar_wait(bar_pv_done + 8 * t, (cnt - 1) & 1, s_abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (tr && t == 0) PAIR_TRACE(0, j, 3);
+                // ---- P = exp2(S*c - m_ref) -> f16x2 -> tensor memory, 32 columns at a time.  The row maximum is tracked
+                // in the same pass (the three-input maximum and the exponential sit on different pipes and overlap) and
+                // only checked afterwards; a row that outgrew its reference by 2^8 raises it, rescales l and O, and the
+                // tile is redone from the registers. ----
+                float lsum = 0.0f;
+                for (int attempt = 0; attempt < 2; attempt++) {
+                    const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+                    const uint64_t nm2 = pack2(-m_use, -m_use);
+                    uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};
+                    float mx[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) mx[i] = -INFINITY;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {
+                        uint32_t preg[16];
+                        if (full) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const float s0 = __uint_as_float(s[q4][i]), s1 = __uint_as_float(s[q4][i + 1]);
+                                mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], s0, s1);
+                                float t0, t1, p0, p1;
+                                unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
+                                if (POLY > 0 && ((i >> 1) % (POLY > 0 ? POLY : 1)) == 0) {
+                                    exp2_poly_pair(t0, t1, p0, p1);
+                                } else {
+                                    p0 = ex2(t0), p1 = ex2(t1);
+                                }
+                                ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+                                preg[i >> 1] = cvt_f16x2(p0, p1);
+                            }
+                        } else if (q4 * 32 >= n_valid) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) preg[i] = 0u;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                float s0 = __uint_as_float(s[q4][i]), s1 = __uint_as_float(s[q4][i + 1]);
+                                if (q4 * 32 + i >= n_valid) s0 = -INFINITY;
+                                if (q4 * 32 + i + 1 >= n_valid) s1 = -INFINITY;
+                                mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], s0, s1);
+                                float t0, t1;
+                                unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
+                                const float p0 = ex2(t0), p1 = ex2(t1);   // -inf -> 0
+                                ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+                                preg[i >> 1] = cvt_f16x2(p0, p1);
+                            }
+                        }
+                        tmem_st16(tP + q4 * 16, preg);
                     }
+                    {
+                        float l0, l1;
+                        unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
+                        lsum = l0 + l1;
+                    }
+                    const float m_tile = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;   // c > 0
+                    if (!__any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold)) break;
                     const float m_new = fmaxf(m_ref, m_tile);
                     const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
                     l_run *= alpha;
                     if (j > 0) {
+                        tmem_wait_st();
 #pragma unroll
                         for (int q4 = 0; q4 < HD / 32; q4++) {
                             uint32_t oreg[32];
@@ -368,60 +446,19 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     }
                     m_ref = m_new;
                 }
-                const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-                const uint64_t nm2 = pack2(-m_use, -m_use);
-                if (tr) PAIR_TRACE(2 * t, j, 2);
-                if (j > 0 && !pv_waited) {   // the slot's P columns are free once its previous P.V has consumed them
-                    ok = mbar_wait(bar_pv_done + 8 * t, (cnt - 1) & 1, s_abort);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                // ---- P = exp2(S*c - m_ref) -> f16x2 -> tensor memory, 32 columns at a time ----
-                if (tr) PAIR_TRACE(2 * t, j, 3);
-                uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    uint32_t preg[16];
-                    if (!full && q4 * 32 >= n_valid) {
-#pragma unroll
-                        for (int i = 0; i < 16; i++) preg[i] = 0u;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float s0 = __uint_as_float(s[q4][i]), s1 = __uint_as_float(s[q4][i + 1]);
-                            bool dead0 = false, dead1 = false;
-                            if (!full) {
-                                dead0 = q4 * 32 + i >= n_valid;
-                                dead1 = q4 * 32 + i + 1 >= n_valid;
-                            }
-                            float t0, t1, p0, p1;
-                            unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
-                            if (POLY > 0 && ((i >> 1) % (POLY > 0 ? POLY : 1)) == 0 && full) {
-                                exp2_poly_pair(t0, t1, p0, p1);
-                            } else {
-                                p0 = dead0 ? 0.0f : ex2(t0), p1 = dead1 ? 0.0f : ex2(t1);
-                            }
-                            ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
-                            preg[i >> 1] = cvt_f16x2(p0, p1);
-                        }
-                    }
-                    tmem_st16(tP + q4 * 16, preg);
-                }
-                {
-                    float l0, l1;
-                    unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
-                    l_run += l0 + l1;
-                }
-                if (tr) PAIR_TRACE(2 * t, j, 4);
+                l_run += lsum;
+                if (tr && t == 0) PAIR_TRACE(0, j, 4);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_p_ready + 8 * t);
-                if (tr) PAIR_TRACE(2 * t, j, 5);
+                if (tr && t == 0) PAIR_TRACE(0, j, 5);
             }
             if (!ok) break;
+            if (tid == 0) PAIR_TRACE(0, 16 + items_done, 1);
             ok = mbar_wait(bar_o_done + 8 * t, items_done & 1, s_abort);
             if (!ok) break;
+            if (tid == 0) PAIR_TRACE(0, 16 + items_done, 2);
             items_done++;
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
@@ -441,11 +478,20 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out + q4 * 32 + i) = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
+            if (tid == 0) PAIR_TRACE(0, 16 + items_done - 1, 3);
             tc_fence_before();   // the reads of O are ordered before this thread's next arrival, which the next item's first P.V waits for
         }
     }
 
     // ---- teardown ----
+#ifdef B200_TC5_TRACE
+    if (tid == 0 && blockIdx.x < 192) {
+        long long tnow;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tnow));
+        (&g_tc5_trace[2][0][0])[blockIdx.x * 2 + 1] = tnow;
+        if (blockIdx.x < 8) (&g_tc5_trace[1][40][0])[blockIdx.x * 2 + 1] = clock64();
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 9) {
