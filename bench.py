@@ -447,6 +447,29 @@ class DeviceWorkload:
         return [a.elapsed_time(b) for a, b in ev]
 
 
+def launch_floor_us(b200, torch, n_launches=30):
+    """Device time per launch of a CUDA graph of `n_launches` empty kernels: what a layer costs when it does nothing."""
+    L = b200.lib()
+    def step():
+        st = torch.cuda.current_stream().cuda_stream
+        for _ in range(n_launches):
+            L.b200_test_empty_launch(st)
+    step()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    for _ in range(3):
+        g.replay()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+    for a, b in ev:
+        a.record()
+        g.replay()
+        b.record()
+    torch.cuda.synchronize()
+    return statistics.median(a.elapsed_time(b) for a, b in ev) * 1e3 / n_launches
+
+
 def roofline_of(abi, w, name, units, dw, step_ms, pk, traffic):
     work = algorithmic_work(w, units)
     launch_s = statistics.fmean(step_ms) * 1e-3 / w["layers"]
@@ -676,6 +699,8 @@ def main():
             except Exception as exc:   # one failing configuration must not take the headline line with it
                 extra[key] = {"error": f"{type(exc).__name__}: {exc}"}
         line["workloads"] = extra
+        # the short decode launches (8 streams: 9 us per layer) next to what an empty kernel per layer costs
+        line["launch_floor_us_per_kernel"] = launch_floor_us(b200, torch)
     if not args.no_cpu_baseline:
         val, sample, cores = cpu_sample(w, budget_s=12.0)
         line["cpu_baseline"] = {"value": val, "unit": f"{w['unit_name']}/s", "cores": cores, "kind": "port", "sample": sample}

@@ -99,6 +99,7 @@ SYMBOLS = {
     "b200_device_status_reset": (C.c_int, []),
     "b200_trace_enable": (C.c_int, [C.c_int]),
     "b200_trace_read": (C.c_int, [C.POINTER(TraceRecord), C.c_int, C.POINTER(C.c_int)]),
+    "b200_test_empty_launch": (C.c_int, [C.c_void_p]),
     "b200_test_bounded_wait": (C.c_int, [C.c_int, C.c_void_p]),
     "b200_kv_create": (C.c_int, [C.POINTER(KvConfig), C.POINTER(C.c_void_p)]),
     "b200_kv_destroy": (None, [C.c_void_p]),

@@ -521,6 +521,12 @@ B200_API int b200_trace_read(b200_trace_record* out, int max_records, int* n_out
     return B200_OK;
 }
 
+B200_API int b200_test_empty_launch(void* cuda_stream) {
+    const int e = launch_empty((cudaStream_t)cuda_stream);
+    if (e != 0) return cuda_fail((cudaError_t)e, "empty launch");
+    return B200_OK;
+}
+
 B200_API int b200_test_bounded_wait(int polls, void* cuda_stream) {
     if (polls < 1 || polls > (1 << 20)) return B200_E_LIMIT;
     DeviceInfo di;

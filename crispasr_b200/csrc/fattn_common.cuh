@@ -142,5 +142,7 @@ int mma_reset_status();
 // Test hook: a one-warp kernel that waits, for at most `polls` polls, on an mbarrier nobody completes, then sets the
 // status word and returns.
 int launch_bounded_wait_probe(int polls, cudaStream_t st);
+// Measurement hook: one empty one-warp kernel on the stream (the launch-latency floor of a kernel per layer).
+int launch_empty(cudaStream_t st);
 
 }  // namespace b200

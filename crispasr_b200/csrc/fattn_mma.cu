@@ -1618,6 +1618,15 @@ __global__ void bounded_wait_probe_kernel(uint32_t polls) {
 }
 }  // namespace
 
+namespace {
+__global__ void empty_kernel() {}
+}  // namespace
+
+int launch_empty(cudaStream_t st) {
+    empty_kernel<<<1, 32, 0, st>>>();
+    return (int)cudaGetLastError();
+}
+
 int launch_bounded_wait_probe(int polls, cudaStream_t st) {
     bounded_wait_probe_kernel<<<1, 32, 0, st>>>((uint32_t)polls);
     return (int)cudaGetLastError();

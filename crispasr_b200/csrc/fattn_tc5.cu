@@ -165,6 +165,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -367,7 +375,13 @@ struct Tc5Smem {
     static constexpr int tile_bytes() { return kPanelBytes * (HD / 64); }
 };
 
-template <int HD, int NSTG, bool HASMASK>
+// EARLY (head_dim 64 without explicit mask): a softmax thread pulls its whole 128-column score row into registers at
+// the start of a tile and says so (s_read); the MMA thread issues S[j+1] right then instead of after P[j], so the next
+// score tile is computed under the exponentials of the current one and the softmax warps do not wait for the tensor
+// pipe between two tiles (the registers are the second score buffer).  P is computed 32 columns at a time against the
+// reference maximum with the tile maximum tracked in the same pass; a row that outgrew its reference redoes the tile
+// from the registers.
+template <int HD, int NSTG, bool HASMASK, bool EARLY = false>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV) {
@@ -385,8 +399,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t sBar = sV + NSTG * TILE_BYTES;  // 8-byte slots
     const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8 * NSTG, bar_v_full = sBar + 16 * NSTG,
                    bar_v_empty = sBar + 24 * NSTG, bar_s_full = sBar + 32 * NSTG, bar_p_ready = bar_s_full + 8,
-                   bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24;
-    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 32;
+                   bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24, bar_s_read = bar_s_full + 32;
+    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 40;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
     constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
@@ -446,6 +460,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         mbar_init(bar_p_ready, 4);   // one arrival per softmax warp
         mbar_init(bar_o_done, 1);
         mbar_init(bar_pv_done, 1);
+        mbar_init(bar_s_read, 4);    // one arrival per softmax warp
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
@@ -547,8 +562,27 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 const int slot = j % NSTG, use = j / NSTG;
                 const int nslot = (j + 1) % NSTG, nuse = (j + 1) / NSTG;
                 const bool more = j + 1 < n_tiles;
-                ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
-                if (ok && more) ok = mbar_wait(bar_k_full + 8 * nslot, nuse & 1, s_abort);
+                if (EARLY) {
+                    // the score columns are free once all four softmax warps hold tile j in registers
+                    if (more) ok = mbar_wait(bar_k_full + 8 * nslot, nuse & 1, s_abort);
+                    if (ok) ok = mbar_wait(bar_s_read, j & 1, s_abort);
+                    if (!ok) break;
+                    if (more) {
+                        tc_fence_after();
+                        const uint32_t kd = k_lo + nslot * (TILE_BYTES >> 4);
+#pragma unroll
+                        for (int ks = 0; ks < HD / 16; ks++) {
+                            const uint32_t off16 = (uint32_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
+                            mma_ss(tmem_S, desc64(q_lo + off16, desc_hi), desc64(kd + off16, desc_hi), IDESC_S, ks > 0 ? 1u : 0u);
+                        }
+                        tc_commit(bar_s_full);
+                        tc_commit(bar_k_empty + 8 * nslot);
+                    }
+                    ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
+                } else {
+                    ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
+                    if (ok && more) ok = mbar_wait(bar_k_full + 8 * nslot, nuse & 1, s_abort);
+                }
                 if (!ok) break;
                 TC5_TRACE(1, j, 2);
                 ok = mbar_wait(bar_p_ready, j & 1, s_abort);
@@ -567,13 +601,13 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     tc_commit(bar_s_full);
                 };
                 // with P in its own columns the next S goes first: the softmax threads wake after 4 MMAs, not 12
-                if (SEP_P && more) issue_next_s();
+                if (SEP_P && more && !EARLY) issue_next_s();
                 const uint32_t vd = v_lo + slot * (TILE_BYTES >> 4);
                 mma_ts(tmem_O, tmem_P, desc64(vd, desc_hi), IDESC_PV, j > 0 ? 1u : 0u);
 #pragma unroll
                 for (int ks = 1; ks < kTile / 16; ks++) mma_ts(tmem_O, tmem_P + ks * 8, desc64(vd + ks * (2048 >> 4), desc_hi), IDESC_PV, 1u);
                 if (SEP_P) {
-                    if (more) tc_commit(bar_k_empty + 8 * nslot);   // after the P.V MMAs: off the softmax threads' critical path
+                    if (more && !EARLY) tc_commit(bar_k_empty + 8 * nslot);   // after the P.V MMAs: off the softmax threads' critical path
                     tc_commit(bar_v_empty + 8 * slot);
                     tc_commit(bar_pv_done);
                 } else {
@@ -610,6 +644,118 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                                             (int64_t)(h % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
                                       : nullptr;
         const float c_exp = HASMASK ? 1.0f : c;   // with a mask the scores are moved to the log2 domain by apply_mask64
+        if constexpr (EARLY) {
+            const uint64_t c2 = pack2(c, c);
+            for (int j = 0; j < n_tiles; j++) {
+                ok = mbar_wait(bar_s_full, j & 1, s_abort);
+                if (!ok) break;
+                if (tid == 0) TC5_TRACE(0, j, 0);
+                tc_fence_after();
+                uint32_t s[4][32];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) tmem_ld32(tmem_S + lane_base + q4 * 32, s[q4]);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_s_read);   // the tile is in registers: its columns may be overwritten
+                if (tid == 0) TC5_TRACE(0, j, 3);
+                const int n_valid = kend - j * kTile;     // columns >= n_valid of this row are masked
+                const bool full = __all_sync(0xffffffffu, n_valid >= kTile);
+                if (j == 0) {
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float x0 = (i < n_valid) ? __uint_as_float(s[0][i]) : -INFINITY;
+                        const float x1 = (i + 1 < n_valid) ? __uint_as_float(s[0][i + 1]) : -INFINITY;
+                        m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], x0, x1);
+                    }
+                    m_ref = max3(fmaxf(m4[0], m4[1]), m4[2], m4[3]) * c;
+                }
+                float lsum = 0.0f;
+                bool pv_waited = false;
+                for (int attempt = 0; attempt < 2; attempt++) {
+                    const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+                    const uint64_t nm2 = pack2(-m_use, -m_use);
+                    uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};
+                    float mx[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) mx[i] = -INFINITY;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {
+                        uint32_t preg[16];
+                        if (full) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const float s0 = __uint_as_float(s[q4][i]), s1 = __uint_as_float(s[q4][i + 1]);
+                                mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], s0, s1);
+                                float t0, t1;
+                                unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
+                                const float p0 = ex2(t0), p1 = ex2(t1);
+                                ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+                                preg[i >> 1] = cvt_f16x2(p0, p1);
+                            }
+                        } else if (q4 * 32 >= n_valid) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) preg[i] = 0u;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                float s0 = __uint_as_float(s[q4][i]), s1 = __uint_as_float(s[q4][i + 1]);
+                                if (q4 * 32 + i >= n_valid) s0 = -INFINITY;
+                                if (q4 * 32 + i + 1 >= n_valid) s1 = -INFINITY;
+                                mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], s0, s1);
+                                float t0, t1;
+                                unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
+                                const float p0 = ex2(t0), p1 = ex2(t1);   // -inf -> 0
+                                ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+                                preg[i >> 1] = cvt_f16x2(p0, p1);
+                            }
+                        }
+                        if (q4 == 0 && j > 0 && !pv_waited) {
+                            // the first 32 probabilities are in registers: only now must P[j-1] have been consumed
+                            ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
+                            tc_fence_after();
+                            pv_waited = true;
+                        }
+                        tmem_st16(tmem_P + lane_base + q4 * 16, preg);
+                    }
+                    if (!ok) break;
+                    {
+                        float l0, l1;
+                        unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
+                        lsum = l0 + l1;
+                    }
+                    const float m_tile = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
+                    if (!__any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold)) break;
+                    // some row of this warp outgrew its reference maximum: rescale O and l (O is at rest: pv_done was
+                    // awaited above), then redo P from the registers
+                    const float m_new = fmaxf(m_ref, m_tile);
+                    const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
+                    l_run *= alpha;
+                    if (j > 0) {
+                        tmem_wait_st();
+#pragma unroll
+                        for (int q4 = 0; q4 < HD / 32; q4++) {
+                            uint32_t oreg[32];
+                            tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                            tmem_st32(tmem_O + lane_base + q4 * 32, oreg);
+                        }
+                    }
+                    m_ref = m_new;
+                }
+                if (!ok) break;
+                l_run += lsum;
+                if (tid == 0) TC5_TRACE(0, j, 1);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_p_ready);
+                if (tid == 0) TC5_TRACE(0, j, 2);
+            }
+        } else
         for (int j = 0; j < n_tiles; j++) {
             ok = mbar_wait(bar_s_full, j & 1, s_abort);
             if (!ok) break;
@@ -1305,15 +1451,23 @@ int launch_pair(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen
     const int64_t n_items64 = (int64_t)n_pairs * a.Hkv * a.B;
     if (n_items64 > INT32_MAX) return B200_E_LIMIT;
     const int n_items = (int)n_items64;
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    dim3 grid(n_items < sms ? n_items : sms);
+    static const int chunk_env = [] {   // B200_PAIR_CHUNK=n: items per CTA (default 4)
+        const char* e = getenv("B200_PAIR_CHUNK");
+        const int n = e ? atoi(e) : 0;
+        return n >= 1 && n <= 1024 ? n : 4;
+    }();
+    const int chunk = chunk_env;
+    static const int stagger = [] {   // B200_PAIR_STAGGER=clocks: delay of slot 1's first tile (default 1200)
+        const char* e = getenv("B200_PAIR_STAGGER");
+        const int n = e ? atoi(e) : -1;
+        return n >= 0 && n <= 100000 ? n : 1200;
+    }();
+    dim3 grid((n_items + chunk - 1) / chunk);
     cudaError_t e;
     auto go = [&](auto kern) {
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, kPairSmem, smem_set);
-        if (e == cudaSuccess) e = launch_pdl(kern, grid, kPairThreads, kPairSmem, st, a, tmK, tmV, n_pairs, n_items);
+        if (e == cudaSuccess) e = launch_pdl(kern, grid, kPairThreads, kPairSmem, st, a, tmK, tmV, n_pairs, n_items, chunk, stagger);
     };
     switch (pair_mode()) {
         case 2: go(fattn_prefill_tc5_pair_kernel<2>); break;
@@ -1329,6 +1483,15 @@ int launch_pair(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen
     return B200_OK;
 }
 
+// B200_PREFILL_EARLY=1 selects the early-score order in the one-tile head_dim 64 kernel (A/B runs; off by default).
+bool early_scores_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200_PREFILL_EARLY");
+        return e && e[0] == '1';   // opt-in: with 168 registers per thread the 128-column row spills (7 M spill instructions per 8-segment launch) and the variant measures 0.6x
+    }();
+    return on;
+}
+
 template <int HD, int NSTG>
 int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     CUtensorMap tmK, tmV;
@@ -1337,11 +1500,18 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
         return B200_E_CUDA;
     }
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
-    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 32 + 16;
+    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 40 + 16;
     cudaError_t e;
     dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
     if (a.has_mask) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
+        }
+    } else if (HD == 64 && early_scores_enabled()) {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {

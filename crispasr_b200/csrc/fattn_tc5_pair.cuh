@@ -18,9 +18,10 @@
 //     A softmax thread pulls its whole score row into registers at the start of a tile and says so (s_read); P has its
 //     own columns; so the MMA thread issues S_t[j+1] right then, under the slot's exponentials of tile j, and the
 //     softmax warps never wait for the tensor pipe between two tiles (the registers are the second score buffer);
-//   * the CTA walks items item = blockIdx.x + k * gridDim.x; K/V tiles stream through one ring across item borders, the
-//     next item's first score tiles are computed while the softmax warps write the previous item's output, and barriers,
-//     tensor memory and tensor maps are set up once per SM instead of once per 128 rows;
+//   * a CTA walks `chunk` consecutive items (the pairs of one head first, so its K/V stay in L2); K/V tiles stream through
+//     one ring across item borders, the next item's first score tiles are computed while the softmax warps write the
+//     previous item's output, and barriers, tensor memory and tensor maps are set up once per chunk instead of once per
+//     128 rows; the grid is ceil(items / chunk) CTAs, one resident per SM, handed out by the hardware as SMs free up;
 //   * the row maximum is taken from registers before the exponentials (same instruction count as tracking it in the
 //     same pass), so a tile is never computed twice; O and l are rescaled lazily (only when a row outgrew its reference
 //     maximum by 2^8);
@@ -66,14 +67,6 @@ __device__ __forceinline__ PairItem pair_item(const FattnArgs& a, int item, int 
     return it;
 }
 
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-
 // 2^x for a pair on the FMA pipe: x = n + f with n = round(x) (magic-number add), 2^f by a cubic on [-0.5, 0.5]
 // (relative error 7.5e-5, below the F16 rounding of P), the exponent added to the bit pattern.  x is clamped to
 // >= -126 so the exponent arithmetic cannot wrap; -inf (a masked column) must not come here.
@@ -98,7 +91,7 @@ __device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& p0, fl
 template <int POLY>
 __global__ void __launch_bounds__(kPairThreads, 1)
 fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
-                              const __grid_constant__ CUtensorMap tmV, const int n_pairs, const int n_items) {
+                              const __grid_constant__ CUtensorMap tmV, const int n_pairs, const int n_items, const int chunk, const int stagger) {
     constexpr int HD = 64;
     constexpr uint32_t IDESC_S = idesc_f16(kTile, false);
     constexpr uint32_t IDESC_PV = idesc_f16(HD, true);
@@ -120,6 +113,10 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
     volatile int* s_abort = reinterpret_cast<volatile int*>(misc + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // This CTA's items: `chunk` consecutive ones.  The grid is not persistent on purpose: SMs differ in speed by more than
+    // a quarter on this part (a static split of the items over 148 resident CTAs finished between 1.64 and 2.08 ms), so
+    // the hardware's CTA scheduler does the load balancing, at chunk granularity.
+    const int item_lo = blockIdx.x * chunk, item_hi = min(n_items, item_lo + chunk);
     asm volatile("griddepcontrol.wait;" ::: "memory");   // programmatic launch: the previous kernel of the stream has completed
 #ifdef B200_TC5_TRACE
     if (tid == 0 && blockIdx.x < 192) {
@@ -163,7 +160,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
             const int lt = lane;   // eight rows each
             bool ok = true;
             int ka = 0;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            for (int item = item_lo; item < item_hi && ok; item++) {
                 const PairItem it = pair_item(a, item, n_pairs);
                 if (!it.active) continue;
                 const int buf = ka & 1, use = ka >> 1;
@@ -191,7 +188,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
             if (lane == 0) {
                 bool ok = true;
                 int g = 0;
-                for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                for (int item = item_lo; item < item_hi && ok; item++) {
                     const PairItem it = pair_item(a, item, n_pairs);
                     if (!it.active) continue;
                     for (int j = 0; j < it.n_tiles && ok; j++, g++) {
@@ -229,7 +226,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                         mma_ss(tS[t], desc64(qd + ks * 2, desc_hi), desc64(kd + ks * 2, desc_hi), IDESC_S, ks > 0 ? 1u : 0u);
                     tc_commit(bar_s_full + 8 * t);
                 };
-                for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                for (int item = item_lo; item < item_hi && ok; item++) {
                     const PairItem it = pair_item(a, item, n_pairs);
                     if (!it.active) continue;
                     const int buf = ka & 1, n = it.n_tiles;
@@ -273,7 +270,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                 int g = 0, ka = 0;
                 int cnt[2] = {0, 0};     // P tiles consumed per slot (phase of p_ready)
                 bool any_mma = false;
-                for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                for (int item = item_lo; item < item_hi && ok; item++) {
                     const PairItem it = pair_item(a, item, n_pairs);
                     if (!it.active) continue;
                     const int n = it.n_tiles;
@@ -321,7 +318,15 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
         const uint64_t c2 = pack2(c, c);
         bool ok = true;
         int cnt = 0, items_done = 0;   // score tiles / items this slot has processed (barrier phases)
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        // The two slots share the exponential unit.  Started together they stay in lockstep: both compute (each at half
+        // the unit's rate), then both wait (the unit idles).  Slot 1 therefore starts its first tile `stagger` clocks late
+        // (about half a tile of exponentials): from then on one slot's loads, barriers and stores fall into the other
+        // slot's exponentials, and since both slots do the same work per tile the offset persists across tiles and items.
+        if (t == 1 && stagger > 0) {
+            const long long t_go = clock64() + stagger;
+            while (clock64() < t_go) __nanosleep(200);
+        }
+        for (int item = item_lo; item < item_hi && ok; item++) {
             const PairItem it = pair_item(a, item, n_pairs);
             const int pr = it.q0 + t * kTile + r;                    // packed row of this thread
             const int iq = pr / a.gqa, h = it.hk * a.gqa + pr % a.gqa;
@@ -367,11 +372,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     m_ref = max3(fmaxf(m4[0], m4[1]), m4[2], m4[3]) * c;
                 }
                 if (tr && t == 0) PAIR_TRACE(0, j, 2);
-                if (j > 0) {   // the slot's previous P.V has completed: its P columns are free and O is at rest
-                    ok = mbar_wait(bar_pv_done + 8 * t, (cnt - 1) & 1, s_abort);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
+                bool pv_waited = (j == 0);   // the slot's previous P.V must have completed before P or O is written
                 if (tr && t == 0) PAIR_TRACE(0, j, 3);
                 // ---- P = exp2(S*c - m_ref) -> f16x2 -> tensor memory, 32 columns at a time.  The row maximum is tracked
                 // in the same pass (the three-input maximum and the exponential sit on different pipes and overlap) and
@@ -420,8 +421,15 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                                 preg[i >> 1] = cvt_f16x2(p0, p1);
                             }
                         }
+                        if (!pv_waited) {
+                            // the first 32 probabilities are in registers: only now must P[j-1] have been consumed
+                            ok = mbar_wait(bar_pv_done + 8 * t, (cnt - 1) & 1, s_abort);
+                            tc_fence_after();
+                            pv_waited = true;
+                        }
                         tmem_st16(tP + q4 * 16, preg);
                     }
+                    if (!ok) break;
                     {
                         float l0, l1;
                         unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
@@ -446,6 +454,7 @@ fattn_prefill_tc5_pair_kernel(const FattnArgs a, const __grid_constant__ CUtenso
                     }
                     m_ref = m_new;
                 }
+                if (!ok) break;
                 l_run += lsum;
                 if (tr && t == 0) PAIR_TRACE(0, j, 4);
                 tmem_wait_st();

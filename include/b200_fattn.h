@@ -252,6 +252,9 @@ B200_API int b200_device_status_reset(void);
  * context stays usable.  After synchronising, b200_device_status must report B200_E_DEVICE_WAIT.
  */
 B200_API int b200_test_bounded_wait(int polls, void* cuda_stream);
+/* Measurement hook: enqueues one empty one-warp kernel.  A stream (or captured graph) of these gives the
+ * launch-latency floor per layer that the short decode launches are compared with. */
+B200_API int b200_test_empty_launch(void* cuda_stream);
 
 /*
  * Per-launch tracing, off by default.  The reference's counterparts are its debug taps and per-op timing buckets

@@ -196,3 +196,29 @@ def test_scheduler_on_device(b200, orc):
         x = qs[u].cpu().numpy()
         assert_close(outs[u].cpu().numpy(), orc.flash_attn_ext(x, x, x, scale=0.125), f"unit {u}")
     s.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_batched_scheduler_over_two_gpus_equals_one(b200, orc):
+    """b200_sched_run_batched over two devices: each worker receives its static share as one batch on its own device
+    and stream, unit_device covers both workers, and the outputs equal a one-GPU run of the same units bit for bit."""
+    rng = np.random.default_rng(8)
+    n, H, T, hd = 6, 4, 200, 64
+    q = rng.standard_normal((n, H, T, hd)).astype(np.float16)
+    ref_dev = b200.flash_attn_ext(*(torch.from_numpy(q).cuda(0),) * 3, scale=0.125)
+    torch.cuda.synchronize(0)
+    outs = {}
+
+    def batch(dev, first, count, stream):
+        with torch.cuda.device(dev):
+            x = torch.from_numpy(q[first:first + count]).cuda(dev)
+            outs[first] = (dev, b200.flash_attn_ext(x, x, x, scale=0.125, stream=stream))
+            torch.cuda.current_stream(dev).synchronize()   # the upload ran on torch's stream
+        return 0
+    s = b200.SegmentScheduler(devices=[0, 1])
+    failed, owners = s.run_batched(n, n, batch, steal=False)
+    assert failed == 0 and owners == [0, 0, 0, 1, 1, 1]
+    for first, (dev, out) in outs.items():
+        torch.cuda.synchronize(dev)
+        assert torch.equal(out.cpu(), ref_dev[first:first + out.shape[0]].cpu())
+    s.close()
