@@ -1281,6 +1281,322 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Split-KV decode over a Q8_0 cache with the KEYS on the M side of the MMA (at most 8 query rows, plain form)
+// ------------------------------------------------------------------------------------------
+// The register kernel above multiplies 16 query rows (at most 8 of them real) with 8 keys per MMA and has to apply the
+// block scale to every operand register of K and V (hsub2 + hmul2 per register: half of its instructions).  This
+// variant transposes both products - S^T = K.Q^T and O^T = V^T.P^T, m16 = keys / output dims, n8 = the query rows - so
+// that a block scale belongs to an accumulator ROW of the thread that loaded the block:
+//   * scores: the quants go into the MMA as the exact halves 1152 + q (0x6400 | (b ^ 0x80), no subtract, no multiply),
+//     one accumulator per 32-element block; then s += d * (acc - 1152 * sum_block(Q)), the block sum of the query row
+//     being a per-thread constant.  fp32(d) * (integer dot) is the oracle's own arithmetic (x = fp32(d) * q), one
+//     rounding closer to it than fp16(d * q) operands;
+//   * P.V: the V block scale moves onto P (two half2 multiplies per block instead of eight), the quants go in as exact
+//     integers q (one subtract, no multiply).  P <= 2^4 here (the lazy-rescale bound is 4 instead of 8), so P * d stays
+//     inside f16 for every representable block scale (d <= 65504 / 127);
+//   * half as many MMAs (no padding rows), no quad shuffles in the common tile: the running maximum is only reduced
+//     across the warp when some key outgrew it.
+// P comes out of the score MMA as (key, row) accumulators and is needed as the (key, row) B operand of the second
+// product: one movmatrix.trans per 8 keys.  Staging (per-warp bulk copies of raw bytes, per-warp mbarriers, 3 stages),
+// split / merge forms and the epilogue are those of the kernel above.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const FattnArgs a) {
+    constexpr int NBLK = HD / 32, RB = NBLK * 34;
+    constexpr int RAW_BYTES = kDecBN * RB;   // one raw K or V tile
+    constexpr int NS = kDecRegStages;
+    constexpr float kGrow = 4.0f;            // lazy-rescale bound in log2 units: P <= 16
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __half* sQ = reinterpret_cast<__half*>(smem_raw);                                  // [16][HD], 16-byte chunks swizzled
+    uint8_t* sRaw = smem_raw + kDecRows * HD * sizeof(__half);                          // NS stages of raw K | V
+    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
+    __shared__ __align__(8) uint64_t s_bar[4][NS];                                      // one barrier per (warp, stage)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int bk = b / a.bq;
+    const int R = a.Tq * a.gqa;  // <= 8; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
+    const float ninf = -INFINITY;
+
+    const int len_b = clamp_len(a, b);
+    const int tq_b = q_rows_of(a, b);
+    const int kmax = tq_b > 0 ? len_b : 0;
+    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
+    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
+    const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
+    const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NS; i++) mbar_init(smem_u32(&s_bar[warp][i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    auto issue = [&](int tile) {
+        if (tile < tile_hi && lane == 0) {
+            const int stage = (tile - tile_lo) % NS;
+            issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES, sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, kbase, vbase, tile * kDecBN,
+                                 len_b, warp, smem_u32(&s_bar[warp][stage]));
+        }
+    };
+#pragma unroll
+    for (int s0 = 0; s0 < NS; s0++) issue(tile_lo + s0);
+
+    // Q rows (tiny): one 8-element chunk per loop step; rows >= R are zero
+    for (int idx = tid; idx < kDecRows * (HD / 8); idx += kThreads) {
+        const int rr = idx / (HD / 8), ch = idx % (HD / 8);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < R) {
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
+                                a.q.type, ch * 8, a.hd, a.q.vec16);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, ch)) * 16) = val;
+    }
+    __syncthreads();
+    // Q as the B operand of S^T = K.Q^T: column n = query row g; per (block, k-step) the thread's four contraction
+    // indices are dims 32blk + 16ks + {4t..4t+3} (the same permutation the K bytes are read in): one 8-byte read.
+    uint32_t qb[NBLK][2][2];
+#pragma unroll
+    for (int blk = 0; blk < NBLK; blk++)
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            const int ch = 4 * blk + 2 * ks + (t >> 1);
+            const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(sQ) + (g * (HD / 8) + swz<HD>(g, ch)) * 16 + (t & 1) * 8);
+            qb[blk][ks][0] = w.x, qb[blk][ks][1] = w.y;
+        }
+    // -1152 * (sum of the query row's f16 values over a block), for this thread's accumulator columns (rows 2t, 2t+1)
+    float negc[NBLK][2];
+#pragma unroll
+    for (int blk = 0; blk < NBLK; blk++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int rr = 2 * t + j;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) {
+                const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, 4 * blk + c4)) * 16);
+                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[i]));
+                    sum += f2.x + f2.y;
+                }
+            }
+            negc[blk][j] = -1152.0f * sum;
+        }
+
+    float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};   // rows 2t, 2t+1; m_run is the same on the 8 lanes that share t
+    float o[NBLK][2][4];   // [block][m-tile]: c0/c1 = dim 32blk+4g+2mt of rows 2t/2t+1, c2/c3 = dim +1
+#pragma unroll
+    for (int blk = 0; blk < NBLK; blk++)
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) o[blk][mt][0] = o[blk][mt][1] = o[blk][mt][2] = o[blk][mt][3] = 0.0f;
+    const __half2 bias = __float2half2_rn(1152.0f);
+    const float c = a.scale * kLog2e;
+
+    for (int tile = tile_lo; tile < tile_hi; tile++) {
+        const int k0 = tile * kDecBN;
+        const int stage = (tile - tile_lo) % NS;
+        if (!mbar_wait_bounded(smem_u32(&s_bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u)) break;
+        const uint8_t* rawK = sRaw + stage * 2 * RAW_BYTES + 16 * warp * RB;   // this warp's 16 keys
+        const uint8_t* rawV = rawK + RAW_BYTES;
+        const int rows_valid = len_b - (k0 + 16 * warp);   // keys at or beyond it hold stale bytes: their scale reads as 0
+        const bool all_live = rows_valid >= 16;
+
+        // ---- S^T = K.Q^T: keys g and g+8 of this warp's 16, query rows 2t and 2t+1 ----
+        float st[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint8_t* rowp[2] = {rawK + g * RB, rawK + (g + 8) * RB};
+        const bool live[2] = {all_live || g < rows_valid, all_live || g + 8 < rows_valid};
+#pragma unroll
+        for (int blk = 0; blk < NBLK; blk++) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                uint32_t w[2];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const uint8_t* bp = rowp[i] + blk * 34 + 2 + 16 * ks + 4 * t;   // block starts are 2 mod 4 for even blk
+                    if (blk & 1) {
+                        w[i] = *reinterpret_cast<const uint32_t*>(bp);
+                    } else {
+                        const uint16_t* hp = reinterpret_cast<const uint16_t*>(bp);
+                        w[i] = hp[0] | ((uint32_t)hp[1] << 16);
+                    }
+                    w[i] ^= 0x80808080u;
+                }
+                const uint32_t af[4] = {__byte_perm(w[0], 0x64646464u, 0x5140), __byte_perm(w[1], 0x64646464u, 0x5140),
+                                        __byte_perm(w[0], 0x64646464u, 0x7362), __byte_perm(w[1], 0x64646464u, 0x7362)};
+                mma16816(acc, af, qb[blk][ks][0], qb[blk][ks][1]);
+            }
+            const uint16_t d0b = live[0] ? *reinterpret_cast<const uint16_t*>(rowp[0] + blk * 34) : (uint16_t)0;
+            const uint16_t d1b = live[1] ? *reinterpret_cast<const uint16_t*>(rowp[1] + blk * 34) : (uint16_t)0;
+            const float d0 = __half2float(__ushort_as_half(d0b)), d1 = __half2float(__ushort_as_half(d1b));
+            st[0] = fmaf(d0, acc[0] + negc[blk][0], st[0]);
+            st[1] = fmaf(d0, acc[1] + negc[blk][1], st[1]);
+            st[2] = fmaf(d1, acc[2] + negc[blk][0], st[2]);
+            st[3] = fmaf(d1, acc[3] + negc[blk][1], st[3]);
+        }
+        // scale to the log2 domain; keys beyond the valid length are masked
+#pragma unroll
+        for (int e = 0; e < 4; e++) st[e] = live[e >> 1] ? st[e] * c : ninf;
+
+        // ---- lazy running maximum: only when some key outgrew the reference by 2^4 is it reduced over the warp ----
+        const float lm[2] = {fmaxf(st[0], st[2]), fmaxf(st[1], st[3])};
+        if (__any_sync(0xffffffffu, lm[0] > m_run[0] + kGrow || lm[1] > m_run[1] + kGrow)) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                float rm = lm[j];
+                rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, 4));
+                rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, 8));
+                rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, 16));
+                const float mnew = (rm > m_run[j] + kGrow) ? rm : m_run[j];   // -inf + 4 = -inf: the first finite maximum is taken
+                if (mnew != m_run[j]) {
+                    const float alpha = exp2f(m_run[j] - mnew);   // m_run = -inf -> 0
+                    l_run[j] *= alpha;
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; blk++)
+#pragma unroll
+                        for (int mt = 0; mt < 2; mt++) o[blk][mt][j] *= alpha, o[blk][mt][2 + j] *= alpha;
+                    m_run[j] = mnew;
+                }
+            }
+        }
+        const float muse[2] = {m_run[0] == ninf ? 0.0f : m_run[0], m_run[1] == ninf ? 0.0f : m_run[1]};
+        float p[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            p[e] = fast_ex2(st[e] - muse[e & 1]);
+            l_run[e & 1] += p[e];
+        }
+        // P^T as the B operand of O^T = V^T.P^T: (key g, rows 2t,2t+1) -> (keys 2t,2t+1, row g)
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p[0], p[1]));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p[2], p[3]));
+        const __half2 pb0h = *reinterpret_cast<const __half2*>(&pb0), pb1h = *reinterpret_cast<const __half2*>(&pb1);
+
+        // ---- O^T += V^T.P^T: keys 2t, 2t+1 (low k half) and 2t+8, 2t+9; this thread's bytes are dims 4g..4g+3 of each block ----
+#pragma unroll
+        for (int blk = 0; blk < NBLK; blk++) {
+            uint32_t w[4];
+            uint16_t db[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int key = 2 * t + (i & 1) + 8 * (i >> 1);
+                const uint8_t* bp = rawV + key * RB + blk * 34;
+                db[i] = (all_live || key < rows_valid) ? *reinterpret_cast<const uint16_t*>(bp) : (uint16_t)0;
+                if (blk & 1) {
+                    w[i] = *reinterpret_cast<const uint32_t*>(bp + 2 + 4 * g);
+                } else {
+                    const uint16_t* hp = reinterpret_cast<const uint16_t*>(bp + 2 + 4 * g);
+                    w[i] = hp[0] | ((uint32_t)hp[1] << 16);
+                }
+                w[i] ^= 0x80808080u;
+            }
+            // the block scales ride on P: P'[key] = P[key] * d(key, blk)
+            const uint32_t d01b = db[0] | ((uint32_t)db[1] << 16), d23b = db[2] | ((uint32_t)db[3] << 16);
+            const __half2 q0 = __hmul2(pb0h, *reinterpret_cast<const __half2*>(&d01b));
+            const __half2 q1 = __hmul2(pb1h, *reinterpret_cast<const __half2*>(&d23b));
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&q0), b1 = *reinterpret_cast<const uint32_t*>(&q1);
+            // pair the two keys of an operand register: x = {k0.j, k1.j, k0.j', k1.j'}
+            const uint32_t x01a = __byte_perm(w[0], w[1], 0x5140), x01b = __byte_perm(w[0], w[1], 0x7362);
+            const uint32_t x23a = __byte_perm(w[2], w[3], 0x5140), x23b = __byte_perm(w[2], w[3], 0x7362);
+            auto exact = [&](uint32_t packed) {   // {0x64 q1' 0x64 q0'} -> {q0, q1} as f16 integers
+                const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&packed), bias);
+                return *reinterpret_cast<const uint32_t*>(&v);
+            };
+            const uint32_t a_lo[4] = {exact(__byte_perm(x01a, 0x64646464u, 0x5140)), exact(__byte_perm(x01a, 0x64646464u, 0x7362)),
+                                      exact(__byte_perm(x23a, 0x64646464u, 0x5140)), exact(__byte_perm(x23a, 0x64646464u, 0x7362))};
+            mma16816(o[blk][0], a_lo, b0, b1);
+            const uint32_t a_hi[4] = {exact(__byte_perm(x01b, 0x64646464u, 0x5140)), exact(__byte_perm(x01b, 0x64646464u, 0x7362)),
+                                      exact(__byte_perm(x23b, 0x64646464u, 0x5140)), exact(__byte_perm(x23b, 0x64646464u, 0x7362))};
+            mma16816(o[blk][1], a_hi, b0, b1);
+        }
+        __syncwarp();       // every lane is done with this stage's bytes
+        issue(tile + NS);
+    }
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // ---- merge the four warps' (m, l, O) in shared memory (same slabs as the kernel above) ----
+    __syncthreads();  // all warps are done with the raw stages (the merge slabs alias them)
+    constexpr int SLAB_STRIDE = HD + 4;
+    float* slab = reinterpret_cast<float*>(smem_raw);   // [4][16][SLAB_STRIDE]
+    float lq[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        float v = l_run[j];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        lq[j] = v;
+    }
+    if (g == 0) {
+        s_m[warp][2 * t] = m_run[0], s_m[warp][2 * t + 1] = m_run[1];
+        s_l[warp][2 * t] = lq[0], s_l[warp][2 * t + 1] = lq[1];
+    }
+    if (lane < 8) s_m[warp][8 + lane] = ninf, s_l[warp][8 + lane] = 0.0f;   // rows 8..15 do not exist in this form
+    __syncthreads();
+    float fac[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int rr = 2 * t + j;
+        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
+        fac[j] = (m_run[j] == ninf) ? 0.0f : exp2f(m_run[j] - M);
+    }
+#pragma unroll
+    for (int blk = 0; blk < NBLK; blk++)
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int j = e & 1, dim = 32 * blk + 4 * g + 2 * mt + (e >> 1);
+                slab[(warp * kDecRows + 2 * t + j) * SLAB_STRIDE + dim] = fac[j] != 0.0f ? o[blk][mt][e] * fac[j] : 0.0f;
+            }
+    if (tid < kDecRows) {
+        const int rr = tid;
+        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
+        float L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) L += (s_m[w][rr] == ninf) ? 0.0f : s_l[w][rr] * exp2f(s_m[w][rr] - M);
+        s_M[rr] = M, s_L[rr] = L;
+    }
+    __syncthreads();
+    auto merged = [&](int rr, int cc) {
+        return (slab[(0 * kDecRows + rr) * SLAB_STRIDE + cc] + slab[(1 * kDecRows + rr) * SLAB_STRIDE + cc]) +
+               (slab[(2 * kDecRows + rr) * SLAB_STRIDE + cc] + slab[(3 * kDecRows + rr) * SLAB_STRIDE + cc]);
+    };
+
+    if (a.n_splits == 1) {
+        for (int idx = tid; idx < R * HD; idx += kThreads) {
+            const int rr = idx / HD, cc = idx % HD;
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            const float L = s_L[rr];
+            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + cc] = (L > 0.0f && iq < tq_b) ? merged(rr, cc) / L : 0.0f;
+        }
+    } else if (a.cluster_merge) {
+        for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
+            const int rr = idx / HD, cc = idx % HD;
+            slab[rr * SLAB_STRIDE + cc] = merged(rr, cc);
+        }
+        cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
+    } else {
+        const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
+        float* wo = a.ws_o + unit * kDecRows * HD;
+        for (int idx = tid; idx < R * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);
+        if (tid < kDecRows) {
+            a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
+            a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
+        }
+    }
+}
+
 // One warp per (batch, kv-head, row): log-sum-exp merge of the split partials.
 template <int HD>
 __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a) {
@@ -1489,7 +1805,17 @@ int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
     const size_t smem = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
-    if (!a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
+    static const bool keys_on_m = [] {   // B200_DECODE_Q8T=0 keeps the rows-on-M register kernel (A/B runs)
+        const char* e = getenv("B200_DECODE_Q8T");
+        return !(e && e[0] == '0');
+    }();
+    if (keys_on_m && !a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
+        auto kern = fattn_decode_q8t_kernel<HD>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        launch_split(kern, grid, smem, st, a);
+    } else if (!a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
         auto kern = fattn_decode_q8reg_kernel<HD, true, true>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
