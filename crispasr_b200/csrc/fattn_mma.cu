@@ -1306,7 +1306,20 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     return y;
 }
 
-template <int HD>
+__device__ __forceinline__ void mma16832_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// S8: the score product runs on the int8 tensor path.  The K quants are the A operand as they lie in the cache (no
+// byte permutes, no bias, no conversion at all); the query row is split once per CTA into two int8 planes per
+// 32-element block, q = dq*(hi + lo/254) with hi = round(x/dq), lo = round((x - dq*hi)*254/dq), dq = max|x|/127, which
+// keeps an absolute error of dq/508 = 1.5e-5 of the block maximum per element (F16 itself resolves 4.9e-4 of a
+// value).  Per block two k32 MMAs give exact int32 dots, combined as 254*hi + lo, converted once and scaled by
+// fp32(d_k)*dq/254.  This empties the integer ALU pipe of the K side, which bounds the F16 form of this kernel.
+template <int HD, bool S8>
 __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const FattnArgs a) {
     constexpr int NBLK = HD / 32, RB = NBLK * 34;
     constexpr int RAW_BYTES = kDecBN * RB;   // one raw K or V tile
@@ -1362,23 +1375,72 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, ch)) * 16) = val;
     }
     __syncthreads();
-    // Q as the B operand of S^T = K.Q^T: column n = query row g; per (block, k-step) the thread's four contraction
-    // indices are dims 32blk + 16ks + {4t..4t+3} (the same permutation the K bytes are read in): one 8-byte read.
+    // S8: the two int8 planes and the block scales of the 8 query rows, built once by 8 * NBLK threads in shared memory
+    // behind the f16 rows (the raw stages are not touched: their copies are already in flight)
+    // (rows 8..15 of the f16 Q tile do not exist in this kernel: the planes take their 16 * HD bytes; the block scales
+    // borrow the first 8 * NBLK floats of s_l, which is not used before the epilogue - four CTAs per SM leave no room
+    // for more static shared memory)
+    int8_t* s_qhi = reinterpret_cast<int8_t*>(sQ) + 8 * HD * sizeof(__half);
+    int8_t* s_qlo = s_qhi + 8 * HD;
+    float* s_qd = &s_l[0][0];
+    if (S8) {
+        if (tid < 8 * NBLK) {
+            const int rr = tid / NBLK, blk = tid % NBLK;
+            float x[32];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) {
+                const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, 4 * blk + c4)) * 16);
+                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[i]));
+                    x[c4 * 8 + 2 * i] = f2.x, x[c4 * 8 + 2 * i + 1] = f2.y;
+                }
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
+            const float dq = amax / 127.0f, inv = dq > 0.0f ? 1.0f / dq : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const float hi = rintf(x[i] * inv);
+                const float lo = fminf(fmaxf(rintf((x[i] - dq * hi) * inv * 254.0f), -127.0f), 127.0f);
+                s_qhi[rr * HD + blk * 32 + i] = (int8_t)hi, s_qlo[rr * HD + blk * 32 + i] = (int8_t)lo;
+            }
+            s_qd[rr * NBLK + blk] = dq * (1.0f / 254.0f);
+        }
+        __syncthreads();
+    }
+    // Q as the B operand of S^T = K.Q^T: column n = query row g.  F16 form: per (block, k-step) the thread's four
+    // contraction indices are dims 32blk + 16ks + {4t..4t+3} (the same permutation the K bytes are read in): one 8-byte
+    // read.  S8 form: per block, k = 4t..4t+3 (b0) and 16+4t..16+4t+3 (b1) of both planes, no permutation.
     uint32_t qb[NBLK][2][2];
 #pragma unroll
     for (int blk = 0; blk < NBLK; blk++)
 #pragma unroll
         for (int ks = 0; ks < 2; ks++) {
-            const int ch = 4 * blk + 2 * ks + (t >> 1);
-            const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(sQ) + (g * (HD / 8) + swz<HD>(g, ch)) * 16 + (t & 1) * 8);
-            qb[blk][ks][0] = w.x, qb[blk][ks][1] = w.y;
+            if (S8) {
+                // ks = plane (0 = hi, 1 = lo); [.][0] = k 4t.., [.][1] = k 16+4t..
+                const int8_t* plane = (ks ? s_qlo : s_qhi) + g * HD;
+                qb[blk][ks][0] = *reinterpret_cast<const uint32_t*>(plane + blk * 32 + 4 * t);
+                qb[blk][ks][1] = *reinterpret_cast<const uint32_t*>(plane + blk * 32 + 16 + 4 * t);
+            } else {
+                const int ch = 4 * blk + 2 * ks + (t >> 1);
+                const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(sQ) + (g * (HD / 8) + swz<HD>(g, ch)) * 16 + (t & 1) * 8);
+                qb[blk][ks][0] = w.x, qb[blk][ks][1] = w.y;
+            }
         }
-    // -1152 * (sum of the query row's f16 values over a block), for this thread's accumulator columns (rows 2t, 2t+1)
+    // F16 form: -1152 * (sum of the query row's f16 values over a block); S8 form: the row's block scale dq / 254 -
+    // for this thread's accumulator columns (rows 2t, 2t+1)
     float negc[NBLK][2];
 #pragma unroll
     for (int blk = 0; blk < NBLK; blk++)
 #pragma unroll
         for (int j = 0; j < 2; j++) {
+            if (S8) {
+                negc[blk][j] = s_qd[(2 * t + j) * NBLK + blk];
+                continue;
+            }
             const int rr = 2 * t + j;
             float sum = 0.0f;
 #pragma unroll
@@ -1418,6 +1480,32 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         const bool live[2] = {all_live || g < rows_valid, all_live || g + 8 < rows_valid};
 #pragma unroll
         for (int blk = 0; blk < NBLK; blk++) {
+            if (S8) {
+                // the K bytes are the A operand as they lie: words at quants 4t..4t+3 and 16+4t.. of keys g and g+8
+                uint32_t af[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint8_t* bp = rowp[i & 1] + blk * 34 + 2 + 16 * (i >> 1) + 4 * t;
+                    if (blk & 1) {
+                        af[i] = *reinterpret_cast<const uint32_t*>(bp);
+                    } else {
+                        const uint16_t* hp = reinterpret_cast<const uint16_t*>(bp);
+                        af[i] = hp[0] | ((uint32_t)hp[1] << 16);
+                    }
+                }
+                int ahi[4] = {0, 0, 0, 0}, alo[4] = {0, 0, 0, 0};
+                mma16832_s8(ahi, af, qb[blk][0][0], qb[blk][0][1]);
+                mma16832_s8(alo, af, qb[blk][1][0], qb[blk][1][1]);
+                const uint16_t d0b = live[0] ? *reinterpret_cast<const uint16_t*>(rowp[0] + blk * 34) : (uint16_t)0;
+                const uint16_t d1b = live[1] ? *reinterpret_cast<const uint16_t*>(rowp[1] + blk * 34) : (uint16_t)0;
+                const float d0 = __half2float(__ushort_as_half(d0b)), d1 = __half2float(__ushort_as_half(d1b));
+                // exact integer dot of the block: 254 * hi + lo (|.| < 2^28), then one conversion and the two scales
+                st[0] = fmaf(d0 * negc[blk][0], (float)(ahi[0] * 254 + alo[0]), st[0]);
+                st[1] = fmaf(d0 * negc[blk][1], (float)(ahi[1] * 254 + alo[1]), st[1]);
+                st[2] = fmaf(d1 * negc[blk][0], (float)(ahi[2] * 254 + alo[2]), st[2]);
+                st[3] = fmaf(d1 * negc[blk][1], (float)(ahi[3] * 254 + alo[3]), st[3]);
+                continue;
+            }
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int ks = 0; ks < 2; ks++) {
@@ -1805,12 +1893,20 @@ int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
     const size_t smem = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
-    static const bool keys_on_m = [] {   // B200_DECODE_Q8T=0 keeps the rows-on-M register kernel (A/B runs)
+    // B200_DECODE_Q8T=0 keeps the rows-on-M register kernel, =1 (default) the keys-on-M kernel with F16 score MMAs, =2
+    // the keys-on-M kernel with int8 score MMAs (measured equal at 256 streams, 5 % slower at 8: its set-up; A/B runs)
+    static const int keys_on_m = [] {
         const char* e = getenv("B200_DECODE_Q8T");
-        return !(e && e[0] == '0');
+        return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
     }();
-    if (keys_on_m && !a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
-        auto kern = fattn_decode_q8t_kernel<HD>;
+    if (keys_on_m == 2 && !a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
+        auto kern = fattn_decode_q8t_kernel<HD, true>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        launch_split(kern, grid, smem, st, a);
+    } else if (keys_on_m == 1 && !a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
+        auto kern = fattn_decode_q8t_kernel<HD, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e != cudaSuccess) return (int)e;
