@@ -60,9 +60,12 @@ WORKLOADS = {
     # the same step over a pool as a running beam search leaves it: 3584 cells, the 5 beams share a 224-token prefix
     # and own 224 private cells each, scattered over the pool.  "dense" is the reference's form (every beam row scans
     # every pooled cell through the F16 membership mask), "index" makes each beam a batch entry that gathers its own
-    # 448 cells through ext->kv_index.  Algorithmic bytes of both: the 1344 live cells, read once.
+    # 448 cells through ext->kv_index, "union" keeps the beams as query rows over ONE list of the 1344 live cells with
+    # a compact mask over its entries.  Algorithmic bytes of all three: the 1344 live cells, read once.
     "whisper_large_v3_decode_self_pool_dense": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=3584, hd=64,
                                                     kv="f16", seed=1, unit_name="segment-steps", pool=(224, 224, "dense")),
+    "whisper_large_v3_decode_self_pool_union": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=3584, hd=64,
+                                                    kv="f16", seed=1, unit_name="segment-steps", pool=(224, 224, "union")),
     "whisper_large_v3_decode_self_pool_index": dict(kind="decode", layers=32, units=64, H=20, Hkv=20, Tq=5, Lk=3584, hd=64,
                                                     kv="f16", seed=1, unit_name="segment-steps", pool=(224, 224, "index")),
     # LLM prefill: 375 audio + 32 text tokens, causal, GQA 32/8 over a Q8_0 cache, 8 streams
@@ -80,7 +83,8 @@ WORKLOADS = {
 
 # (workload, units per GPU or None for the workload's own) measured into the `workloads` object of a 1-GPU run
 EXTRA = [("whisper_large_v3_decode_cross", None), ("whisper_large_v3_decode_self", None),
-         ("whisper_large_v3_decode_self_pool_dense", None), ("whisper_large_v3_decode_self_pool_index", None), ("voxtral_decode_q8_0", 8),
+         ("whisper_large_v3_decode_self_pool_dense", None), ("whisper_large_v3_decode_self_pool_index", None),
+         ("whisper_large_v3_decode_self_pool_union", None), ("voxtral_decode_q8_0", 8),
          ("voxtral_decode_q8_0", 256), ("voxtral_prefill_q8_0", None), ("parakeet_relpos_encoder", None)]
 
 TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "dram_traffic.md")
@@ -396,6 +400,16 @@ class DeviceWorkload:
             if form == "dense":
                 from oracle import oracle as orc_mask   # input generation only: the beam-membership mask rule
                 mask = torch.from_numpy(orc_mask.whisper_beam_mask(cell_pos, bits, tok_seq, tok_pos)[None, None]).to(dev)
+            elif form == "union":
+                stride = -(-(prefix + beams * suffix) // 64) * 64
+                uidx, ulen, umask = np.zeros(stride, np.int32), np.zeros(1, np.int32), np.zeros((beams, stride), np.uint16)
+                rc = b200.lib().b200_beam_cells_to_union(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data,
+                                                         tok_pos.ctypes.data, beams, uidx.ctypes.data, stride, ulen.ctypes.data,
+                                                         umask.ctypes.data)
+                assert rc == 0
+                mask = torch.from_numpy(umask.view(np.float16)[None, None]).to(dev)
+                kw["kv_index"] = torch.from_numpy(np.tile(uidx[None], (units, 1))).to(dev)
+                kw["kv_len"] = torch.from_numpy(np.tile(ulen, units)).to(dev)
             else:
                 stride = prefix + suffix
                 idx, lens = np.zeros((beams, stride), np.int32), np.zeros(beams, np.int32)

@@ -108,6 +108,7 @@ SYMBOLS = {
     "b200_kv_append": (C.c_int, [C.c_void_p, C.c_int, TP, TP, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200_kv_copy_stream": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "b200_beam_cells_to_index": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "b200_beam_cells_to_union": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "b200_relpos_table": (C.c_int, [TP, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_relpos_cache_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "b200_relpos_cache_destroy": (None, [C.c_void_p]),

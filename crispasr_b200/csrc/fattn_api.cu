@@ -180,7 +180,9 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     memset(&a, 0, sizeof(a));
     if (mask) {
         if ((rc = check_operand(mask, false, true, false))) return rc;
-        if (mask->ne[0] != Lk || mask->ne[1] < Tq) return B200_E_SHAPE;
+        // one mask value per logical key: the rows of K, or the entries of the index lists when keys are gathered
+        const int64_t n_logical = (ext && ext->kv_index) ? ext->kv_index_stride : Lk;
+        if (mask->ne[0] != n_logical || mask->ne[1] < Tq) return B200_E_SHAPE;
         if (mask->ne[2] != 1 && mask->ne[2] != H) return B200_E_SHAPE;
         if (mask->ne[3] != 1 && mask->ne[3] != B) return B200_E_SHAPE;
         a.mask = make_view(mask);
@@ -258,7 +260,11 @@ int make_plan(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, 
     // kernel choice
     int kernel = B200_KERNEL_TILE_MMA;
     const bool decode_ok = !a.relpos && Tq * (H / Hkv) <= 16;
-    if (a.kv_index && (!decode_ok || a.has_mask || a.causal || a.softcap != 0.0f || a.q_len)) return B200_E_UNSUPPORTED;
+    // index lists: the decode kernel only; a mask must be one the F16 ring can stage (16-byte aligned rows, no ALiBi)
+    if (a.kv_index && (!decode_ok || a.causal || a.softcap != 0.0f || a.q_len || (a.has_mask && (!a.mask.vec16 || a.n2 != 0))))
+        return B200_E_UNSUPPORTED;
+    if (a.kv_index && a.has_mask && (a.k.type != B200_TYPE_F16 || !a.k.vec16 || !a.v.vec16 || (a.hd != 32 && a.hd != 64 && a.hd != 128)))
+        return B200_E_UNSUPPORTED;
     const bool tc5_ok = tc5_supported(a);
     const int override_k = g_override.load(std::memory_order_relaxed);
     if (decode_ok) kernel = B200_KERNEL_DECODE_SPLIT;
@@ -568,6 +574,34 @@ B200_API int b200_beam_cells_to_index(const int32_t* cell_pos, const uint32_t* c
         len_out[j] = n;
         for (int i = n; i < stride; i++) row[i] = 0;   // never read (beyond kv_len), kept in range all the same
     }
+    return B200_OK;
+}
+
+B200_API int b200_beam_cells_to_union(const int32_t* cell_pos, const uint32_t* cell_seq_bits, int n_cells,
+                                      const int32_t* tok_seq, const int32_t* tok_pos, int n_tokens,
+                                      int32_t* index_out, int stride, int32_t* len_out, uint16_t* mask_out) {
+    if (!cell_pos || !cell_seq_bits || !tok_seq || !tok_pos || !index_out || !len_out || !mask_out) return B200_E_NULL;
+    if (n_cells < 0 || n_tokens < 0 || stride <= 0) return B200_E_SHAPE;
+    for (int j = 0; j < n_tokens; j++)
+        if (tok_seq[j] < 0 || tok_seq[j] >= 32) return B200_E_SHAPE;
+    int n = 0;
+    for (int i = 0; i < n_cells; i++) {
+        bool any = false;
+        for (int j = 0; j < n_tokens && !any; j++) any = ((cell_seq_bits[i] >> tok_seq[j]) & 1u) && cell_pos[i] <= tok_pos[j];
+        if (!any) continue;   // a cell no token of this step can see (free, or ahead of every token): not in the list
+        if (n == stride) return B200_E_LIMIT;
+        index_out[n] = i;
+        for (int j = 0; j < n_tokens; j++) {
+            const bool visible = ((cell_seq_bits[i] >> tok_seq[j]) & 1u) && cell_pos[i] <= tok_pos[j];
+            mask_out[(size_t)j * stride + n] = visible ? 0x0000u : 0xFC00u;   // F16 0 / -inf, the reference's values
+        }
+        n++;
+    }
+    for (int i = n; i < stride; i++) {
+        index_out[i] = 0;
+        for (int j = 0; j < n_tokens; j++) mask_out[(size_t)j * stride + i] = 0xFC00u;
+    }
+    *len_out = n;
     return B200_OK;
 }
 

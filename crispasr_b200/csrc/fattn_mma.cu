@@ -607,7 +607,8 @@ __device__ __forceinline__ void cluster_merge_store(const FattnArgs& a, const fl
     cluster_sync_all();
 }
 
-// IDX (F16 ring, PLAIN): keys are gathered through ext->kv_index (one list per batch entry).
+// IDX (F16 ring; PLAIN or STAGE_MASK): keys are gathered through ext->kv_index (one list per batch entry); an explicit
+// mask is then indexed by the logical key, like the list.
 template <int HD, int MODE, bool STAGE_MASK = false, bool PLAIN = false, bool LOW = false, bool IDX = false>
 __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_decode_split_kernel(const FattnArgs a) {
     constexpr int NR = LOW ? 1 : 2, NE = 2 * NR;   // live row halves / accumulator elements per n-tile
@@ -673,7 +674,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
                 const int rr = tid >> 3, ch = tid & 7;
                 const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
                 const int key0 = tile * kDecBN + ch * 8;
-                const int nbytes = max(0, min(8, a.Lk - key0)) * 2;   // the mask row holds Lk values; the rest reads as 0
+                const int n_logical = a.kv_index ? a.kv_index_stride : a.Lk;   // a mask row holds one value per logical key
+                const int nbytes = max(0, min(8, n_logical - key0)) * 2;          // the rest reads as 0
                 const uint8_t* src = a.mask.p + (int64_t)iq * a.mask.nb1 + (int64_t)(hq % a.mask_ne2) * a.mask.nb2 +
                                      (int64_t)(b % a.mask_ne3) * a.mask.nb3 + (int64_t)(nbytes ? key0 : 0) * 2;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(sMask + ((stage * R + rr) * kDecBN + ch * 8))),
@@ -1819,7 +1821,19 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
     const bool low = a.Tq * a.gqa <= 8;
-    if (staged_mask && low) {
+    if (staged_mask && a.kv_index && low) {   // a shared index list plus a compact membership mask over its entries
+        auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem_attr, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        launch_split(kern, grid, smem, st, a);
+    } else if (staged_mask && a.kv_index) {
+        auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16, false, false, MODE == kDecAsyncF16>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem_attr, smem_set);
+        if (e != cudaSuccess) return (int)e;
+        launch_split(kern, grid, smem, st, a);
+    } else if (staged_mask && low) {
         auto kern = fattn_decode_split_kernel<HD, MODE, MODE == kDecAsyncF16, false, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem_attr, smem_set);

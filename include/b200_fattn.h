@@ -103,9 +103,13 @@ typedef struct b200_fattn_ext {
      * kv_index is a device array [B][kv_index_stride]; logical key i of batch entry b is row kv_index[b][i] of
      * K and V (rows of batch entry b / (B/Bk), so the beams of one segment are batch entries that share its pool),
      * for i < kv_len[b] (kv_len is then required; kv_len[b] <= kv_index_stride).  Entries are clamped to
-     * [0, Lk).  Only for launches that b200_fattn_plan maps to B200_KERNEL_DECODE_SPLIT, without mask and without
-     * the causal flag (a list already says which keys a row sees); otherwise B200_E_UNSUPPORTED.
-     * b200_beam_cells_to_index builds the lists from whisper's cells. */
+     * [0, Lk).  Two ways to use it: one list per beam (every beam a batch entry with Tq = 1, no mask:
+     * b200_beam_cells_to_index), or one list per segment holding the UNION of the cells its beams can see, the beams
+     * as the Tq query rows, and a compact F16 `mask` [kv_index_stride, Tq] over the list's entries that says which
+     * beam sees which entry (b200_beam_cells_to_union) - every live cell is then read once for all beams.  With
+     * kv_index the mask has one value per list entry (mask.ne[0] == kv_index_stride) and 16-byte aligned rows.
+     * Only for launches that b200_fattn_plan maps to B200_KERNEL_DECODE_SPLIT, without the causal flag, softcap or
+     * ALiBi; the masked form needs an F16 pool with 16-byte aligned rows; otherwise B200_E_UNSUPPORTED. */
     int32_t kv_index_stride;
     const int32_t* kv_index;
     /* Device array [B] of valid query rows per batch entry (rows >= q_len[b] are not computed; their dst rows are
@@ -336,6 +340,13 @@ B200_API int b200_kv_copy_stream(b200_kv_cache* kv, int dst_stream, int src_stre
 B200_API int b200_beam_cells_to_index(const int32_t* cell_pos, const uint32_t* cell_seq_bits, int n_cells,
                                       const int32_t* tok_seq, const int32_t* tok_pos, int n_tokens,
                                       int32_t* index_out, int stride, int32_t* len_out);
+/* The shared form: ONE list (index_out[stride], ascending cell order, *len_out entries) of the cells that at least one
+ * of the n_tokens tokens can see, and the compact mask mask_out[n_tokens][stride] over its entries (F16 bits: 0 where
+ * the reference's mask has 0, -inf where it has -inf or beyond the list).  The step then reads every live cell once
+ * for all beams instead of scanning the whole pool (reference) or once per beam (b200_beam_cells_to_index). */
+B200_API int b200_beam_cells_to_union(const int32_t* cell_pos, const uint32_t* cell_seq_bits, int n_cells,
+                                      const int32_t* tok_seq, const int32_t* tok_pos, int n_tokens,
+                                      int32_t* index_out, int stride, int32_t* len_out, uint16_t* mask_out);
 
 /* ------------------------------------------------------------------------------------------
  * Relative-position table of the FastConformer attention block.  Replaces make_pos_enc

@@ -313,3 +313,25 @@ def test_beam_cells_to_index_is_the_complement_of_the_mask_rule(b200, orc):
         assert idx[j, :lens[j]].tolist() == np.flatnonzero(mask[j] == 0).tolist()
     assert L.b200_beam_cells_to_index(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data, tok_pos.ctypes.data,
                                       n_tok, idx.ctypes.data, 8, lens.ctypes.data) == abi.E_LIMIT
+
+
+def test_beam_cells_to_union_lists_each_visible_cell_once(b200, orc):
+    """The shared list holds every cell some token of the step can see, in pool order; the compact mask over the
+    list's entries is the reference's mask (src/crispasr.cpp:3480-3488) restricted to those columns."""
+    L = b200.lib()
+    rng = np.random.default_rng(11)
+    n_cells, n_tok, stride = 300, 5, 320
+    cell_pos = rng.integers(0, 60, n_cells).astype(np.int32)
+    bits = rng.integers(0, 32, n_cells).astype(np.uint32)
+    tok_seq, tok_pos = np.arange(n_tok, dtype=np.int32), rng.integers(20, 60, n_tok).astype(np.int32)
+    idx, n = np.full(stride, -1, np.int32), np.zeros(1, np.int32)
+    cmask = np.zeros((n_tok, stride), np.uint16)
+    args = (cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data, tok_pos.ctypes.data, n_tok)
+    assert L.b200_beam_cells_to_union(*args, idx.ctypes.data, stride, n.ctypes.data, cmask.ctypes.data) == 0
+    mask = orc.whisper_beam_mask(cell_pos, bits, tok_seq, tok_pos)   # (n_tok, n_cells) f16: 0 or -inf
+    seen = np.flatnonzero((mask == 0).any(axis=0))
+    assert idx[:n[0]].tolist() == seen.tolist()
+    got = cmask.view(np.float16)
+    assert np.array_equal(got[:, :n[0]], mask[:, seen])
+    assert np.all(np.isneginf(got[:, n[0]:])) and np.all(idx[n[0]:] == 0)   # the tail is masked out and points at a valid row
+    assert L.b200_beam_cells_to_union(*args, idx.ctypes.data, 8, n.ctypes.data, cmask.ctypes.data) == abi.E_LIMIT

@@ -74,6 +74,20 @@ def test_index_lists_equal_the_dense_mask_form(b200, orc, kv, case):
     assert ma <= 2e-3 and rl <= 1e-3, f"index form vs dense form: {ma:.2e} / {rl:.2e}"
     if case == "one beam empty":
         assert not got[0, 1].any() and not dense[0, 1].any()
+    if kv == "f16":
+        # the shared form: one list with the union of the live cells, the beams as query rows, a compact mask over the
+        # list's entries - every live cell read once for all beams
+        ustride = 256
+        uidx, ulen, umask = np.zeros(ustride, np.int32), np.zeros(1, np.int32), np.zeros((n_beams, ustride), np.uint16)
+        rc = b200.lib().b200_beam_cells_to_union(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data,
+                                                 tok_pos.ctypes.data, n_beams, uidx.ctypes.data, ustride, ulen.ctypes.data,
+                                                 umask.ctypes.data)
+        live = np.flatnonzero((mask[0, 0] == 0).any(axis=0))
+        assert rc == 0 and ulen[0] == len(live) and uidx[:ulen[0]].tolist() == live.tolist()
+        assert np.array_equal(umask.view(np.float16)[:, :ulen[0]], mask[0, 0][:, live])
+        got_u = gpu_op(b200, q, k, v, umask.view(np.float16)[None, None], kv_index=uidx[None], kv_len=ulen, **kw)
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+        assert_close(got_u, ref, "shared list + compact mask vs oracle")
     # every forced split count merges to the same result
     for ns in (1, 2, 3):
         assert b200.lib().b200_set_decode_splits(ns) == 0
