@@ -32,7 +32,10 @@ __device__ int g_tc5_status = 0;  // 0 ok, 1 = a bounded wait ran out in some CT
 
 #ifdef B200_TC5_TRACE
 __device__ long long g_tc5_trace[3][64][8];
-#define TC5_TRACE(role, j, k) do { if (blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == 0 && (j) < 64) g_tc5_trace[role][j][k] = clock64(); } while (0)
+#ifndef B200_TC5_TRACE_Z
+#define B200_TC5_TRACE_Z 0
+#endif
+#define TC5_TRACE(role, j, k) do { if (blockIdx.x == 1 && blockIdx.y == 3 && blockIdx.z == B200_TC5_TRACE_Z && (j) < 64) g_tc5_trace[role][j][k] = clock64(); } while (0)
 #else
 #define TC5_TRACE(role, j, k) do { } while (0)
 #endif
@@ -375,13 +378,15 @@ struct Tc5Smem {
     static constexpr int tile_bytes() { return kPanelBytes * (HD / 64); }
 };
 
-// EARLY (head_dim 64 without explicit mask): a softmax thread pulls its whole 128-column score row into registers at
-// the start of a tile and says so (s_read); the MMA thread issues S[j+1] right then instead of after P[j], so the next
-// score tile is computed under the exponentials of the current one and the softmax warps do not wait for the tensor
-// pipe between two tiles (the registers are the second score buffer).  P is computed 32 columns at a time against the
-// reference maximum with the tile maximum tracked in the same pass; a row that outgrew its reference redoes the tile
-// from the registers.
-template <int HD, int NSTG, bool HASMASK, bool EARLY = false>
+// EARLY (head_dim 64 without explicit mask; A/B variants, both measured slower than EARLY = 0 and opt-in):
+//   1  a softmax thread pulls its whole 128-column score row into registers at the start of a tile and says so
+//      (s_read); the MMA thread issues S[j+1] right then instead of after P[j], so the next score tile is computed
+//      under the exponentials of the current one.  With 168 registers per thread the row spills: 0.6x.
+//   2  the score columns are released after the SECOND 64-column half is in registers (no extra registers); a half
+//      that outgrew the reference maximum is redone from registers and the other half's probabilities are scaled.
+//      The score MMAs and the P.V MMAs are issued from two warps on two schedulers, each refilling the K (V) slots
+//      its own MMAs free.  Tile period of a traced CTA about equal to EARLY = 0; whole launches 0.79x.
+template <int HD, int NSTG, bool HASMASK, int EARLY = 0>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV) {
@@ -399,8 +404,9 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t sBar = sV + NSTG * TILE_BYTES;  // 8-byte slots
     const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8 * NSTG, bar_v_full = sBar + 16 * NSTG,
                    bar_v_empty = sBar + 24 * NSTG, bar_s_full = sBar + 32 * NSTG, bar_p_ready = bar_s_full + 8,
-                   bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24, bar_s_read = bar_s_full + 32;
-    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 40;
+                   bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24, bar_s_read = bar_s_full + 32,
+                   bar_s_drain = bar_s_full + 40;
+    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 48;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
     constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
@@ -461,6 +467,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         mbar_init(bar_o_done, 1);
         mbar_init(bar_pv_done, 1);
         mbar_init(bar_s_read, 4);    // one arrival per softmax warp
+        mbar_init(bar_s_drain, 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
@@ -503,7 +510,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t tmem_P = SEP_P ? tmem_base + kTile + HD : tmem_base;  // f16x2: cols [192,256) (hd 64) or aliasing S [0,64)
     const uint32_t tmem_O = tmem_base + kTile;    // cols [128,128+HD)
 
-    if (warp == 4) {
+    if (EARLY != 2 && warp == 4) {
         // ================= TMA producer =================
         if (lane == 0) {
             bool ok = true;
@@ -532,6 +539,95 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 // drain: wait (bounded) for the copies this thread still has in flight
                 for (int j = max(0, issued_k - NSTG); j < issued_k; j++)
                     for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_k_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
+                for (int j = max(0, issued_v - NSTG); j < issued_v; j++)
+                    for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_v_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
+            }
+        }
+    } else if (EARLY == 2 && warp == 4) {
+        // ================= K loader + score-MMA issuer (half-tile release variant) =================
+        // An issuing thread costs the other warps of its scheduler issue slots (60-80 clk per tcgen05 instruction), and
+        // a tile ends when the slowest softmax warp is done: the two products are issued from two schedulers, and each
+        // issuer refills the operand slots its own MMAs free (their completion lies a tile back: no real wait).
+        if (lane == 0) {
+            const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16);
+            constexpr uint32_t desc_hi = smem_desc_hi(1024);
+            bool ok = true;
+            int issued_k = min(NSTG, n_tiles);
+            for (int j = 0; j < n_tiles && ok; j++) {   // S[j]
+                const int slot = j % NSTG, use = j / NSTG;
+                // K[j+1] goes into the slot S[j-1] read (NSTG = 2); the softmax warps are already working on that product
+                const int jn = j + NSTG - 1;
+                if (j > 0 && jn < n_tiles) {
+                    const int ns = jn % NSTG, nu = jn / NSTG;
+                    ok = mbar_wait(bar_k_empty + 8 * ns, (nu - 1) & 1, s_abort);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_k_full + 8 * ns, TILE_BYTES);
+#pragma unroll
+                    for (int p = 0; p < PANELS; p++)
+                        tma_load_4d(sK + ns * TILE_BYTES + p * kPanelBytes, &tmK, bar_k_full + 8 * ns, p * 64, jn * kTile, hk, bk);
+                    issued_k = jn + 1;
+                }
+                ok = mbar_wait(bar_k_full + 8 * slot, use & 1, s_abort);
+                if (ok && j > 0) ok = mbar_wait(bar_s_read, (j - 1) & 1, s_abort);   // every softmax warp holds S[j-1] in registers
+                if (!ok) break;
+                if (j > 0) TC5_TRACE(1, j - 1, 0);
+                tc_fence_after();
+                const uint32_t kd = k_lo + slot * (TILE_BYTES >> 4);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    const uint32_t off16 = (uint32_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
+                    mma_ss(tmem_S, desc64(q_lo + off16, desc_hi), desc64(kd + off16, desc_hi), IDESC_S, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_s_full);
+                tc_commit(bar_k_empty + 8 * slot);
+                if (j > 0) TC5_TRACE(1, j - 1, 1);
+            }
+            if (!ok) {   // no score MMA and no K copy of this CTA may still be running when the CTA ends
+                tc_commit(bar_s_drain);
+                for (uint32_t it = 0; it < 65536 && !mbar_try_wait(bar_s_drain, 0); ++it) __nanosleep(256);
+                for (int j = max(0, issued_k - NSTG); j < issued_k; j++)
+                    for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_k_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
+            }
+        }
+    } else if (EARLY == 2 && warp == 5) {
+        // ================= V loader + P.V-MMA issuer (half-tile release variant) =================
+        if (lane == 0) {
+            const uint32_t v_lo = smem_desc_lo(sV, kPanelBytes);
+            constexpr uint32_t desc_hi = smem_desc_hi(1024);
+            bool ok = true;
+            int issued_v = min(NSTG, n_tiles);
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int slot = j % NSTG, use = j / NSTG;
+                // V[j+1] goes into the slot P.V[j-1] read; that product was issued a tile ago
+                const int jn = j + NSTG - 1;
+                if (j > 0 && jn < n_tiles) {
+                    const int ns = jn % NSTG, nu = jn / NSTG;
+                    ok = mbar_wait(bar_v_empty + 8 * ns, (nu - 1) & 1, s_abort);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_v_full + 8 * ns, TILE_BYTES);
+#pragma unroll
+                    for (int p = 0; p < PANELS; p++)
+                        tma_load_4d(sV + ns * TILE_BYTES + p * kPanelBytes, &tmV, bar_v_full + 8 * ns, p * 64, jn * kTile, hk, bk);
+                    issued_v = jn + 1;
+                }
+                ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
+                TC5_TRACE(1, j, 2);
+                if (ok) ok = mbar_wait(bar_p_ready, j & 1, s_abort);
+                if (!ok) break;
+                TC5_TRACE(1, j, 3);
+                tc_fence_after();
+                const uint32_t vd = v_lo + slot * (TILE_BYTES >> 4);
+                mma_ts(tmem_O, tmem_P, desc64(vd, desc_hi), IDESC_PV, j > 0 ? 1u : 0u);
+#pragma unroll
+                for (int ks = 1; ks < kTile / 16; ks++) mma_ts(tmem_O, tmem_P + ks * 8, desc64(vd + ks * (2048 >> 4), desc_hi), IDESC_PV, 1u);
+                tc_commit(bar_v_empty + 8 * slot);
+                tc_commit(bar_pv_done);
+                if (j + 1 == n_tiles) tc_commit(bar_o_done);
+                TC5_TRACE(1, j, 4);
+            }
+            if (!ok) {
+                tc_commit(bar_o_done);
+                for (uint32_t it = 0; it < 65536 && !mbar_try_wait(bar_o_done, 0); ++it) __nanosleep(256);
                 for (int j = max(0, issued_v - NSTG); j < issued_v; j++)
                     for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_v_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
             }
@@ -567,6 +663,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     if (more) ok = mbar_wait(bar_k_full + 8 * nslot, nuse & 1, s_abort);
                     if (ok) ok = mbar_wait(bar_s_read, j & 1, s_abort);
                     if (!ok) break;
+                    if (j > 0) TC5_TRACE(1, j, 0);
                     if (more) {
                         tc_fence_after();
                         const uint32_t kd = k_lo + nslot * (TILE_BYTES >> 4);
@@ -578,6 +675,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                         tc_commit(bar_s_full);
                         tc_commit(bar_k_empty + 8 * nslot);
                     }
+                    if (j > 0) TC5_TRACE(1, j, 1);
                     ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
                 } else {
                     ok = mbar_wait(bar_v_full + 8 * slot, use & 1, s_abort);
@@ -644,7 +742,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                                             (int64_t)(h % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3
                                       : nullptr;
         const float c_exp = HASMASK ? 1.0f : c;   // with a mask the scores are moved to the log2 domain by apply_mask64
-        if constexpr (EARLY) {
+        if constexpr (EARLY == 1) {
             const uint64_t c2 = pack2(c, c);
             for (int j = 0; j < n_tiles; j++) {
                 ok = mbar_wait(bar_s_full, j & 1, s_abort);
@@ -749,6 +847,97 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 if (!ok) break;
                 l_run += lsum;
                 if (tid == 0) TC5_TRACE(0, j, 1);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_p_ready);
+                if (tid == 0) TC5_TRACE(0, j, 2);
+            }
+        } else if constexpr (EARLY == 2) {
+            // Half-tile release: the score columns are handed back (s_read) as soon as the second 64-column half is in
+            // registers, so the tensor pipe computes S[j+1] under the exponentials of that half and the next tile's
+            // scores are waiting when this loop comes round.  Nothing is read from the score columns afterwards: a
+            // half that outgrew the reference maximum is redone from the registers it still sits in, and when that
+            // is the second half the first half's probabilities (finite: they passed their own check) are scaled.
+            for (int j = 0; j < n_tiles; j++) {
+                ok = mbar_wait(bar_s_full, j & 1, s_abort);
+                if (!ok) break;
+                if (tid == 0) TC5_TRACE(0, j, 0);
+                tc_fence_after();
+                const int n_valid = kend - j * kTile;  // columns >= n_valid of this row are masked
+                const bool full_tile = __all_sync(0xffffffffu, n_valid >= kTile);
+                uint32_t preg[2][32];
+                float lsum = 0.0f;
+                bool pv_waited = false;
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    uint32_t sreg[2][32];
+                    tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
+                    tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                    tmem_wait_ld();
+                    if (hh == 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_s_read);
+                        if (lane == 0) TC5_TRACE(2, j, 2 + warp);
+                    }
+                    if (tid == 0) TC5_TRACE(0, j, 3 + 2 * hh);
+                    if (HASMASK) apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
+                    if (j == 0 && hh == 0) m_ref = row_max64(sreg, 0, full_tile ? 2 * kTile : n_valid) * c_exp;
+                    for (int attempt = 0; attempt < 2; attempt++) {
+                        const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+                        float mx = -INFINITY, ls = 0.0f;
+                        if (full_tile) softmax64<false>(sreg, preg[hh], c_exp, m_use, 0, 0, mx, ls);
+                        else softmax64<true>(sreg, preg[hh], c_exp, m_use, hh * 64, n_valid, mx, ls);
+                        const float m_tile = mx * c_exp;
+                        if (attempt == 1 || !__any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold)) {
+                            lsum += ls;
+                            break;
+                        }
+                        if (j > 0 && !pv_waited) {  // O must be at rest: P.V of the previous tile has completed
+                            ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
+                            if (!ok) break;
+                            tc_fence_after();
+                            pv_waited = true;
+                        }
+                        const float m_new = fmaxf(m_ref, m_tile);
+                        const float alpha = (m_new == -INFINITY) ? 1.0f : ex2(m_ref - m_new);
+                        l_run *= alpha;
+                        lsum *= alpha;
+                        if (hh == 1) {
+                            const __half2 a2 = __float2half2_rn(alpha);
+#pragma unroll
+                            for (int i = 0; i < 32; i++) {
+                                const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&preg[0][i]), a2);
+                                preg[0][i] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+                        }
+                        if (j > 0) {
+#pragma unroll
+                            for (int q4 = 0; q4 < HD / 32; q4++) {
+                                uint32_t oreg[32];
+                                tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int i = 0; i < 32; i++) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                                tmem_st32(tmem_O + lane_base + q4 * 32, oreg);
+                            }
+                        }
+                        m_ref = m_new;
+                    }
+                    if (!ok) break;
+                    if (tid == 0) TC5_TRACE(0, j, 4 + 2 * hh);
+                }
+                if (!ok) break;
+                l_run += lsum;
+                if (j > 0 && !pv_waited) {  // P[j-1] must have been consumed before P[j] overwrites it
+                    ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (tid == 0) TC5_TRACE(0, j, 1);
+                tmem_st32(tmem_P + lane_base, preg[0]);
+                tmem_st32(tmem_P + lane_base + 32, preg[1]);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -1422,6 +1611,38 @@ cudaError_t launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStrea
 }
 
 #include "fattn_tc5_pair.cuh"
+#include "fattn_tc5_split.cuh"
+
+// B200_PREFILL_SPLIT=1 selects the split-row kernel (eight softmax warps, scores released at once) for head_dim 64
+// without explicit mask.
+bool split_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200_PREFILL_SPLIT");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+
+bool split_supported(const FattnArgs& a) { return split_enabled() && a.hd == 64 && !a.has_mask && !a.relpos; }
+
+int launch_split(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+    CUtensorMap tmK, tmV;
+    if (!encode_kv_map(&tmK, a.k, a.hd, a.Lk, a.Hkv, a.B / a.bq) || !encode_kv_map(&tmV, a.v, a.hd, a.Lk, a.Hkv, a.B / a.bq)) {
+        snprintf(errbuf, errlen, "cuTensorMapEncodeTiled failed for K/V");
+        return B200_E_CUDA;
+    }
+    const size_t smem = 1024 + (size_t)5 * kPanelBytes + 64 + 72 + 8 + 2048 + 16;
+    dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);
+    auto kern = fattn_prefill_tc5_split_kernel;
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(kern, smem, smem_set);
+    if (e == cudaSuccess) e = launch_pdl(kern, grid, kThreadsSplit, smem, st, a, tmK, tmV);
+    if (e != cudaSuccess) {
+        snprintf(errbuf, errlen, "tcgen05 split-row prefill launch: %s", cudaGetErrorString(e));
+        return B200_E_CUDA;
+    }
+    return B200_OK;
+}
 
 // The paired-tile persistent kernel takes head_dim 64 without explicit mask and without causal bound.
 // B200_PREFILL_PAIR=1 selects it (the one-tile kernel is the default); B200_PREFILL_POLY=n (2..16) moves every n-th pair of
@@ -1483,17 +1704,19 @@ int launch_pair(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen
     return B200_OK;
 }
 
-// B200_PREFILL_EARLY=1 selects the early-score order in the one-tile head_dim 64 kernel (A/B runs; off by default).
-bool early_scores_enabled() {
-    static const bool on = [] {
-        const char* e = getenv("B200_PREFILL_EARLY");
-        return e && e[0] == '1';   // opt-in: with 168 registers per thread the 128-column row spills (7 M spill instructions per 8-segment launch) and the variant measures 0.6x
+// B200_PREFILL_EARLY=1 or 2 selects an early-score order in the one-tile head_dim 64 kernel (A/B runs; off by default).
+int early_scores_mode() {
+    static const int mode = [] {
+        const char* e = getenv("B200_PREFILL_EARLY");   // 0 (default), 1 or 2: see the kernel's EARLY parameter
+        const int v = e ? atoi(e) : 0;
+        return (v == 1 || v == 2) ? v : 0;
     }();
-    return on;
+    return mode;
 }
 
 template <int HD, int NSTG>
-int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
+int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen) {
+    const FattnArgs& a = a_in;
     CUtensorMap tmK, tmV;
     if (!encode_kv_map(&tmK, a.k, a.hd, a.Lk, a.Hkv, a.B / a.bq) || !encode_kv_map(&tmV, a.v, a.hd, a.Lk, a.Hkv, a.B / a.bq)) {
         snprintf(errbuf, errlen, "cuTensorMapEncodeTiled failed for K/V");
@@ -1510,8 +1733,15 @@ int launch_t(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
         if (e == cudaSuccess) {
             e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
         }
-    } else if (HD == 64 && early_scores_enabled()) {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64>;
+    } else if (HD == 64 && early_scores_mode() == 2) {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 2 : 0>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
+        }
+    } else if (HD == 64 && early_scores_mode() == 1) {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 1 : 0>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
@@ -1555,6 +1785,7 @@ bool tc5_supported(const FattnArgs& a) {
 int launch_prefill_tc5(const FattnArgs& a, cudaStream_t st, char* errbuf, size_t errlen) {
     if (a.relpos) return launch_relpos(a, st, errbuf, errlen);
     if (pair_supported(a)) return launch_pair(a, st, errbuf, errlen);
+    if (split_supported(a)) return launch_split(a, st, errbuf, errlen);
     if (a.hd == 64) return launch_t<64, 2>(a, st, errbuf, errlen);
     return launch_t<128, 1>(a, st, errbuf, errlen);
 }

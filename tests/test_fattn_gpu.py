@@ -139,6 +139,22 @@ def test_cfg3_large_v3_encoder_segments(b200, orc, kernel):
         assert b200.lib().b200_device_status() == 0
 
 
+@pytest.mark.parametrize("env", ["B200_PREFILL_EARLY=1", "B200_PREFILL_EARLY=2", "B200_PREFILL_SPLIT=1", "B200_PREFILL_PAIR=1"])
+def test_opt_in_prefill_variants(env):
+    """The head_dim 64 prefill variants that are kept for A/B runs (early score issue, split rows, paired tiles) are
+    selected per process by an environment variable: each runs an encoder-shaped and a causal case against the oracle
+    in a child process."""
+    import subprocess
+    import sys
+
+    name, value = env.split("=")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "tests", "variant_case.py")], env={**os.environ, name: value},
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == 2, r.stdout
+
+
 def test_voxtral_audio_encoder_f32_kv(b200, orc, kernel):
     """core_attn::encoder_self_attn (src/core/attention.h:517-580): contiguous F32 Q/K/V, Whisper large dims, no pad,
     no mask.  K/V are converted to F16 by a pre-pass into the workspace and the call runs on the tcgen05 kernel."""
