@@ -1186,7 +1186,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
             for (int i = 0; i < 4; i++) {
                 const int key = 2 * t + (i & 1) + 8 * (i >> 1);
                 const uint8_t* bp = rawV + key * RB + blk * 34;
-                db[i] = (all_live || key < rows_valid) ? *reinterpret_cast<const uint16_t*>(bp) : (uint16_t)0;
+                db[i] = *reinterpret_cast<const uint16_t*>(bp);
+                if (!all_live && key >= rows_valid) db[i] = (uint16_t)0;   // a dead key's scale may be any bit pattern: 0 * NaN
                 if (blk & 1) {
                     w[i] = *reinterpret_cast<const uint32_t*>(bp + 2 + 4 * g);
                 } else {
@@ -1434,29 +1435,31 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         }
     // F16 form: -1152 * (sum of the query row's f16 values over a block); S8 form: the row's block scale dq / 254 -
     // for this thread's accumulator columns (rows 2t, 2t+1)
+    if (!S8) {
+        // the 8 * NBLK block sums of the query rows, once per CTA: four threads per (row, block), one 16-byte chunk each
+        // (s_l is free until the epilogue)
+        const int pair = tid >> 2, c4 = tid & 3;
+        float sum = 0.0f;
+        if (pair < 8 * NBLK) {
+            const int rr = pair / NBLK, blk = pair % NBLK;
+            const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, 4 * blk + c4)) * 16);
+            const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[i]));
+                sum += f2.x + f2.y;
+            }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (pair < 8 * NBLK && c4 == 0) s_qd[pair] = -1152.0f * sum;
+        __syncthreads();
+    }
     float negc[NBLK][2];
 #pragma unroll
     for (int blk = 0; blk < NBLK; blk++)
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            if (S8) {
-                negc[blk][j] = s_qd[(2 * t + j) * NBLK + blk];
-                continue;
-            }
-            const int rr = 2 * t + j;
-            float sum = 0.0f;
-#pragma unroll
-            for (int c4 = 0; c4 < 4; c4++) {
-                const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sQ) + (rr * (HD / 8) + swz<HD>(rr, 4 * blk + c4)) * 16);
-                const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w4[i]));
-                    sum += f2.x + f2.y;
-                }
-            }
-            negc[blk][j] = -1152.0f * sum;
-        }
+        for (int j = 0; j < 2; j++) negc[blk][j] = s_qd[(2 * t + j) * NBLK + blk];
 
     float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};   // rows 2t, 2t+1; m_run is the same on the 8 lanes that share t
     float o[NBLK][2][4];   // [block][m-tile]: c0/c1 = dim 32blk+4g+2mt of rows 2t/2t+1, c2/c3 = dim +1
@@ -1508,7 +1511,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
                 st[3] = fmaf(d1 * negc[blk][1], (float)(ahi[3] * 254 + alo[3]), st[3]);
                 continue;
             }
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // the accumulators start at -1152 * sum_block(Q): the products of the biased halves land on the integer dot
+            float acc[4] = {negc[blk][0], negc[blk][1], negc[blk][0], negc[blk][1]};
 #pragma unroll
             for (int ks = 0; ks < 2; ks++) {
                 uint32_t w[2];
@@ -1527,17 +1531,23 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
                                         __byte_perm(w[0], 0x64646464u, 0x7362), __byte_perm(w[1], 0x64646464u, 0x7362)};
                 mma16816(acc, af, qb[blk][ks][0], qb[blk][ks][1]);
             }
-            const uint16_t d0b = live[0] ? *reinterpret_cast<const uint16_t*>(rowp[0] + blk * 34) : (uint16_t)0;
-            const uint16_t d1b = live[1] ? *reinterpret_cast<const uint16_t*>(rowp[1] + blk * 34) : (uint16_t)0;
-            const float d0 = __half2float(__ushort_as_half(d0b)), d1 = __half2float(__ushort_as_half(d1b));
-            st[0] = fmaf(d0, acc[0] + negc[blk][0], st[0]);
-            st[1] = fmaf(d0, acc[1] + negc[blk][1], st[1]);
-            st[2] = fmaf(d1, acc[2] + negc[blk][0], st[2]);
-            st[3] = fmaf(d1, acc[3] + negc[blk][1], st[3]);
+            // the scale is read whether or not the key is live (stale bytes of a finished stage are harmless here: dead
+            // scores are replaced by -inf below), so the common tile has no branch around the load
+            const float d0 = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rowp[0] + blk * 34)));
+            const float d1 = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(rowp[1] + blk * 34)));
+            st[0] = fmaf(d0, acc[0], st[0]);
+            st[1] = fmaf(d0, acc[1], st[1]);
+            st[2] = fmaf(d1, acc[2], st[2]);
+            st[3] = fmaf(d1, acc[3], st[3]);
         }
-        // scale to the log2 domain; keys beyond the valid length are masked
+        // scale to the log2 domain; keys beyond the valid length are masked (last tile of a stream only)
 #pragma unroll
-        for (int e = 0; e < 4; e++) st[e] = live[e >> 1] ? st[e] * c : ninf;
+        for (int e = 0; e < 4; e++) st[e] *= c;
+        if (!all_live) {
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (!live[e >> 1]) st[e] = ninf;
+        }
 
         // ---- lazy running maximum: only when some key outgrew the reference by 2^4 is it reduced over the warp ----
         const float lm[2] = {fmaxf(st[0], st[2]), fmaxf(st[1], st[3])};
