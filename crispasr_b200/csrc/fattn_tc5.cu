@@ -378,6 +378,53 @@ struct Tc5Smem {
     static constexpr int tile_bytes() { return kPanelBytes * (HD / 64); }
 };
 
+// Coalesced forms of the two per-row transfers of a CTA.  A thread that moves its own row makes every warp instruction
+// touch 32 rows (32 sectors for 16 bytes each); here a warp instruction covers whole rows, the row pointers travel by
+// shuffle from the lanes that own them (lane i of warp w owns row 32w + i).
+//
+// F32 query rows -> f16 operand tile: per instruction RPI = 128 / HD rows, lane l reads float4 number l % (HD/4) of row
+// l / (HD/4), converts and writes 8 bytes into the swizzled tile.  A null row pointer gives a zero row.
+template <int HD>
+__device__ __forceinline__ void load_q_rows_f32_coalesced(uint8_t* tile, int warp, int lane, const uint8_t* my_rowp) {
+    constexpr int F4 = HD / 4, RPI = 32 / F4;   // float4 per row; rows per warp instruction
+    const uint32_t plo = (uint32_t)reinterpret_cast<uintptr_t>(my_rowp), phi = (uint32_t)(reinterpret_cast<uintptr_t>(my_rowp) >> 32);
+    const int c = lane % F4, sub = lane / F4;
+#pragma unroll
+    for (int batch = 0; batch < 32 / RPI / 16; batch++) {
+        float4 f[16];
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const int src = (batch * 16 + k) * RPI + sub;
+            const uintptr_t p = (uintptr_t)__shfl_sync(0xffffffffu, plo, src) | ((uintptr_t)__shfl_sync(0xffffffffu, phi, src) << 32);
+            f[k] = p ? __ldg(reinterpret_cast<const float4*>(p) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const int row = warp * 32 + (batch * 16 + k) * RPI + sub;
+            const int cc = c >> 1;   // 16-byte chunk of the f16 row
+            *reinterpret_cast<uint2*>(tile + (cc >> 3) * kPanelBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4) + (c & 1) * 8) =
+                make_uint2(pack_half2(f[k].x, f[k].y), pack_half2(f[k].z, f[k].w));
+        }
+    }
+}
+
+// Output rows: each thread parks its scaled row in its warp's staging area (chunks swizzled by the row), then the warp
+// writes whole rows.  `stage` is this warp's 32 * HD floats; a null row pointer skips the row.
+template <int HD>
+__device__ __forceinline__ void store_o_rows_coalesced(float* stage, int lane, float* my_out) {
+    constexpr int F4 = HD / 4, RPI = 32 / F4;
+    __syncwarp();
+    const uint32_t plo = (uint32_t)reinterpret_cast<uintptr_t>(my_out), phi = (uint32_t)(reinterpret_cast<uintptr_t>(my_out) >> 32);
+    const int c = lane % F4, sub = lane / F4;
+#pragma unroll 4
+    for (int k = 0; k < 32 / RPI; k++) {
+        const int row = k * RPI + sub;
+        const uintptr_t p = (uintptr_t)__shfl_sync(0xffffffffu, plo, row) | ((uintptr_t)__shfl_sync(0xffffffffu, phi, row) << 32);
+        const float4 v = *reinterpret_cast<const float4*>(stage + row * HD + ((c ^ (row & 7)) << 2));
+        if (p) *(reinterpret_cast<float4*>(p) + c) = v;
+    }
+}
+
 // EARLY (head_dim 64 without explicit mask; A/B variants, both measured slower than EARLY = 0 and opt-in):
 //   1  a softmax thread pulls its whole 128-column score row into registers at the start of a tile and says so
 //      (s_read); the MMA thread issues S[j+1] right then instead of after P[j], so the next score tile is computed
@@ -495,8 +542,9 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         // Q tile -> shared memory (thread r writes row r)
         const int r = tid;
         const int iq = (q0 + r) / a.gqa, h = hk * a.gqa + (q0 + r) % a.gqa;
-        load_q_row<HD>(smem_gen, r, a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3, a.q.type,
-                       a.q.vec16 != 0, q0 + r < rows_total);
+        const uint8_t* rowp = a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3;
+        if (a.q.type == B200_TYPE_F32 && a.q.vec16) load_q_rows_f32_coalesced<HD>(smem_gen, warp, lane, q0 + r < rows_total ? rowp : nullptr);
+        else load_q_row<HD>(smem_gen, r, rowp, a.q.type, a.q.vec16 != 0, q0 + r < rows_total);
         fence_proxy_async();
         if (tid == 0) TC5_TRACE(2, 61, 1);
     }
@@ -1050,24 +1098,24 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         if (tid == 0) TC5_TRACE(2, 60, 2);
         if (ok) {
             tc_fence_after();
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            float* out = a.dst + (((int64_t)b * a.Tq + iq_dst) * a.H + h) * HD;
+            // dead rows are written as literal zeros (whatever the padding row of Q held never reaches dst), rows
+            // outside the tensor not at all.  The K/V stages are free once the last MMA has completed: they stage O.
+            const float inv = row_live && l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            float* out = (row_live || row_zero) ? a.dst + (((int64_t)b * a.Tq + iq_dst) * a.H + h) * HD : nullptr;
+            float* stage = reinterpret_cast<float*>(smem_gen + TILE_BYTES) + warp * 32 * HD;
 #pragma unroll
             for (int q4 = 0; q4 < HD / 32; q4++) {
                 uint32_t oreg[32];
                 tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
                 tmem_wait_ld();
-                if (row_live) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(out + q4 * 32 + i) =
-                            make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
-                                        __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv);
-                } else if (row_zero) {   // literal zeros: whatever the padding row of Q held never reaches dst
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out + q4 * 32 + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(stage + lane * HD + ((((q4 * 32 + i) >> 2) ^ (lane & 7)) << 2)) =
+                        row_live ? make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
+                                               __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+            store_o_rows_coalesced<HD>(stage, lane, out);
         }
     }
 
