@@ -204,12 +204,17 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "samples_under_load": len(load)}
 
 
+Q_TYPE = "f16"   # --q-type
+
+
 def make_inputs_np(w, units, rng):
     """One layer's operands for `units` units, numpy, in the workload's storage types."""
     from oracle import oracle as orc
     f16 = lambda shape, s=1.0: (rng.standard_normal(shape).astype(np.float32) * np.float32(s)).astype(np.float16)
     sc = 0.5 if w["seed"] == 1 else 1.0
     q = f16((units, w["H"], w["Tq"], w["hd"]), sc)
+    if Q_TYPE == "f32":   # the reference's graphs hand the op an F32 Q; the values stay those of the F16 draw
+        q = q.astype(np.float32)
     if w["kv"] == "q8_0":
         k = orc.quantize_q8_0(rng.standard_normal((units, w["Hkv"], w["Lk"], w["hd"])).astype(np.float32))
         v = orc.quantize_q8_0(rng.standard_normal((units, w["Hkv"], w["Lk"], w["hd"])).astype(np.float32))
@@ -342,7 +347,7 @@ def run_reference(args, w, rank, world):
 def config_of(args, w, units):
     return {"workload": args.workload, "layers": w["layers"], f"{w['unit_name']}_per_gpu": units, "heads": w["H"],
             "kv_heads": w["Hkv"], "head_dim": w["hd"], "q_len": w["Tq"], "kv_len": w["Lk"], "kv_type": w["kv"],
-            "q_type": "f16", "sharding": "units across GPUs, no collective", "launch": "python loop" if args.no_graph else "cuda graph of one step",
+            "q_type": Q_TYPE, "sharding": "units across GPUs, no collective", "launch": "python loop" if args.no_graph else "cuda graph of one step",
             "l2": "inputs of one launch exceed L2" if w["kind"] == "prefill" else "L2 flushed between steps"}
 
 
@@ -552,11 +557,14 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the `workloads` object (the other configurations)")
     ap.add_argument("--no-strong", action="store_true", help="skip the scheduler-partitioned fixed batch")
+    ap.add_argument("--q-type", default="f16", choices=["f16", "f32"], help="storage type of Q (K/V follow the workload)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "tile"])
     ap.add_argument("--decode-splits", type=int, default=0, help="force the split count of the split-KV decode kernel (A/B runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch each layer from Python instead of replaying a CUDA graph")
     ap.add_argument("--record-traffic", nargs="+", metavar="CSV", help="rewrite the DRAM traffic table from ncu CSV exports and exit")
     args = ap.parse_args()
+    global Q_TYPE
+    Q_TYPE = args.q_type
     if args.record_traffic:
         record_traffic(args.record_traffic)
         return

@@ -408,6 +408,26 @@ __device__ __forceinline__ void load_q_rows_f32_coalesced(uint8_t* tile, int war
     }
 }
 
+// The same for F16 query rows: a row is HD / 8 16-byte chunks, 256 / HD rows per warp instruction, copied as they are.
+template <int HD>
+__device__ __forceinline__ void load_q_rows_f16_coalesced(uint8_t* tile, int warp, int lane, const uint8_t* my_rowp) {
+    constexpr int C16 = HD / 8, RPI = 32 / C16;
+    const uint32_t plo = (uint32_t)reinterpret_cast<uintptr_t>(my_rowp), phi = (uint32_t)(reinterpret_cast<uintptr_t>(my_rowp) >> 32);
+    const int cc = lane % C16, sub = lane / C16;
+    uint4 v[32 / RPI];
+#pragma unroll
+    for (int k = 0; k < 32 / RPI; k++) {
+        const int src = k * RPI + sub;
+        const uintptr_t p = (uintptr_t)__shfl_sync(0xffffffffu, plo, src) | ((uintptr_t)__shfl_sync(0xffffffffu, phi, src) << 32);
+        v[k] = p ? __ldg(reinterpret_cast<const uint4*>(p) + cc) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int k = 0; k < 32 / RPI; k++) {
+        const int row = warp * 32 + k * RPI + sub;
+        *reinterpret_cast<uint4*>(tile + (cc >> 3) * kPanelBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = v[k];
+    }
+}
+
 // Output rows: each thread parks its scaled row in its warp's staging area (chunks swizzled by the row), then the warp
 // writes whole rows.  `stage` is this warp's 32 * HD floats; a null row pointer skips the row.
 template <int HD>
@@ -544,6 +564,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         const int iq = (q0 + r) / a.gqa, h = hk * a.gqa + (q0 + r) % a.gqa;
         const uint8_t* rowp = a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)h * a.q.nb2 + (int64_t)b * a.q.nb3;
         if (a.q.type == B200_TYPE_F32 && a.q.vec16) load_q_rows_f32_coalesced<HD>(smem_gen, warp, lane, q0 + r < rows_total ? rowp : nullptr);
+        else if (a.q.type == B200_TYPE_F16 && a.q.vec16) load_q_rows_f16_coalesced<HD>(smem_gen, warp, lane, q0 + r < rows_total ? rowp : nullptr);
         else load_q_row<HD>(smem_gen, r, rowp, a.q.type, a.q.vec16 != 0, q0 + r < rows_total);
         fence_proxy_async();
         if (tid == 0) TC5_TRACE(2, 61, 1);
