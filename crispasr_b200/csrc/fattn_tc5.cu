@@ -1347,8 +1347,10 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 const bool more = j + 1 < n_tiles;
                 if (more) {
                     // X[j+1] needs half-block j+2 (slot j%2, its (j+2)/2-th use) and the X columns drained
-                    ok = mbar_wait(bar_r_full + 8 * (j & 1), ((j + 2) >> 1) & 1, s_abort) &&
-                         mbar_wait(bar_x_free, j & 1, s_abort);
+                    TC5_TRACE(1, j, 5);
+                    ok = mbar_wait(bar_r_full + 8 * (j & 1), ((j + 2) >> 1) & 1, s_abort);
+                    TC5_TRACE(1, j, 6);
+                    if (ok) ok = mbar_wait(bar_x_free, j & 1, s_abort);
                     if (!ok) break;
                     TC5_TRACE(1, j, 0);
                     tc_fence_after();
@@ -1451,15 +1453,17 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
 #pragma unroll
                 for (int k = 0; k < 3; k++) tmem_ld32(tmem_X + lane_base + ((x_col0 + k * 32 + xswap) & 255u), xa[k]);
                 tmem_wait_ld();
+                // the X columns are free the moment every warp holds its 96 values in registers: X[j+1] is computed
+                // under the rest of this tile instead of after the extraction
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_x_free);
                 bounce_chunk(xa[0], 0);
                 bounce_chunk(xa[1], 1);
                 read_quarter(0);
                 bounce_chunk(xa[2], 2);
                 read_quarter(1);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_x_free);
             if (tid == 0) TC5_TRACE(0, j, 1);
             uint4 mv[8];
             if (HASMASK) load_mask64(mv, mrow + (int64_t)(j * kTile + ch * 64) * 2, a.Lk - (j * kTile + ch * 64));   // in flight during the wait for S
