@@ -1347,10 +1347,8 @@ fattn_prefill_tc5_relpos_kernel(const FattnArgs a, const __grid_constant__ CUten
                 const bool more = j + 1 < n_tiles;
                 if (more) {
                     // X[j+1] needs half-block j+2 (slot j%2, its (j+2)/2-th use) and the X columns drained
-                    TC5_TRACE(1, j, 5);
-                    ok = mbar_wait(bar_r_full + 8 * (j & 1), ((j + 2) >> 1) & 1, s_abort);
-                    TC5_TRACE(1, j, 6);
-                    if (ok) ok = mbar_wait(bar_x_free, j & 1, s_abort);
+                    ok = mbar_wait(bar_r_full + 8 * (j & 1), ((j + 2) >> 1) & 1, s_abort) &&
+                         mbar_wait(bar_x_free, j & 1, s_abort);
                     if (!ok) break;
                     TC5_TRACE(1, j, 0);
                     tc_fence_after();
