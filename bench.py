@@ -241,7 +241,12 @@ def algorithmic_work(w, units):
         flops = 4.0 * w["Tq"] * w["Lk"] * w["hd"] * w["H"] * units
         if w.get("causal"):
             flops = 2.0 * w["Tq"] * (w["Lk"] + 1) * w["hd"] * w["H"] * units   # lower triangle only
-        return dict(bound="tensor", amount=flops, unit="TFLOP/s", div=1e12)
+        # the bytes the launch has to move at least: Q once, K/V once, the F32 output once (bias operands of the
+        # rel-pos form not counted); a short causal prefill over a quantised cache is bound by these, not by the FLOPs
+        kv_row = w["hd"] * 2 if w["kv"] == "f16" else w["hd"] // 32 * 34
+        q_bytes = 4 if Q_TYPE == "f32" else 2
+        nbytes = units * (w["H"] * w["Tq"] * w["hd"] * (q_bytes + 4) + 2.0 * w["Hkv"] * w["Lk"] * kv_row)
+        return dict(bound="tensor", amount=flops, unit="TFLOP/s", div=1e12, bytes=nbytes)
     row = w["hd"] * 2 if w["kv"] == "f16" else w["hd"] // 32 * 34
     rows = w["Tq"] * w["beam_cells"] if "beam_cells" in w else w["Lk"]    # valid cells only
     if "pool" in w:
@@ -492,10 +497,16 @@ def launch_floor_us(b200, torch, n_launches=30):
 def roofline_of(abi, w, name, units, dw, step_ms, pk, traffic):
     work = algorithmic_work(w, units)
     launch_s = statistics.fmean(step_ms) * 1e-3 / w["layers"]
+    floors = None
+    if "bytes" in work:   # a contraction: the bound is whichever of the two floors is the longer one for this shape
+        floors = {"tensor": work["amount"] / (pk["tensor"] * 1e12) * 1e6, "hbm": work["bytes"] / (pk["hbm"] * 1e9) * 1e6}
+        if floors["hbm"] > floors["tensor"]:
+            work = dict(bound="hbm", amount=work["bytes"], unit="GB/s", div=1e9)
     achieved = work["amount"] / launch_s / work["div"]
     peak = pk["tensor"] if work["bound"] == "tensor" else pk["hbm"]
     t = traffic.get(name)
     return {"bound": work["bound"], "achieved": achieved, "peak": peak, "unit": work["unit"], "frac": achieved / peak,
+            **({"floors_us": floors} if floors else {}),
             "traffic": (t[0] * units / t[1]) if t else None,
             "traffic_source": "ncu capture of one launch, scaled by units" if t else None,
             "peak_source": f"{pk['src']} ({'sustained bf16 GEMM' if work['bound'] == 'tensor' else 'copy'})",
