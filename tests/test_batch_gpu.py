@@ -97,6 +97,43 @@ def test_index_lists_equal_the_dense_mask_form(b200, orc, kv, case):
             b200.lib().b200_set_decode_splits(0)
 
 
+def test_shared_lists_over_a_batch_of_segments(b200, orc):
+    """Three segments in one launch, each with its own pool state: one shared list + compact mask per segment
+    (list stride 200: not a multiple of the 64-key tile), lengths 0 (a segment whose beams see nothing yet), 37 and
+    200 (a full list), every forced split count.  The oracle sees each segment's dense pool and the reference's mask."""
+    rng = np.random.default_rng(12)
+    S, H, hd, n_beams, n_cells, stride = 3, 4, 64, 5, 512, 200
+    q = (rng.standard_normal((S, H, n_beams, hd)) * 0.5).astype(np.float16)
+    k = (rng.standard_normal((S, H, n_cells, hd)) * 0.5).astype(np.float16)
+    v = (rng.standard_normal((S, H, n_cells, hd)) * 0.5).astype(np.float16)
+    uidx, ulen = np.zeros((S, stride), np.int32), np.zeros(S, np.int32)
+    umask = np.zeros((S, 1, n_beams, stride), np.uint16)
+    dense = np.full((S, 1, n_beams, n_cells), -np.inf, np.float16)
+    pools = [(0, [0, 0, 0, 0, 0]), (12, [9, 3, 1, 7, 5]), (100, [20, 20, 20, 20, 20])]
+    for s, (prefix, suffix) in enumerate(pools):
+        cell_pos, bits, tok_seq, tok_pos = _beam_pool(rng, n_cells, n_beams, prefix, suffix, scatter=True)
+        if s == 0:
+            tok_pos[:] = -1     # nothing is at or before position -1: no beam sees any cell
+        one = np.zeros(1, np.int32)
+        rc = b200.lib().b200_beam_cells_to_union(cell_pos.ctypes.data, bits.ctypes.data, n_cells, tok_seq.ctypes.data,
+                                                 tok_pos.ctypes.data, n_beams, uidx[s].ctypes.data, stride, one.ctypes.data,
+                                                 umask[s, 0].ctypes.data)
+        assert rc == 0
+        ulen[s] = one[0]
+        dense[s, 0] = orc.whisper_beam_mask(cell_pos, bits, tok_seq, tok_pos)
+    assert ulen.tolist() == [0, 37, 200]
+    ref = orc.flash_attn_ext(q, k, v, dense, scale=1.0)
+    for ns in (0, 1, 2, 3):
+        assert b200.lib().b200_set_decode_splits(ns) == 0
+        try:
+            got = gpu_op(b200, q, k, v, umask.view(np.float16), kv_index=uidx, kv_len=ulen, scale=1.0)
+        finally:
+            b200.lib().b200_set_decode_splits(0)
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+        assert_close(got, ref, f"shared lists, {ns} splits")
+        assert not got[0].any()
+
+
 def test_index_lists_are_refused_where_no_kernel_has_them(b200):
     q = torch.zeros((2, 4, 300, 64), dtype=torch.float16, device="cuda")
     k = torch.zeros((1, 4, 512, 64), dtype=torch.float16, device="cuda")
