@@ -70,6 +70,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test.  The answer takes about 120 clocks to come back even when the phase completed long ago, so a
+// wait whose barrier is normally complete is probed early (the result is consumed after other work) and only falls
+// back to the polling wait when the probe said no.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
@@ -1054,6 +1068,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             uint32_t preg[2][32];
             float lsum = 0.0f;
             bool pv_waited = false;
+            uint32_t pv_probe = 0;   // early answer to "has P.V of the previous tile completed" (it normally has by mid-tile)
             for (int attempt = 0; attempt < 2; attempt++) {
                 // P = exp2(S*c - m_ref), rounded to f16x2; the tile maximum is tracked in the same pass and
                 // only checked afterwards (lazy rescale).
@@ -1065,6 +1080,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     uint32_t sreg[2][32];
                     tmem_ld32(tmem_S + lane_base + hh * 64, sreg[0]);
                     tmem_ld32(tmem_S + lane_base + hh * 64 + 32, sreg[1]);
+                    if (SEP_P && hh == 1 && j > 0 && !pv_waited && !pv_probe) pv_probe = mbar_test(bar_pv_done, (j - 1) & 1);
                     tmem_wait_ld();
                     if (tid == 0) TC5_TRACE(0, j, 3 + 2 * hh);
                     if (HASMASK) apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
@@ -1102,7 +1118,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             if (!ok) break;
             l_run += lsum;
             if (SEP_P && j > 0 && !pv_waited) {  // P[j-1] must have been consumed before P[j] overwrites it
-                ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
+                if (!pv_probe) ok = mbar_wait(bar_pv_done, (j - 1) & 1, s_abort);
                 if (!ok) break;
                 tc_fence_after();
             }
