@@ -138,9 +138,9 @@ def record_traffic(paths):
         f.write("# DRAM traffic per launch of each workload's dominant kernel\n\n"
                 "`dram__bytes_read.sum` and `dram__bytes_write.sum` of ONE launch, from ncu captures of the command\n\n"
                 "    ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --print-units base --clock-control none \\\n"
-                "        -k regex:<kernel> -s <launches before it> -c 1 --csv --log-file gpurun_out/traffic_<workload>_u<units>.csv \\\n"
+                "        -k regex:<kernel> -s <launches before it> -c 1 --csv --log-file <dir>/traffic_<workload>_u<units>.csv \\\n"
                 "        python bench.py --workload <workload> --units <units> --steps 1 --warmup 1 --no-cpu-baseline --no-e2e --no-graph --no-extra\n\n"
-                "written by `python bench.py --record-traffic gpurun_out/traffic_*.csv`.  `bench.py` scales a row to the units of\n"
+                "written by `python bench.py --record-traffic <dir>/traffic_*.csv`.  `bench.py` scales a row to the units of\n"
                 "its own launch (every unit reads its own operands once and writes its own output: traffic grows in proportion).\n\n"
                 "| workload | units in the captured launch | kernel | bytes read | bytes written | capture |\n|---|---|---|---|---|---|\n")
         for name in sorted(old):
