@@ -19,6 +19,8 @@
 
 namespace b200 {
 
+int decode_ctas_per_sm(const FattnArgs& a);   // resident CTAs of the split kernel per SM for these operands (defined below)
+
 __device__ int g_mma_status = 0;  // 0 ok, 1 = a bounded wait of a kernel in this file ran out
 
 namespace {
@@ -1788,8 +1790,10 @@ cudaError_t launch_merge(const FattnArgs& a, cudaStream_t st) {
 
 // The splits of one (batch entry, kv-head) of the Q8_0 register kernel run as one thread-block cluster when there
 // are at most 8 of them (the portable cluster size): they merge through distributed shared memory and the merge
-// kernel is not launched.  (Measured on the F16 kernel, whose CTAs hold 100 KB of shared memory, the cluster form
-// was 3-6 % slower than workspace + merge kernel, so that kernel keeps the latter.)
+// kernel is not launched.  The F16 kernel takes the same form: one to eight segments per launch measured 4-14 %
+// faster for cross-attention (1500 keys) and +9 % / +4 % at four / eight segments of the pooled self-attention
+// (2304 cells); where twelve workspace splits beat eight cluster splits (one segment of the latter) the cost model
+// below keeps the merge kernel.
 // B200_DECODE_CLUSTER_MERGE=0 keeps the workspace + merge-kernel form everywhere.
 bool cluster_merge_enabled() {
     static const bool enabled = [] {
@@ -1800,9 +1804,10 @@ bool cluster_merge_enabled() {
 }
 
 bool use_cluster_merge(const FattnArgs& a) {
-    // only while the whole grid is resident at once (4 CTAs on each of 148 SMs): with several waves the cluster
+    // only while the whole grid is resident at once (2 to 4 CTAs on each of 148 SMs): with several waves the cluster
     // barriers hold finished CTAs on their SMs and the form measured 10 % slower than the merge kernel
-    return decode_cluster_merge_ok(a) && a.n_splits > 1 && a.n_splits <= 8 && (long)a.n_splits * a.Hkv * a.B <= 4L * 148;
+    return decode_cluster_merge_ok(a) && a.n_splits > 1 && a.n_splits <= 8 &&
+           (long)a.n_splits * a.Hkv * a.B <= (long)decode_ctas_per_sm(a) * 148;
 }
 
 template <typename Kern>
@@ -2096,12 +2101,12 @@ int launch_bounded_wait_probe(int polls, cudaStream_t st) {
 }
 
 bool decode_cluster_merge_ok(const FattnArgs& a) {
-    return cluster_merge_enabled() && a.k.type == B200_TYPE_Q8_0 && (a.hd == 64 || a.hd == 128);
+    return cluster_merge_enabled() && (a.k.type == B200_TYPE_Q8_0 || a.k.type == B200_TYPE_F16) && (a.hd == 64 || a.hd == 128);
 }
 
 // CTAs of the split kernel that fit on one SM for these operands (shared memory of the staging form; registers
 // allow four).
-static int decode_ctas_per_sm(const FattnArgs& a) {
+int decode_ctas_per_sm(const FattnArgs& a) {
     const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
     size_t smem;
     switch (decode_mode(a, hdp)) {
@@ -2148,9 +2153,15 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
         if ((tiles + tps - 1) / tps != n) continue;   // some split would get no tile
         const double w = units * n / cap;
         const double waves = w <= 4.0 ? ceil(w) : w + 0.5;
-        const bool cluster = cluster_ok && n > 1 && n <= 8 && units * n <= 4.0 * 148;
+        const bool cluster = cluster_ok && n > 1 && n <= 8 && units * n <= cap;
         double cost = waves * (tps + 1.5 + (n == 1 ? 0.0 : (cluster ? 0.5 : 1.0)));
-        if (n > 1) cost += cluster ? 0.1 * n : 1.5 + 0.2 * n;   // the merge reads n partials per output row
+        // the merge reads n partials per output row.  F16 kernel (100 KB CTAs, merge kernel launched under its tail):
+        // merge kernel 0.8 + 0.2 n, cluster 1.0 + 0.1 n, fitted to one segment of Whisper cross-attention (24 tiles:
+        // 8 cluster splits 4.93 k segment-steps/s, 12 workspace splits 4.66 k) and of the pooled self-attention (36
+        // tiles: 12 workspace splits 3.87 k, 18: 3.61 k, 8 cluster splits 3.54 k) and to 2 / 4 / 8 segments (cluster
+        // +13 % / +14 % / +4 % and 0 % / +9 % / +4 %)
+        const bool f16 = a.k.type == B200_TYPE_F16;
+        if (n > 1) cost += cluster ? (f16 ? 1.0 : 0.0) + 0.1 * n : (f16 ? 0.8 : 1.5) + 0.2 * n;
         if (n == 1 || cost < best_cost - 1e-9) best = n, best_cost = cost;
     }
     return best;

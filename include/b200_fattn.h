@@ -180,7 +180,7 @@ B200_API int b200_fattn_plan(const b200_tensor* q, const b200_tensor* k, const b
  * copies of K/V/R that the conversion pre-pass of the tensor-core prefill writes).
  * Mirrors ggml's per-op work buffer sizing (the reference sizes it inside
  * ggml_backend_sched_alloc_graph, src/voxtral.cpp:1196-1198). May return 0 bytes: one split,
- * or splits that merge inside thread-block clusters (small Q8_0 decode batches).
+ * or splits that merge inside thread-block clusters (small decode batches: at most eight splits of a resident grid).
  */
 B200_API int b200_fattn_workspace_bytes(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
                                         const b200_tensor* mask, const b200_tensor* dst,

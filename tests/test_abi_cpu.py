@@ -102,20 +102,27 @@ def test_plan_choices(b200):
     enc_k = _desc((1, 20, 1500, 64))
     kern, ns = b200.plan(enc_q, enc_k, enc_k, scale=0.125)
     assert kern in (abi.KERNEL_PREFILL_TC5, abi.KERNEL_TILE_MMA) and ns == 1
-    # whisper cross-attention decode: 5 beams share the cache -> split-KV with a workspace
+    # whisper cross-attention decode: 5 beams share the cache -> split-KV; up to eight splits of a resident grid merge
+    # inside thread-block clusters (no workspace), more splits go through the workspace and the merge kernel
     dq = _desc((1, 20, 5, 64), torch.float32)
     kern, ns = b200.plan(dq, enc_k, enc_k, scale=0.35)
-    assert kern == abi.KERNEL_DECODE_SPLIT and 1 < ns <= 24
-    assert b200.workspace_bytes(dq, enc_k, enc_k, scale=0.35) >= 20 * ns * 16 * 64 * 4
+    assert kern == abi.KERNEL_DECODE_SPLIT and 1 < ns <= 8
+    assert b200.workspace_bytes(dq, enc_k, enc_k, scale=0.35) == 0
+    assert b200.lib().b200_set_decode_splits(12) == 0
+    try:
+        assert b200.plan(dq, enc_k, enc_k, scale=0.35) == (abi.KERNEL_DECODE_SPLIT, 12)
+        assert b200.workspace_bytes(dq, enc_k, enc_k, scale=0.35) >= 20 * 12 * 16 * 64 * 4
+    finally:
+        b200.lib().b200_set_decode_splits(0)
     # LLM decode, GQA 4, Q8_0
     kq = torch.zeros((8, 8, 663, 136), dtype=torch.uint8)
     kern, ns = b200.plan(_desc((8, 32, 1, 128), torch.float32), kq, kq, scale=0.088, kv_type=abi.Q8_0)
     assert kern == abi.KERNEL_DECODE_SPLIT and 1 < ns <= 8
     # ... whose few splits merge inside thread-block clusters: no workspace is asked for
     assert b200.workspace_bytes(_desc((8, 32, 1, 128), torch.float32), kq, kq, scale=0.088, kv_type=abi.Q8_0) == 0
-    # the same streams over an F16 cache merge through the workspace
+    # the same streams over an F16 cache: the same form
     kf = _desc((8, 8, 663, 128))
-    assert b200.workspace_bytes(_desc((8, 32, 1, 128), torch.float32), kf, kf, scale=0.088) > 0
+    assert b200.workspace_bytes(_desc((8, 32, 1, 128), torch.float32), kf, kf, scale=0.088) == 0
     # explicit per-head mask or relpos -> general tile kernel unless the tcgen05 kernel takes it
     r = _desc((1, 20, 2999, 64))
     kern, _ = b200.plan(enc_q, enc_k, enc_k, scale=0.125, q_v=enc_q, r=r)

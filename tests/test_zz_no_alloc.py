@@ -65,12 +65,21 @@ def _plan(L, q, k, v, kv_type, scale):
 
 
 def test_static_scratch_matches_workspace_launch_twice(b200, orc):
-    """Three calls in a row on the shared array, every one a form whose splits really travel through it (an F16
-    cache: partials go to the scratch and a merge kernel reads them back; the small Q8_0 batches that merge inside
-    thread-block clusters would never touch it).  Call 1 leaves the largest footprint, so calls 2 and 3 find stale
-    bytes both inside and beyond the range they use; call 3 repeats call 1's geometry with other data."""
+    """Three calls in a row on the shared array, every one a form whose splits really travel through it: more than
+    eight splits per (stream, kv-head), so the partials go to the scratch and a merge kernel reads them back (up to
+    eight splits of a resident grid would merge inside thread-block clusters and never touch it).  Call 1 leaves the
+    largest footprint, so calls 2 and 3 find stale bytes both inside and beyond the range they use; call 3 repeats
+    call 1's geometry with other data."""
     L = b200.lib()
     assert L.b200_fattn_static_scratch_bytes() == 8 << 20
+    assert L.b200_set_decode_splits(12) == 0
+    try:
+        _static_scratch_three_calls(L, orc)
+    finally:
+        assert L.b200_set_decode_splits(0) == 0
+
+
+def _static_scratch_three_calls(L, orc):
     rng = np.random.default_rng(77)
     S, H, Hkv, hd, Lk = 8, 32, 8, 128, 663
     lens = torch.tensor([663, 408, 500, 64, 1, 650, 129, 333], dtype=torch.int32, device="cuda")
