@@ -312,6 +312,32 @@ __device__ __forceinline__ void softmax64(const uint32_t (&sreg)[2][32], uint32_
     lsum_io += l0 + l1;
 }
 
+// One 32-column chunk of the same arithmetic with the accumulators kept by the caller (mx[8], ls[4] live across the
+// four chunks of a tile): lets the TMEM load of a later chunk run under the exponentials of an earlier one.
+template <bool MASKED>
+__device__ __forceinline__ void softmax32(const uint32_t (&sreg)[32], uint32_t* preg16, uint64_t c2, uint64_t nm2, int col0, int n_valid,
+                                          float (&mx)[8], uint64_t (&ls)[4]) {
+    if (MASKED && col0 >= n_valid) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) preg16[i] = 0u;
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float s0 = __uint_as_float(sreg[i]), s1 = __uint_as_float(sreg[i + 1]);
+        if (MASKED) {
+            if (col0 + i >= n_valid) s0 = -INFINITY;
+            if (col0 + i + 1 >= n_valid) s1 = -INFINITY;
+        }
+        mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], s0, s1);
+        float t0, t1;
+        unpack2(fma2(pack2(s0, s1), c2, nm2), t0, t1);
+        const float p0 = ex2(t0), p1 = ex2(t1);
+        ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+        preg16[i >> 1] = cvt_f16x2(p0, p1);
+    }
+}
+
 // 64 consecutive F16 mask values starting at `mptr` as eight 16-byte loads, all in flight at once (2-byte loads
 // where the address is not 16-byte aligned); values at or beyond `avail` (the end of the mask row) read as 0 and
 // are never touched in memory.
@@ -1075,6 +1101,47 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
                 float mx = -INFINITY;
                 lsum = 0.0f;
+                if constexpr (!HASMASK) {
+                    // rolling 32-column chunks: the load of chunk k+2 is issued into the registers chunk k has just
+                    // left and completes under the exponentials of chunk k+1
+                    float mx8[8];
+                    uint64_t ls4[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+                    for (int i = 0; i < 8; i++) mx8[i] = -INFINITY;
+                    const uint64_t c2 = pack2(c_exp, c_exp), nm2 = pack2(-m_use, -m_use);
+                    uint32_t sA[32], sB[32];
+                    // a partial tile (the last one, or the diagonal of a causal call) puts -inf into the dead columns
+                    // first and skips chunks that are dead for the whole warp: one copy of the arithmetic serves both
+                    auto chunk = [&](uint32_t (&sx)[32], uint32_t* p16, int col0) {
+                        if (!full_tile) {
+                            if (__all_sync(0xffffffffu, col0 >= n_valid)) {
+#pragma unroll
+                                for (int i = 0; i < 16; i++) p16[i] = 0u;
+                                return;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                if (col0 + i >= n_valid) sx[i] = 0xFF800000u;
+                        }
+                        softmax32<false>(sx, p16, c2, nm2, 0, 0, mx8, ls4);
+                    };
+                    tmem_ld32(tmem_S + lane_base, sA);
+                    tmem_ld32(tmem_S + lane_base + 32, sB);
+                    tmem_wait_ld();
+                    chunk(sA, preg[0], 0);
+                    tmem_ld32(tmem_S + lane_base + 64, sA);
+                    if (SEP_P && j > 0 && !pv_waited && !pv_probe) pv_probe = mbar_test(bar_pv_done, (j - 1) & 1);
+                    chunk(sB, preg[0] + 16, 32);
+                    tmem_wait_ld();
+                    tmem_ld32(tmem_S + lane_base + 96, sB);
+                    chunk(sA, preg[1], 64);
+                    tmem_wait_ld();
+                    chunk(sB, preg[1] + 16, 96);
+                    mx = max3(max3(fmaxf(mx8[0], mx8[1]), mx8[2], mx8[3]), max3(fmaxf(mx8[4], mx8[5]), mx8[6], mx8[7]), mx);
+                    float l0, l1;
+                    unpack2(add2(add2(ls4[0], ls4[1]), add2(ls4[2], ls4[3])), l0, l1);
+                    lsum = l0 + l1;
+                } else
 #pragma unroll
                 for (int hh = 0; hh < 2; hh++) {
                     uint32_t sreg[2][32];
