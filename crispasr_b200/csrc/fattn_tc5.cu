@@ -378,6 +378,39 @@ __device__ __forceinline__ void apply_mask64(uint32_t (&sreg)[2][32], const uint
     }
 }
 
+// Explicit mask, fused form: 64 raw scores and their 64 mask values -> probabilities in one pass,
+// x = s*c + (mask*log2(e) - m) with two packed FMAs per pair (folding the mask into the scores first and subtracting the
+// maximum afterwards costs four scalar operations more per pair, and this path is bound by instruction issue).  The
+// running maximum is tracked on x; the caller adds m back.  Columns >= n_valid (tile-relative) are dead.
+template <bool MASKED>
+__device__ __forceinline__ void softmax64_masked(const uint32_t (&sreg)[2][32], const uint4 (&mv)[8], uint32_t (&preg)[32], float c,
+                                                 float m_use, int col0, int n_valid, float& mx_io, float& lsum_io) {
+    float mx[8];
+    uint64_t ls[4] = {0ull, 0ull, 0ull, 0ull};
+    const uint64_t c2 = pack2(c, c), l2e2 = pack2(kLog2e, kLog2e), nm2 = pack2(-m_use, -m_use);
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx[i] = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 64; i += 2) {
+        const float2 m2 = mask_pair(mv, i);
+        float x0, x1;
+        unpack2(fma2(pack2(__uint_as_float(sreg[i >> 5][i & 31]), __uint_as_float(sreg[i >> 5][(i + 1) & 31])), c2,
+                     fma2(pack2(m2.x, m2.y), l2e2, nm2)), x0, x1);
+        if (MASKED) {
+            if (col0 + i >= n_valid) x0 = -INFINITY;
+            if (col0 + i + 1 >= n_valid) x1 = -INFINITY;
+        }
+        mx[(i >> 1) & 7] = max3(mx[(i >> 1) & 7], x0, x1);
+        const float p0 = ex2(x0), p1 = ex2(x1);
+        ls[(i >> 1) & 3] = add2(ls[(i >> 1) & 3], pack2(p0, p1));
+        preg[i >> 1] = cvt_f16x2(p0, p1);
+    }
+    mx_io = max3(mx_io, max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]), max3(fmaxf(mx[4], mx[5]), mx[6], mx[7]));
+    float l0, l1;
+    unpack2(add2(add2(ls[0], ls[1]), add2(ls[2], ls[3])), l0, l1);
+    lsum_io += l0 + l1;
+}
+
 // One query row (HD elements) -> f16, written into the 128-byte swizzled operand tile: row r, 16-byte chunk c of
 // panel p at p*16384 + r*128 + ((c ^ (r & 7)) * 16).  The type is tested once and all loads of the row are issued
 // before the first store, so the row costs one memory round trip instead of HD/8.
@@ -1150,13 +1183,19 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                     if (SEP_P && hh == 1 && j > 0 && !pv_waited && !pv_probe) pv_probe = mbar_test(bar_pv_done, (j - 1) & 1);
                     tmem_wait_ld();
                     if (tid == 0) TC5_TRACE(0, j, 3 + 2 * hh);
-                    if (HASMASK) apply_mask64(sreg, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64), c);
-                    if (full_tile) softmax64<false>(sreg, preg[hh], c_exp, m_use, 0, 0, mx, lsum);
-                    else softmax64<true>(sreg, preg[hh], c_exp, m_use, hh * 64, n_valid, mx, lsum);
+                    if constexpr (HASMASK) {
+                        uint4 mv[8];
+                        load_mask64(mv, mrow + (int64_t)(j * kTile + hh * 64) * 2, a.Lk - (j * kTile + hh * 64));
+                        if (full_tile) softmax64_masked<false>(sreg, mv, preg[hh], c, m_use, 0, 0, mx, lsum);
+                        else softmax64_masked<true>(sreg, mv, preg[hh], c, m_use, hh * 64, n_valid, mx, lsum);
+                    } else {
+                        if (full_tile) softmax64<false>(sreg, preg[hh], c_exp, m_use, 0, 0, mx, lsum);
+                        else softmax64<true>(sreg, preg[hh], c_exp, m_use, hh * 64, n_valid, mx, lsum);
+                    }
                     if (tid == 0) TC5_TRACE(0, j, 4 + 2 * hh);
                 }
                 if (tid == 0 && attempt == 1) TC5_TRACE(0, j, 7);
-                const float m_tile = mx * c_exp;
+                const float m_tile = HASMASK ? mx + m_use : mx * c_exp;   // (the masked form tracks the maximum of x = logit - m)
                 const bool grow = m_tile > m_ref + kRescaleThreshold;
                 if (!__any_sync(0xffffffffu, grow)) break;
                 // some row of this warp outgrew its reference maximum: rescale O and l, then redo P
