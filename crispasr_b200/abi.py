@@ -80,6 +80,8 @@ TP = C.POINTER(Tensor)
 
 # name -> (restype, argtypes); every symbol include/b200_fattn.h declares.
 _OP_ARGS = [TP, TP, TP, TP, TP, C.POINTER(Params), C.POINTER(Ext)]
+MASK_GENERAL, MASK_NONE, MASK_CAUSAL, MASK_TAIL = 0, 1, 2, 3
+
 SYMBOLS = {
     "b200_set_kernel_override": (C.c_int, [C.c_int]),
     "b200_set_decode_splits": (C.c_int, [C.c_int]),
@@ -108,6 +110,7 @@ SYMBOLS = {
     "b200_kv_append": (C.c_int, [C.c_void_p, C.c_int, TP, TP, C.c_void_p, C.c_int32, C.c_void_p]),
     "b200_kv_copy_stream": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "b200_beam_cells_to_index": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "b200_mask_classify": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200_beam_cells_to_union": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "b200_relpos_table": (C.c_int, [TP, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_relpos_cache_create": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_void_p)]),

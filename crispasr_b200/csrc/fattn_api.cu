@@ -605,6 +605,38 @@ B200_API int b200_beam_cells_to_union(const int32_t* cell_pos, const uint32_t* c
     return B200_OK;
 }
 
+B200_API int b200_mask_classify(const uint16_t* mask, int Lk, int Tq, int64_t row_stride, int* kind, int* n_past,
+                                int* kv_len) {
+    if (!mask || !kind) return B200_E_NULL;
+    if (Lk <= 0 || Tq <= 0 || row_stride < Lk) return B200_E_SHAPE;
+    *kind = B200_MASK_GENERAL;
+    // per row: the number of leading zeros (0x0000 / 0x8000) followed by -inf (0xFC00) to the end, or -1
+    int first = -1;
+    bool same = true, step = true;
+    for (int i = 0; i < Tq; i++) {
+        const uint16_t* row = mask + (int64_t)i * row_stride;
+        int z = 0;
+        while (z < Lk && (row[z] & 0x7FFFu) == 0) z++;
+        for (int j = z; j < Lk; j++)
+            if (row[j] != 0xFC00u) return B200_OK;   // a finite bias, or a hole: general
+        if (i == 0) first = z;
+        if (z != first) same = false;
+        // causal with n_past = first - 1: row i shows min(Lk, first + i) keys
+        if (z != (first + i < Lk ? first + i : Lk)) step = false;
+    }
+    if (same) {
+        if (first == Lk) *kind = B200_MASK_NONE;
+        else {
+            *kind = B200_MASK_TAIL;
+            if (kv_len) *kv_len = first;
+        }
+    } else if (step && first >= 1) {
+        *kind = B200_MASK_CAUSAL;
+        if (n_past) *n_past = first - 1;
+    }
+    return B200_OK;
+}
+
 B200_API int b200_fattn_supports(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
                                  const b200_tensor* mask, const b200_tensor* dst, const b200_fattn_params* params,
                                  const b200_fattn_ext* ext, int* why) {

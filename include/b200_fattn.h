@@ -348,6 +348,26 @@ B200_API int b200_beam_cells_to_union(const int32_t* cell_pos, const uint32_t* c
                                       const int32_t* tok_seq, const int32_t* tok_pos, int n_tokens,
                                       int32_t* index_out, int stride, int32_t* len_out, uint16_t* mask_out);
 
+/*
+ * b200_mask_classify — host helper for adapters whose runtime fills its F16 mask on the host before uploading it
+ * (the causal prefill mask of src/voxtral.cpp:1187-1194, the bucket padding mask of src/canary_ctc.cpp:370-382): says
+ * whether the mask [Lk, Tq] (row_stride elements between query rows) is one of the shapes the operator takes as a
+ * parameter instead of as a tensor.  An explicit mask costs the kernels a load, a conversion and a fold per score;
+ * the parameters cost nothing per element and skip dead tiles.
+ *   B200_MASK_GENERAL  pass the mask as it is (any value other than 0 / -0 / -inf, or any other pattern)
+ *   B200_MASK_NONE     every entry is 0: pass no mask
+ *   B200_MASK_CAUSAL   entry (query i, key j) is 0 for j <= n_past + i and -inf beyond: pass ext.causal = 1 and
+ *                      ext.n_past = *n_past (no mask)
+ *   B200_MASK_TAIL     keys >= *kv_len are -inf for every query row, the rest 0: pass ext.kv_len (no mask)
+ * Returns B200_OK or an argument error.
+ */
+#define B200_MASK_GENERAL 0
+#define B200_MASK_NONE 1
+#define B200_MASK_CAUSAL 2
+#define B200_MASK_TAIL 3
+B200_API int b200_mask_classify(const uint16_t* mask, int Lk, int Tq, int64_t row_stride, int* kind, int* n_past,
+                                int* kv_len);
+
 /* ------------------------------------------------------------------------------------------
  * Relative-position table of the FastConformer attention block.  Replaces make_pos_enc
  * (src/core/fastconformer.h:118-130), its upload, and R = MUL_MAT(attn_pos_w, pos_enc) with the

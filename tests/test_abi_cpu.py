@@ -322,6 +322,49 @@ def test_beam_cells_to_index_is_the_complement_of_the_mask_rule(b200, orc):
                                       n_tok, idx.ctypes.data, 8, lens.ctypes.data) == abi.E_LIMIT
 
 
+def test_mask_classify_recognises_the_masks_the_runtimes_build_on_the_host(b200, orc):
+    """The causal prefill mask of src/voxtral.cpp:1187-1194 and a tail padding mask map to ext.causal / ext.kv_len;
+    anything else stays an explicit mask."""
+    L = b200.lib()
+
+    def classify(m):
+        m = np.ascontiguousarray(m, np.float16)
+        kind, n_past, kv_len = np.zeros(1, np.int32), np.full(1, -7, np.int32), np.full(1, -7, np.int32)
+        rc = L.b200_mask_classify(m.ctypes.data, m.shape[1], m.shape[0], m.strides[0] // 2, kind.ctypes.data, n_past.ctypes.data,
+                                  kv_len.ctypes.data)
+        assert rc == 0
+        return int(kind[0]), int(n_past[0]), int(kv_len[0])
+
+    for n_past, T in ((0, 7), (5, 3), (407, 1), (0, 300)):
+        m = orc.causal_mask(n_past + T, T, n_past)            # (T, Lk), the reference's fill
+        kind, got_past, _ = classify(m)
+        if T == 1:
+            assert kind == abi.MASK_NONE                      # a single row that sees every key
+        else:
+            assert (kind, got_past) == (abi.MASK_CAUSAL, n_past)
+    assert classify(np.zeros((4, 64)))[0] == abi.MASK_NONE
+    pad = np.zeros((6, 96), np.float16)
+    pad[:, 70:] = -np.inf
+    assert classify(pad) == (abi.MASK_TAIL, -7, 70)
+    assert classify(-np.zeros((2, 8)))[0] == abi.MASK_NONE    # -0.0
+    holes = pad.copy()
+    holes[2, 10] = -np.inf
+    assert classify(holes)[0] == abi.MASK_GENERAL
+    bias = np.zeros((3, 16), np.float16)
+    bias[1, 4] = -0.5
+    assert classify(bias)[0] == abi.MASK_GENERAL
+    shifted = orc.causal_mask(12, 4, 8).copy()
+    shifted[3, :] = shifted[2, :]                             # not a step of one key per row
+    assert classify(shifted)[0] == abi.MASK_GENERAL
+    wide = np.zeros((5, 32 + 8), np.float16)[:, :32]          # a view with a row stride
+    wide[:, 20:] = -np.inf
+    m = np.ascontiguousarray(wide)
+    assert classify(m) == (abi.MASK_TAIL, -7, 20)
+    kind = np.zeros(1, np.int32)
+    assert L.b200_mask_classify(None, 4, 4, 4, kind.ctypes.data, None, None) == abi.E_NULL
+    assert L.b200_mask_classify(m.ctypes.data, 32, 5, 16, kind.ctypes.data, None, None) == abi.E_SHAPE
+
+
 def test_beam_cells_to_union_lists_each_visible_cell_once(b200, orc):
     """The shared list holds every cell some token of the step can see, in pool order; the compact mask over the
     list's entries is the reference's mask (src/crispasr.cpp:3480-3488) restricted to those columns."""
