@@ -22,6 +22,12 @@ namespace b200 {
 int decode_ctas_per_sm(const FattnArgs& a);   // resident CTAs of the split kernel per SM for these operands (defined below)
 
 __device__ int g_mma_status = 0;  // 0 ok, 1 = a bounded wait of a kernel in this file ran out
+#ifdef B200_Q8T_TRACE
+__device__ long long g_q8t_trace[16];
+#define Q8T_TRACE(k) do { if (blockIdx.x == 0 && blockIdx.y == 3 && blockIdx.z == B200_Q8T_TRACE && threadIdx.x == 0) g_q8t_trace[k] = clock64(); } while (0)
+#else
+#define Q8T_TRACE(k) do { } while (0)
+#endif
 
 namespace {
 
@@ -1344,6 +1350,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    Q8T_TRACE(0);
     const int bk = b / a.bq;
     const int R = a.Tq * a.gqa;  // <= 8; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
     const float ninf = -INFINITY;
@@ -1351,6 +1358,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     // launched with programmatic stream serialisation: the previous kernel of the stream has completed and flushed
     // before anything is read or written (a no-op under an ordinary launch)
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    Q8T_TRACE(1);
     const int len_b = clamp_len(a, b);
     const int tq_b = q_rows_of(a, b);
     const int kmax = tq_b > 0 ? len_b : 0;
@@ -1360,23 +1368,35 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
     const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
 
-    if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < NS; i++) mbar_init(smem_u32(&s_bar[warp][i]), 1);
+    // A CTA of this kernel shares its SM with three others in their key loops, where a lone thread gets an issue slot
+    // every few tens of clocks: the set-up below is spread over lanes so that its chain of dependent instructions is
+    // short - lane i initialises barrier i, lanes 2s and 2s+1 request the K and the V bytes of stage s.
+    if (lane < NS) {
+        mbar_init(smem_u32(&s_bar[warp][lane]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
-    auto issue = [&](int tile) {
-        if (tile < tile_hi && lane == 0) {
+    // lanes 2s (K) and 2s+1 (V) of a warp copy the raw bytes of the warp's 16 keys of tile `tile0 + s`; lane 2s also
+    // announces both copies to the stage's barrier.  Copies stop at the stream's length (whole 16-byte units).
+    auto issue_lanes = [&](int tile0, int n_stages) {
+        const int s_ = lane >> 1, tile = tile0 + s_;
+        if (s_ < n_stages && tile < tile_hi) {
             const int stage = (tile - tile_lo) % NS;
-            issue_tile_q8raw<HD>(sRaw + stage * 2 * RAW_BYTES, sRaw + stage * 2 * RAW_BYTES + RAW_BYTES, kbase, vbase, tile * kDecBN,
-                                 len_b, warp, smem_u32(&s_bar[warp][stage]));
+            const int r0 = tile * kDecBN + 16 * warp;
+            const int n = min(16, max(0, len_b - r0));
+            const uint32_t bytes = (uint32_t)((n * RB + 15) / 16 * 16);
+            const uint32_t bar = smem_u32(&s_bar[warp][stage]);
+            if ((lane & 1) == 0) mbar_expect_tx(bar, 2 * bytes);
+            if (bytes) {
+                const uint32_t dst = smem_u32(sRaw + stage * 2 * RAW_BYTES + (lane & 1) * RAW_BYTES) + 16 * warp * RB;
+                bulk_g2s(dst, ((lane & 1) ? vbase : kbase) + (int64_t)r0 * RB, bytes, bar);
+            }
         }
     };
-#pragma unroll
-    for (int s0 = 0; s0 < NS; s0++) issue(tile_lo + s0);
-
+    auto issue = [&](int tile) { issue_lanes(tile, 1); };
+    issue_lanes(tile_lo, NS);
+    Q8T_TRACE(2);
     // Q rows (tiny): one 8-element chunk per loop step; rows >= R are zero
     for (int idx = tid; idx < kDecRows * (HD / 8); idx += kThreads) {
         const int rr = idx / (HD / 8), ch = idx % (HD / 8);
@@ -1466,6 +1486,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         if (pair < 8 * NBLK && c4 == 0) s_qd[pair] = -1152.0f * sum;
         __syncthreads();
     }
+    Q8T_TRACE(3);
     float negc[NBLK][2];
 #pragma unroll
     for (int blk = 0; blk < NBLK; blk++)
@@ -1481,10 +1502,13 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     const __half2 bias = __float2half2_rn(1152.0f);
     const float c = a.scale * kLog2e;
 
+    Q8T_TRACE(4);
     for (int tile = tile_lo; tile < tile_hi; tile++) {
         const int k0 = tile * kDecBN;
         const int stage = (tile - tile_lo) % NS;
         if (!mbar_wait_bounded(smem_u32(&s_bar[warp][stage]), (uint32_t)((tile - tile_lo) / NS) & 1u)) break;
+        if (tile == tile_lo) Q8T_TRACE(5);
+        if (tile == tile_lo + 1) Q8T_TRACE(6);
         const uint8_t* rawK = sRaw + stage * 2 * RAW_BYTES + 16 * warp * RB;   // this warp's 16 keys
         const uint8_t* rawV = rawK + RAW_BYTES;
         const int rows_valid = len_b - (k0 + 16 * warp);   // keys at or beyond it hold stale bytes: their scale reads as 0
@@ -1634,9 +1658,9 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         issue(tile + NS);
     }
 
+    Q8T_TRACE(7);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- merge the four warps' (m, l, O) in shared memory (same slabs as the kernel above) ----
-    __syncthreads();  // all warps are done with the raw stages (the merge slabs alias them)
     constexpr int SLAB_STRIDE = HD + 4;
     float* slab = reinterpret_cast<float*>(smem_raw);   // [4][16][SLAB_STRIDE]
     float lq[2];
@@ -1653,59 +1677,62 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         s_l[warp][2 * t] = lq[0], s_l[warp][2 * t + 1] = lq[1];
     }
     if (lane < 8) s_m[warp][8 + lane] = ninf, s_l[warp][8 + lane] = 0.0f;   // rows 8..15 do not exist in this form
-    __syncthreads();
-    float fac[2];
+    __syncthreads();  // the warps' (m, l) are visible, and all warps are done with the raw stages (the merge slabs alias them)
+    Q8T_TRACE(8);
+    // Each warp parks its accumulators as they are (scaled to its OWN running maximum): a thread's accumulators of one
+    // block are four consecutive dims (4g .. 4g+3) of rows 2t and 2t+1, one 16-byte store per (block, row), conflict-free
+    // (quarter-warps cover eight different 16-byte slots of a 128-byte line); rows at or beyond R are never read.
 #pragma unroll
     for (int j = 0; j < 2; j++) {
-        const int rr = 2 * t + j;
-        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
-        fac[j] = (m_run[j] == ninf) ? 0.0f : exp2f(m_run[j] - M);
+        if (2 * t + j >= R) continue;
+#pragma unroll
+        for (int blk = 0; blk < NBLK; blk++)
+            *reinterpret_cast<float4*>(slab + (warp * kDecRows + 2 * t + j) * SLAB_STRIDE + 32 * blk + 4 * g) =
+                make_float4(o[blk][0][j], o[blk][0][2 + j], o[blk][1][j], o[blk][1][2 + j]);
     }
-#pragma unroll
-    for (int blk = 0; blk < NBLK; blk++)
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int j = e & 1, dim = 32 * blk + 4 * g + 2 * mt + (e >> 1);
-                slab[(warp * kDecRows + 2 * t + j) * SLAB_STRIDE + dim] = fac[j] != 0.0f ? o[blk][mt][e] * fac[j] : 0.0f;
-            }
-    if (tid < kDecRows) {
-        const int rr = tid;
-        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
-        float L = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) L += (s_m[w][rr] == ninf) ? 0.0f : s_l[w][rr] * exp2f(s_m[w][rr] - M);
-        s_M[rr] = M, s_L[rr] = L;
-    }
+    Q8T_TRACE(12);
     __syncthreads();
-    auto merged = [&](int rr, int cc) {
-        return (slab[(0 * kDecRows + rr) * SLAB_STRIDE + cc] + slab[(1 * kDecRows + rr) * SLAB_STRIDE + cc]) +
-               (slab[(2 * kDecRows + rr) * SLAB_STRIDE + cc] + slab[(3 * kDecRows + rr) * SLAB_STRIDE + cc]);
-    };
-
-    if (a.n_splits == 1) {
-        for (int idx = tid; idx < R * HD; idx += kThreads) {
-            const int rr = idx / HD, cc = idx % HD;
+    Q8T_TRACE(9);
+    // Write-out: one warp per live row, one 16-byte column group per lane, the log-sum-exp merge of the four warps'
+    // partials on the way.  A CTA of this kernel lives for nine tiles at the usual cache lengths and shares its SM with
+    // three others in their key loops, where every dependent step of a tail like this one waits for an issue slot: the
+    // first form (scale by the common maximum, barrier, per-row sums by sixteen threads, barrier, element-wise write-out
+    // with an index division per element) took a sixth of the CTA's lifetime.
+    for (int rr = warp; rr < R; rr += 4) {
+        const float m0 = s_m[0][rr], m1 = s_m[1][rr], m2 = s_m[2][rr], m3 = s_m[3][rr];
+        const float l0 = s_l[0][rr], l1 = s_l[1][rr], l2 = s_l[2][rr], l3 = s_l[3][rr];
+        const float M = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        const float w0 = m0 == ninf ? 0.0f : fast_ex2(m0 - M), w1 = m1 == ninf ? 0.0f : fast_ex2(m1 - M);
+        const float w2 = m2 == ninf ? 0.0f : fast_ex2(m2 - M), w3 = m3 == ninf ? 0.0f : fast_ex2(m3 - M);
+        const float L = (w0 * l0 + w1 * l1) + (w2 * l2 + w3 * l3);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane < HD / 4) {
+            const float4 x0 = *reinterpret_cast<const float4*>(slab + (0 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
+            const float4 x1 = *reinterpret_cast<const float4*>(slab + (1 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
+            const float4 x2 = *reinterpret_cast<const float4*>(slab + (2 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
+            const float4 x3 = *reinterpret_cast<const float4*>(slab + (3 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
+            // a warp that saw no live key holds zeros and weight 0
+            v.x = (w0 * x0.x + w1 * x1.x) + (w2 * x2.x + w3 * x3.x), v.y = (w0 * x0.y + w1 * x1.y) + (w2 * x2.y + w3 * x3.y);
+            v.z = (w0 * x0.z + w1 * x1.z) + (w2 * x2.z + w3 * x3.z), v.w = (w0 * x0.w + w1 * x1.w) + (w2 * x2.w + w3 * x3.w);
+        }
+        if (a.n_splits == 1) {
             const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
-            const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + cc] = (L > 0.0f && iq < tq_b) ? merged(rr, cc) / L : 0.0f;
-        }
-    } else if (a.cluster_merge) {
-        for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
-            const int rr = idx / HD, cc = idx % HD;
-            slab[rr * SLAB_STRIDE + cc] = merged(rr, cc);
-        }
-        cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
-    } else {
-        const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
-        float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < R * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);
-        if (tid < kDecRows) {
-            a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
-            a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
+            const float inv = (L > 0.0f && iq < tq_b) ? 1.0f / L : 0.0f;
+            if (lane < HD / 4)
+                *reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * HD + 4 * lane) =
+                    make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv);
+        } else if (a.cluster_merge) {
+            // slab 0 <- the CTA's merged partial, in place (a lane rewrites the columns it read; rows belong to one warp)
+            if (lane < HD / 4) *reinterpret_cast<float4*>(slab + rr * SLAB_STRIDE + 4 * lane) = v;
+            if (lane == 0) s_M[rr] = M, s_L[rr] = L;
+        } else {
+            const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
+            if (lane < HD / 4) *reinterpret_cast<float4*>(a.ws_o + unit * kDecRows * HD + rr * HD + 4 * lane) = v;   // live rows only: the merge kernel reads no others
+            if (lane == 0) a.ws_ml[(unit * kDecRows + rr) * 2] = M, a.ws_ml[(unit * kDecRows + rr) * 2 + 1] = L;
         }
     }
+    if (a.n_splits > 1 && a.cluster_merge) cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
+    Q8T_TRACE(10);
 }
 
 // One warp per (batch, kv-head, row): log-sum-exp merge of the split partials.
@@ -2058,6 +2085,12 @@ size_t decode_split_ws_bytes(int B, int Hkv, int n_splits, int hd) {
 }
 
 bool decode_uses_cluster_merge(const FattnArgs& a) { return use_cluster_merge(a); }
+
+#ifdef B200_Q8T_TRACE
+extern "C" __attribute__((visibility("default"))) int b200_dbg_q8t_trace(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_q8t_trace, sizeof(long long) * 16);
+}
+#endif
 
 int mma_read_status(int* status) {
     int v = 0;
