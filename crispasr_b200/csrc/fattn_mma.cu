@@ -19,7 +19,7 @@
 
 namespace b200 {
 
-int decode_ctas_per_sm(const FattnArgs& a);   // resident CTAs of the split kernel per SM for these operands (defined below)
+int decode_ctas_per_sm(const FattnArgs& a, bool cluster = false);   // resident CTAs of the split kernel per SM for these operands, as a cluster launch with its receive area if asked (defined below)
 
 __device__ int g_mma_status = 0;  // 0 ok, 1 = a bounded wait of a kernel in this file ran out
 #ifdef B200_Q8T_TRACE
@@ -570,49 +570,128 @@ __device__ __forceinline__ void dequant_tile_q8(const uint8_t* raw, __half* sm, 
 // memory, the cluster meets at its hardware barrier, and each CTA finishes a slice of the output rows by reading
 // all peers' partials through distributed shared memory.  A second barrier keeps every CTA's shared memory alive
 // until its peers are done reading.
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_peer_f32(const float* p, uint32_t rank) {
+__device__ __forceinline__ uint32_t peer_addr(const void* p, uint32_t rank) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    return remote;
 }
-// `part` is this CTA's merged partial [16][HD + 4]; s_M / s_L its row maxima and sums.
+__device__ __forceinline__ void st_peer_v4(uint32_t remote, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_peer_v2(uint32_t remote, float x, float y) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" :: "r"(remote), "f"(x), "f"(y) : "memory");
+}
+// A split kernel launched as clusters says "this CTA runs" at its start; the write-out waits for that phase before its
+// first store into a peer's shared memory.
+__device__ __forceinline__ void cluster_announce(const FattnArgs& a) {
+    if (a.n_splits > 1 && a.cluster_merge) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+
+// Receive area of the merge inside a cluster: shared memory of its own behind a kernel's stages (a peer may push while
+// this CTA is still in its key loop): [n_splits][slots] 16-byte column groups this CTA owns (rows * hd / 4 of them over the
+// cluster, rounded up per split), then [8][16] (M, L).
+// `rows` = the launch's query rows per KV head (Tq * gqa).
+__host__ __device__ constexpr size_t cluster_push_bytes(int hd, int rows) { return (size_t)(rows * (hd / 4) + 8) * 16 + 8 * kDecRows * 8; }
+
+// Write-out shared by the split-KV decode kernels.  `slab` holds the four warps' partial O [4][16][HD + 4], each scaled
+// to its own warp's running maximum s_m[w][row] with row sum s_l[w][row]; the CTA has passed a barrier since they were
+// written.  One warp per live row, one 16-byte column group per lane, the log-sum-exp merge of the four partials on
+// the way; the result goes
+//   * n_splits == 1: to dst, divided by the row sum;
+//   * workspace form: to this split's [16][HD] partial and (M, L) pairs, for the merge kernel;
+//   * cluster form: the column groups of the R x HD result are dealt round-robin to the CTAs of the cluster; every CTA
+//     stores its partial of a group into the OWNER's receive area (and its (M, L) into everybody's), one cluster
+//     barrier later each owner merges what it received from its own shared memory and writes the rows.  One barrier and
+//     no remote load on the critical path; the first form of this merge (barrier, every CTA pulls 3 n_splits values per
+//     element from its peers, barrier) took 4.0 k of a 13.7 k clk CTA at 8 streams of the Q8_0 cache, this one 2.0 k.
+// A CTA with two or three tiles shares its SM with few others, but at the usual 256-stream size three neighbours are
+// in their key loops and every dependent step of a tail waits for an issue slot, so the chain is kept short: no
+// separate pass for the common maximum, no index division per element.
 template <int HD>
-__device__ __forceinline__ void cluster_merge_store(const FattnArgs& a, const float* part, const float* s_M, const float* s_L,
-                                                    int R, int b, int hk, int split, int tid) {
-    constexpr int STRIDE = HD + 4;
-    cluster_sync_all();
-    const int n = a.n_splits;
-    for (int idx = split * kThreads + tid; idx < R * HD; idx += n * kThreads) {
-        const int rr = idx / HD, c = idx % HD;
-        if (c >= a.hd) continue;
-        float m[8], l[8], o[8];
-        float M = -INFINITY;
+__device__ __forceinline__ void decode_write_out(const FattnArgs& a, const float* slab, const float (*s_m)[kDecRows],
+                                                 const float (*s_l)[kDecRows], uint8_t* recv, int R, int b, int hk, int split,
+                                                 int tq_b, int tid) {
+    constexpr int STRIDE = HD + 4, G = HD / 4;
+    const int warp = tid >> 5, lane = tid & 31;
+    const float ninf = -INFINITY;
+    const bool push = a.n_splits > 1 && a.cluster_merge;
+    float4* recv_o = reinterpret_cast<float4*>(recv);
+    float2* recv_ml = reinterpret_cast<float2*>(recv_o + (R * G + 8));
+    const int n_groups = R * G, slots = (n_groups + a.n_splits - 1) / a.n_splits;
+    if (push) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // every CTA of the cluster has started
+    for (int rr = warp; rr < R; rr += 4) {
+        const float m0 = s_m[0][rr], m1 = s_m[1][rr], m2 = s_m[2][rr], m3 = s_m[3][rr];
+        const float l0 = s_l[0][rr], l1 = s_l[1][rr], l2 = s_l[2][rr], l3 = s_l[3][rr];
+        const float M = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        const float w0 = m0 == ninf ? 0.0f : fast_ex2(m0 - M), w1 = m1 == ninf ? 0.0f : fast_ex2(m1 - M);
+        const float w2 = m2 == ninf ? 0.0f : fast_ex2(m2 - M), w3 = m3 == ninf ? 0.0f : fast_ex2(m3 - M);
+        const float L = (w0 * l0 + w1 * l1) + (w2 * l2 + w3 * l3);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane < G) {
+            const float4 x0 = *reinterpret_cast<const float4*>(slab + (0 * kDecRows + rr) * STRIDE + 4 * lane);
+            const float4 x1 = *reinterpret_cast<const float4*>(slab + (1 * kDecRows + rr) * STRIDE + 4 * lane);
+            const float4 x2 = *reinterpret_cast<const float4*>(slab + (2 * kDecRows + rr) * STRIDE + 4 * lane);
+            const float4 x3 = *reinterpret_cast<const float4*>(slab + (3 * kDecRows + rr) * STRIDE + 4 * lane);
+            // a warp that saw no live key holds zeros and weight 0
+            v.x = (w0 * x0.x + w1 * x1.x) + (w2 * x2.x + w3 * x3.x), v.y = (w0 * x0.y + w1 * x1.y) + (w2 * x2.y + w3 * x3.y);
+            v.z = (w0 * x0.z + w1 * x1.z) + (w2 * x2.z + w3 * x3.z), v.w = (w0 * x0.w + w1 * x1.w) + (w2 * x2.w + w3 * x3.w);
+        }
+        if (a.n_splits == 1) {
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            const float inv = (L > 0.0f && iq < tq_b) ? 1.0f / L : 0.0f;
+            float* drow = a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd;
+            if (lane < G) {
+                if (a.hd == HD) {
+                    *reinterpret_cast<float4*>(drow + 4 * lane) = make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv);
+                } else {   // a head dim padded up to HD: the row is a.hd floats long
+                    const float vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int s = 0; s < 8; s++) {
-            m[s] = -INFINITY, l[s] = 0.0f, o[s] = 0.0f;
-            if (s < n) {
-                m[s] = ld_peer_f32(s_M + rr, s);
-                l[s] = ld_peer_f32(s_L + rr, s);
-                o[s] = ld_peer_f32(part + rr * STRIDE + c, s);
+                    for (int j = 0; j < 4; j++)
+                        if (4 * lane + j < a.hd) drow[4 * lane + j] = vv[j] * inv;
+                }
             }
-            M = fmaxf(M, m[s]);
+        } else if (a.cluster_merge) {
+            if (lane < G) {
+                const int grp = rr * G + lane;   // owner grp % n_splits, its slot grp / n_splits
+                st_peer_v4(peer_addr(recv_o + split * slots + grp / a.n_splits, grp % a.n_splits), v);
+            }
+            if (lane < a.n_splits) st_peer_v2(peer_addr(recv_ml + split * kDecRows + rr, lane), M, L);
+        } else {
+            const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
+            if (lane < G) *reinterpret_cast<float4*>(a.ws_o + unit * kDecRows * HD + rr * HD + 4 * lane) = v;   // live rows only: the merge kernel reads no others
+            if (lane == 0) a.ws_ml[(unit * kDecRows + rr) * 2] = M, a.ws_ml[(unit * kDecRows + rr) * 2 + 1] = L;
         }
-        float L = 0.0f, acc = 0.0f;
-#pragma unroll
-        for (int s = 0; s < 8; s++) {
-            const float w = m[s] == -INFINITY ? 0.0f : exp2f(m[s] - M);
-            L = fmaf(w, l[s], L), acc = fmaf(w, o[s], acc);
-        }
-        const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
-        a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = (L > 0.0f && iq < q_rows_of(a, b)) ? acc / L : 0.0f;
     }
-    cluster_sync_all();
+    if (push) {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        for (int pos = tid; pos * a.n_splits + split < n_groups; pos += kThreads) {
+            const int grp = pos * a.n_splits + split, rr = grp / G, cg = grp % G;
+            float2 ml[8];
+            float M = ninf;
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                ml[s] = make_float2(ninf, 0.0f);
+                if (s < a.n_splits) ml[s] = recv_ml[s * kDecRows + rr];
+                M = fmaxf(M, ml[s].x);
+            }
+            float L = 0.0f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                if (s < a.n_splits && ml[s].x != ninf) {   // a split that saw no live key holds zeros
+                    const float w = fast_ex2(ml[s].x - M);
+                    const float4 x = recv_o[s * slots + pos];
+                    L = fmaf(w, ml[s].y, L);
+                    acc.x = fmaf(w, x.x, acc.x), acc.y = fmaf(w, x.y, acc.y), acc.z = fmaf(w, x.z, acc.z), acc.w = fmaf(w, x.w, acc.w);
+                }
+            }
+            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            const float inv = (L > 0.0f && iq < tq_b) ? 1.0f / L : 0.0f;
+            *reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * HD + 4 * cg) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);   // the cluster form is offered for a.hd == HD only
+        }
+    }
 }
 
 // IDX (F16 ring; PLAIN or STAGE_MASK): keys are gathered through ext->kv_index (one list per batch entry); an explicit
@@ -635,13 +714,14 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     // stalling on global loads issued right before their use.
     constexpr bool stage_mask = STAGE_MASK;   // separate instantiation: the maskless kernel carries none of it
     __half* sMask = reinterpret_cast<__half*>(sRaw);   // [NS][R][64] (F16 ring mode has no raw stages)
-    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
+    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int bk = b / a.bq;
     const int R = a.Tq * a.gqa;  // <= 16; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
     const float ninf = -INFINITY;
+    cluster_announce(a);
 
     // launched with programmatic stream serialisation: the previous kernel of the stream has completed and flushed
     // before anything is read or written (a no-op under an ordinary launch)
@@ -883,71 +963,31 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     // the merge kernel (if any) may start launching: it waits for this grid's completion before reading anything
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- merge the four warps' (m, l, O) in shared memory ----
-    __syncthreads();  // all warps are done with the K/V tiles
-    // Each warp scales its partial O to the common maximum and parks it in its own padded slab (plain stores; the
-    // slabs start at the base of dynamic shared memory - Q and the tiles are dead by now); the CTA then sums the four
-    // slabs while writing out.  (Shared-memory atomics on one [16][HD] array serialised the four warps and cost
-    // about 15 us per launch when a CTA has a single tile.)
     constexpr int SLAB_STRIDE = HD + 4;
     float* slab = reinterpret_cast<float*>(smem_raw);   // [4][16][SLAB_STRIDE]
-    const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
-    if (t == 0) {
-        s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
-        s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
+    {
+        const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
+        if (t == 0) {   // static shared memory: written before the barrier that retires the tiles
+            s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
+            s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
+        }
+    }
+    __syncthreads();  // all warps are done with the K/V tiles; the warps' (m, l) are visible
+    // Each warp parks its partial O as it is, scaled to its OWN running maximum, in its own padded slab (the slabs start
+    // at the base of dynamic shared memory - Q and the tiles are dead by now): a thread's accumulators of one n-tile are
+    // two consecutive dims of rows g and g + 8, one 8-byte store each; rows at or beyond R are never read.
+    // (Shared-memory atomics on one [16][HD] array serialised the four warps and cost about 15 us per launch when a
+    // CTA has a single tile.)
+#pragma unroll
+    for (int rI = 0; rI < NR; rI++) {
+        if (g + rI * 8 >= R) continue;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; nt++)
+            *reinterpret_cast<float2*>(slab + (warp * kDecRows + g + rI * 8) * SLAB_STRIDE + nt * 8 + 2 * t) =
+                make_float2(o[nt][2 * rI], o[nt][2 * rI + 1]);
     }
     __syncthreads();
-    float fac[2];
-#pragma unroll
-    for (int rI = 0; rI < 2; rI++) {
-        const int rr = g + rI * 8;
-        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
-        fac[rI] = (m_run[rI] == ninf) ? 0.0f : exp2f(m_run[rI] - M);
-    }
-#pragma unroll
-    for (int nt = 0; nt < HD / 8; nt++)
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int rI = e >> 1;
-            const int dim = nt * 8 + 2 * t + (e & 1);
-            slab[(warp * kDecRows + g + rI * 8) * SLAB_STRIDE + dim] = fac[rI] != 0.0f ? o[nt][e] * fac[rI] : 0.0f;
-        }
-    if (tid < kDecRows) {
-        const int rr = tid;
-        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
-        float L = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) L += (s_m[w][rr] == ninf) ? 0.0f : s_l[w][rr] * exp2f(s_m[w][rr] - M);
-        s_M[rr] = M, s_L[rr] = L;
-    }
-    __syncthreads();
-    auto merged = [&](int rr, int c) {
-        return (slab[(0 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(1 * kDecRows + rr) * SLAB_STRIDE + c]) +
-               (slab[(2 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(3 * kDecRows + rr) * SLAB_STRIDE + c]);
-    };
-
-    if (a.n_splits == 1) {
-        for (int idx = tid; idx < R * HD; idx += kThreads) {
-            const int rr = idx / HD, c = idx % HD;
-            if (c >= a.hd) continue;
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
-            const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = (L > 0.0f && iq < tq_b) ? merged(rr, c) / L : 0.0f;
-        }
-    } else if (a.cluster_merge) {
-        for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
-            const int rr = idx / HD, c = idx % HD;
-            slab[rr * SLAB_STRIDE + c] = merged(rr, c);
-        }
-        cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
-    } else {
-        const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
-        float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < R * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);   // live rows only: the merge kernel reads no others
-        if (tid < kDecRows) {
-            a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
-            a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
-        }
-    }
+    decode_write_out<HD>(a, slab, s_m, s_l, reinterpret_cast<uint8_t*>(sRaw) + (MODE == kDecAsyncQ8 ? NS * 2 * RAW_BYTES : (stage_mask ? NS * R * kDecBN * (int)sizeof(__half) : 0)), R, b, hk, split, tq_b, tid);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -979,7 +1019,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);                                  // [16][HD], 16-byte chunks swizzled
     uint8_t* sRaw = smem_raw + kDecRows * HD * sizeof(__half);                          // NS stages of raw K | V
-    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
+    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows];
     __shared__ __align__(8) uint64_t s_bar[4][NS];                                      // one barrier per (warp, stage)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -987,6 +1027,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     const int bk = b / a.bq;
     const int R = a.Tq * a.gqa;  // <= 16; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
     const float ninf = -INFINITY;
+    cluster_announce(a);
 
     // launched with programmatic stream serialisation: the previous kernel of the stream has completed and flushed
     // before anything is read or written (a no-op under an ordinary launch)
@@ -1231,71 +1272,32 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
     // the merge kernel (if any) may start launching: it waits for this grid's completion before reading anything
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- merge the four warps' (m, l, O) in shared memory ----
-    __syncthreads();  // all warps are done with the raw stages (the merge slabs alias them)
-    // Each warp scales its partial O to the common maximum and parks it in its own padded slab (plain stores; the
-    // slabs start at the base of dynamic shared memory - Q and the tiles are dead by now); the CTA then sums the four
-    // slabs while writing out.  (Shared-memory atomics on one [16][HD] array serialised the four warps and cost
-    // about 15 us per launch when a CTA has a single tile.)
     constexpr int SLAB_STRIDE = HD + 4;
     float* slab = reinterpret_cast<float*>(smem_raw);   // [4][16][SLAB_STRIDE]
-    const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
-    if (t == 0) {
-        s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
-        s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
+    {
+        const float lq[2] = {quad_sum(l_run[0]), quad_sum(l_run[1])};
+        if (t == 0) {   // static shared memory: written before the barrier that retires the tiles
+            s_m[warp][g] = m_run[0], s_m[warp][g + 8] = m_run[1];
+            s_l[warp][g] = lq[0], s_l[warp][g + 8] = lq[1];
+        }
+    }
+    __syncthreads();  // all warps are done with the raw stages (the merge slabs alias them); the warps' (m, l) are visible
+    // Each warp parks its partial O as it is, scaled to its OWN running maximum, in its own padded slab (the slabs start
+    // at the base of dynamic shared memory - Q and the raw stages are dead by now): the four n-tiles of a block give a
+    // thread four consecutive dims of rows g and g + 8 (dim = 32 blk + 4 (2t + e) + n-tile), one 16-byte store each;
+    // rows at or beyond R are never read.
+#pragma unroll
+    for (int rI = 0; rI < NR; rI++) {
+        if (g + rI * 8 >= R) continue;
+#pragma unroll
+        for (int blk = 0; blk < HD / 32; blk++)
+#pragma unroll
+            for (int e = 0; e < 2; e++)
+                *reinterpret_cast<float4*>(slab + (warp * kDecRows + g + rI * 8) * SLAB_STRIDE + 32 * blk + 4 * (2 * t + e)) =
+                    make_float4(o[4 * blk + 0][2 * rI + e], o[4 * blk + 1][2 * rI + e], o[4 * blk + 2][2 * rI + e], o[4 * blk + 3][2 * rI + e]);
     }
     __syncthreads();
-    float fac[2];
-#pragma unroll
-    for (int rI = 0; rI < 2; rI++) {
-        const int rr = g + rI * 8;
-        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
-        fac[rI] = (m_run[rI] == ninf) ? 0.0f : exp2f(m_run[rI] - M);
-    }
-#pragma unroll
-    for (int nt = 0; nt < HD / 8; nt++)
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int rI = e >> 1;
-            const int dim = 32 * (nt >> 2) + 4 * (2 * t + (e & 1)) + (nt & 3);
-            slab[(warp * kDecRows + g + rI * 8) * SLAB_STRIDE + dim] = fac[rI] != 0.0f ? o[nt][e] * fac[rI] : 0.0f;
-        }
-    if (tid < kDecRows) {
-        const int rr = tid;
-        const float M = fmaxf(fmaxf(s_m[0][rr], s_m[1][rr]), fmaxf(s_m[2][rr], s_m[3][rr]));
-        float L = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) L += (s_m[w][rr] == ninf) ? 0.0f : s_l[w][rr] * exp2f(s_m[w][rr] - M);
-        s_M[rr] = M, s_L[rr] = L;
-    }
-    __syncthreads();
-    auto merged = [&](int rr, int c) {
-        return (slab[(0 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(1 * kDecRows + rr) * SLAB_STRIDE + c]) +
-               (slab[(2 * kDecRows + rr) * SLAB_STRIDE + c] + slab[(3 * kDecRows + rr) * SLAB_STRIDE + c]);
-    };
-
-    if (a.n_splits == 1) {
-        for (int idx = tid; idx < R * HD; idx += kThreads) {
-            const int rr = idx / HD, c = idx % HD;
-            if (c >= a.hd) continue;
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
-            const float L = s_L[rr];
-            a.dst[(((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd + c] = (L > 0.0f && iq < tq_b) ? merged(rr, c) / L : 0.0f;
-        }
-    } else if (a.cluster_merge) {
-        for (int idx = tid; idx < R * HD; idx += kThreads) {   // slab 0 <- the CTA's merged partial, in place
-            const int rr = idx / HD, c = idx % HD;
-            slab[rr * SLAB_STRIDE + c] = merged(rr, c);
-        }
-        cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
-    } else {
-        const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
-        float* wo = a.ws_o + unit * kDecRows * HD;
-        for (int idx = tid; idx < R * HD; idx += kThreads) wo[idx] = merged(idx / HD, idx % HD);   // live rows only: the merge kernel reads no others
-        if (tid < kDecRows) {
-            a.ws_ml[(unit * kDecRows + tid) * 2] = s_M[tid];
-            a.ws_ml[(unit * kDecRows + tid) * 2 + 1] = s_L[tid];
-        }
-    }
+    decode_write_out<HD>(a, slab, s_m, s_l, sRaw + NS * 2 * RAW_BYTES, R, b, hk, split, tq_b, tid);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1345,7 +1347,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);                                  // [16][HD], 16-byte chunks swizzled
     uint8_t* sRaw = smem_raw + kDecRows * HD * sizeof(__half);                          // NS stages of raw K | V
-    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows], s_M[kDecRows], s_L[kDecRows];
+    __shared__ float s_m[4][kDecRows], s_l[4][kDecRows];
     __shared__ __align__(8) uint64_t s_bar[4][NS];                                      // one barrier per (warp, stage)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -1354,6 +1356,7 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     const int bk = b / a.bq;
     const int R = a.Tq * a.gqa;  // <= 8; row rr -> (iq = rr / gqa, head hk*gqa + rr % gqa)
     const float ninf = -INFINITY;
+    cluster_announce(a);
 
     // launched with programmatic stream serialisation: the previous kernel of the stream has completed and flushed
     // before anything is read or written (a no-op under an ordinary launch)
@@ -1371,12 +1374,14 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     // A CTA of this kernel shares its SM with three others in their key loops, where a lone thread gets an issue slot
     // every few tens of clocks: the set-up below is spread over lanes so that its chain of dependent instructions is
     // short - lane i initialises barrier i, lanes 2s and 2s+1 request the K and the V bytes of stage s.
+    Q8T_TRACE(14);
     if (lane < NS) {
         mbar_init(smem_u32(&s_bar[warp][lane]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
+    Q8T_TRACE(15);
     // lanes 2s (K) and 2s+1 (V) of a warp copy the raw bytes of the warp's 16 keys of tile `tile0 + s`; lane 2s also
     // announces both copies to the stage's barrier.  Copies stop at the stream's length (whole 16-byte units).
     auto issue_lanes = [&](int tile0, int n_stages) {
@@ -1693,45 +1698,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     Q8T_TRACE(12);
     __syncthreads();
     Q8T_TRACE(9);
-    // Write-out: one warp per live row, one 16-byte column group per lane, the log-sum-exp merge of the four warps'
-    // partials on the way.  A CTA of this kernel lives for nine tiles at the usual cache lengths and shares its SM with
-    // three others in their key loops, where every dependent step of a tail like this one waits for an issue slot: the
-    // first form (scale by the common maximum, barrier, per-row sums by sixteen threads, barrier, element-wise write-out
-    // with an index division per element) took a sixth of the CTA's lifetime.
-    for (int rr = warp; rr < R; rr += 4) {
-        const float m0 = s_m[0][rr], m1 = s_m[1][rr], m2 = s_m[2][rr], m3 = s_m[3][rr];
-        const float l0 = s_l[0][rr], l1 = s_l[1][rr], l2 = s_l[2][rr], l3 = s_l[3][rr];
-        const float M = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-        const float w0 = m0 == ninf ? 0.0f : fast_ex2(m0 - M), w1 = m1 == ninf ? 0.0f : fast_ex2(m1 - M);
-        const float w2 = m2 == ninf ? 0.0f : fast_ex2(m2 - M), w3 = m3 == ninf ? 0.0f : fast_ex2(m3 - M);
-        const float L = (w0 * l0 + w1 * l1) + (w2 * l2 + w3 * l3);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (lane < HD / 4) {
-            const float4 x0 = *reinterpret_cast<const float4*>(slab + (0 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
-            const float4 x1 = *reinterpret_cast<const float4*>(slab + (1 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
-            const float4 x2 = *reinterpret_cast<const float4*>(slab + (2 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
-            const float4 x3 = *reinterpret_cast<const float4*>(slab + (3 * kDecRows + rr) * SLAB_STRIDE + 4 * lane);
-            // a warp that saw no live key holds zeros and weight 0
-            v.x = (w0 * x0.x + w1 * x1.x) + (w2 * x2.x + w3 * x3.x), v.y = (w0 * x0.y + w1 * x1.y) + (w2 * x2.y + w3 * x3.y);
-            v.z = (w0 * x0.z + w1 * x1.z) + (w2 * x2.z + w3 * x3.z), v.w = (w0 * x0.w + w1 * x1.w) + (w2 * x2.w + w3 * x3.w);
-        }
-        if (a.n_splits == 1) {
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
-            const float inv = (L > 0.0f && iq < tq_b) ? 1.0f / L : 0.0f;
-            if (lane < HD / 4)
-                *reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * HD + 4 * lane) =
-                    make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv);
-        } else if (a.cluster_merge) {
-            // slab 0 <- the CTA's merged partial, in place (a lane rewrites the columns it read; rows belong to one warp)
-            if (lane < HD / 4) *reinterpret_cast<float4*>(slab + rr * SLAB_STRIDE + 4 * lane) = v;
-            if (lane == 0) s_M[rr] = M, s_L[rr] = L;
-        } else {
-            const int64_t unit = ((int64_t)b * a.Hkv + hk) * a.n_splits + split;
-            if (lane < HD / 4) *reinterpret_cast<float4*>(a.ws_o + unit * kDecRows * HD + rr * HD + 4 * lane) = v;   // live rows only: the merge kernel reads no others
-            if (lane == 0) a.ws_ml[(unit * kDecRows + rr) * 2] = M, a.ws_ml[(unit * kDecRows + rr) * 2 + 1] = L;
-        }
-    }
-    if (a.n_splits > 1 && a.cluster_merge) cluster_merge_store<HD>(a, slab, s_M, s_L, R, b, hk, split, tid);
+    Q8T_TRACE(13);
+    decode_write_out<HD>(a, slab, s_m, s_l, sRaw + NS * 2 * RAW_BYTES, R, b, hk, split, tq_b, tid);
     Q8T_TRACE(10);
 }
 
@@ -1834,7 +1802,7 @@ bool use_cluster_merge(const FattnArgs& a) {
     // only while the whole grid is resident at once (2 to 4 CTAs on each of 148 SMs): with several waves the cluster
     // barriers hold finished CTAs on their SMs and the form measured 10 % slower than the merge kernel
     return decode_cluster_merge_ok(a) && a.n_splits > 1 && a.n_splits <= 8 &&
-           (long)a.n_splits * a.Hkv * a.B <= (long)decode_ctas_per_sm(a) * 148;
+           (long)a.n_splits * a.Hkv * a.B <= (long)decode_ctas_per_sm(a, true) * 148;
 }
 
 template <typename Kern>
@@ -1874,9 +1842,10 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     size_t smem = (size_t)(kDecRows + F16_TILES * kDecBN) * HD * sizeof(__half);
     if (MODE == kDecAsyncQ8) smem += (size_t)NS * 2 * kDecBN * (HD / 32 * 34);
     // the attribute is raised once, to the largest size this instantiation can ask for (mask staging for 16 rows)
-    const size_t smem_attr = smem + (MODE == kDecAsyncF16 ? (size_t)NS * kDecRows * kDecBN * sizeof(__half) : 0);
+    const size_t smem_attr = smem + (MODE == kDecAsyncF16 ? (size_t)NS * kDecRows * kDecBN * sizeof(__half) : 0) + cluster_push_bytes(HD, kDecRows);
     const bool staged_mask = MODE == kDecAsyncF16 && a.has_mask && a.mask.vec16 && a.softcap == 0.0f && !a.causal && a.n2 == 0;
     if (staged_mask) smem += (size_t)NS * (a.Tq * a.gqa) * kDecBN * sizeof(__half);
+    if (use_cluster_merge(a)) smem += cluster_push_bytes(HD, a.Tq * a.gqa);   // the receive area of the merge inside a cluster, behind everything else
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
     const bool low = a.Tq * a.gqa <= 8;
@@ -1907,31 +1876,31 @@ int launch_decode_m(const FattnArgs& a, cudaStream_t st) {
     } else if (MODE == kDecAsyncF16 && a.kv_index && low) {   // index lists come without mask / softcap / causal bound
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else if (MODE == kDecAsyncF16 && a.kv_index) {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, false, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal && low) {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else if (MODE == kDecAsyncF16 && !a.has_mask && a.softcap == 0.0f && !a.causal) {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, MODE == kDecAsyncF16>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else {
         auto kern = fattn_decode_split_kernel<HD, MODE, false, false>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     }
@@ -1963,7 +1932,10 @@ int decode_mode(const FattnArgs& a, int hdp) {
 
 template <int HD>
 int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
-    const size_t smem = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
+    // a cluster launch carries the receive area of the merge behind the stages; the attribute is raised once, to that size
+    const size_t smem_main = (size_t)kDecRows * HD * sizeof(__half) + (size_t)kDecRegStages * 2 * kDecBN * (HD / 32 * 34);
+    const size_t smem_attr = smem_main + cluster_push_bytes(HD, kDecRows);
+    const size_t smem = smem_main + (use_cluster_merge(a) ? cluster_push_bytes(HD, a.Tq * a.gqa) : 0);
     dim3 grid(a.n_splits, a.Hkv, a.B);
     cudaError_t e;
     // B200_DECODE_Q8T=0 keeps the rows-on-M register kernel, =1 (default) the keys-on-M kernel with F16 score MMAs, =2
@@ -1975,31 +1947,31 @@ int launch_decode_q8reg(const FattnArgs& a, cudaStream_t st) {
     if (keys_on_m == 2 && !a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
         auto kern = fattn_decode_q8t_kernel<HD, true>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else if (keys_on_m == 1 && !a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
         auto kern = fattn_decode_q8t_kernel<HD, false>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else if (!a.has_mask && a.softcap == 0.0f && !a.causal && a.Tq * a.gqa <= 8) {
         auto kern = fattn_decode_q8reg_kernel<HD, true, true>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else if (!a.has_mask && a.softcap == 0.0f && !a.causal) {
         auto kern = fattn_decode_q8reg_kernel<HD, true, false>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     } else {
         auto kern = fattn_decode_q8reg_kernel<HD, false, false>;
         static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
+        e = set_smem_once(kern, smem_attr, smem_set);
         if (e != cudaSuccess) return (int)e;
         launch_split(kern, grid, smem, st, a);
     }
@@ -2139,7 +2111,7 @@ bool decode_cluster_merge_ok(const FattnArgs& a) {
 
 // CTAs of the split kernel that fit on one SM for these operands (shared memory of the staging form; registers
 // allow four).
-int decode_ctas_per_sm(const FattnArgs& a) {
+int decode_ctas_per_sm(const FattnArgs& a, bool cluster) {
     const int hdp = a.hd <= 32 ? 32 : (a.hd <= 64 ? 64 : 128);
     size_t smem;
     switch (decode_mode(a, hdp)) {
@@ -2153,7 +2125,8 @@ int decode_ctas_per_sm(const FattnArgs& a) {
         case kDecAsyncQ8: smem = (size_t)(kDecRows + kDecBN) * hdp * 2 + (size_t)kDecQ8Stages * 2 * kDecBN * (hdp / 32 * 34); break;
         default: smem = (size_t)(kDecRows + 2 * kDecBN) * hdp * 2; break;
     }
-    const int n = (int)((size_t)227 * 1024 / (smem + 1024));
+    if (cluster) smem += cluster_push_bytes(hdp, a.Tq * a.gqa);   // the receive area of the merge
+    const int n = (int)((size_t)227 * 1024 / (smem + 640 + 1024));   // static shared memory of the kernels, 1 KB the system keeps per CTA
     return n < 1 ? 1 : (n > 4 ? 4 : n);
 }
 
@@ -2178,6 +2151,7 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
     if (forced) return forced < tiles ? forced : tiles;
     const double units = (double)B * a.Hkv;
     const double cap = (double)(per_sm_env ? per_sm_env : decode_ctas_per_sm(a)) * sm_count;
+    const double cap_cluster = (double)(per_sm_env ? per_sm_env : decode_ctas_per_sm(a, true)) * sm_count;   // with the receive area of the merge
     const bool cluster_ok = decode_cluster_merge_ok(a);
     int best = 1;
     double best_cost = 0.0;
@@ -2186,7 +2160,7 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
         if ((tiles + tps - 1) / tps != n) continue;   // some split would get no tile
         const double w = units * n / cap;
         const double waves = w <= 4.0 ? ceil(w) : w + 0.5;
-        const bool cluster = cluster_ok && n > 1 && n <= 8 && units * n <= cap;
+        const bool cluster = cluster_ok && n > 1 && n <= 8 && units * n <= cap_cluster;
         double cost = waves * (tps + 1.5 + (n == 1 ? 0.0 : (cluster ? 0.5 : 1.0)));
         // the merge reads n partials per output row.  F16 kernel (100 KB CTAs, merge kernel launched under its tail):
         // merge kernel 0.8 + 0.2 n, cluster 1.0 + 0.1 n, fitted to one segment of Whisper cross-attention (24 tiles:
@@ -2194,7 +2168,7 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
         // tiles: 12 workspace splits 3.87 k, 18: 3.61 k, 8 cluster splits 3.54 k) and to 2 / 4 / 8 segments (cluster
         // +13 % / +14 % / +4 % and 0 % / +9 % / +4 %)
         const bool f16 = a.k.type == B200_TYPE_F16;
-        if (n > 1) cost += cluster ? (f16 ? 1.0 : 0.0) + 0.1 * n : (f16 ? 0.8 : 1.5) + 0.2 * n;
+        if (n > 1) cost += cluster ? (f16 ? 1.0 : 0.0) + 0.1 * n : (f16 ? 0.8 : 3.0) + 0.2 * n;
         if (n == 1 || cost < best_cost - 1e-9) best = n, best_cost = cost;
     }
     return best;
