@@ -2164,9 +2164,9 @@ int decode_split_choose(const FattnArgs& a, int B, int sm_count) {
         double cost = waves * (tps + 1.5 + (n == 1 ? 0.0 : (cluster ? 0.5 : 1.0)));
         // the merge reads n partials per output row.  F16 kernel (100 KB CTAs, merge kernel launched under its tail):
         // merge kernel 0.8 + 0.2 n, cluster 1.0 + 0.1 n, fitted to one segment of Whisper cross-attention (24 tiles:
-        // 8 cluster splits 4.93 k segment-steps/s, 12 workspace splits 4.66 k) and of the pooled self-attention (36
-        // tiles: 12 workspace splits 3.87 k, 18: 3.61 k, 8 cluster splits 3.54 k) and to 2 / 4 / 8 segments (cluster
-        // +13 % / +14 % / +4 % and 0 % / +9 % / +4 %)
+        // 8 cluster splits 5.54 k segment-steps/s, 12 workspace splits 4.67 k) and of the pooled self-attention (36
+        // tiles: 12 workspace splits 3.95 k, 18: 3.61 k, 6 / 8 cluster splits 3.91 / 3.83 k) and to 2 / 4 / 8 segments.
+        // Q8_0 kernel through the workspace: 3.0 + 0.2 n (32 streams: one split 80.0 k stream-steps/s, two 71.9 k)
         const bool f16 = a.k.type == B200_TYPE_F16;
         if (n > 1) cost += cluster ? (f16 ? 1.0 : 0.0) + 0.1 * n : (f16 ? 0.8 : 3.0) + 0.2 * n;
         if (n == 1 || cost < best_cost - 1e-9) best = n, best_cost = cost;
