@@ -455,6 +455,31 @@ __device__ __forceinline__ void issue_tile_f16(__half* sm, const uint8_t* base, 
     }
 }
 
+// The same copy for a gathered tile whose cache rows were looked up one tile ahead: `pre[it]` is the cache row of
+// this thread's it-th 16-byte piece (see load_tile_index), so the copies do not wait for the list.
+template <int HD>
+__device__ __forceinline__ void load_tile_index(int (&pre)[kDecBN * (HD / 8) / kThreads], const int32_t* index, int row0, int row_hi,
+                                                int tid) {
+    constexpr int CPR = HD / 8;
+#pragma unroll
+    for (int it = 0; it < kDecBN * CPR / kThreads; it++) {
+        const int grow = row0 + (tid + it * kThreads) / CPR;
+        pre[it] = grow < row_hi ? __ldg(index + grow) : 0;   // clamped where it is used: nothing here waits for the load
+    }
+}
+template <int HD>
+__device__ __forceinline__ void issue_tile_f16_pre(__half* sm, const uint8_t* base, int64_t nb1, int row0, int row_hi, int tid,
+                                                   const int (&pre)[kDecBN * (HD / 8) / kThreads], int pool_rows) {
+    constexpr int CPR = HD / 8;
+#pragma unroll
+    for (int it = 0; it < kDecBN * CPR / kThreads; it++) {
+        const int idx = tid + it * kThreads;
+        const int row = idx / CPR, ch = idx % CPR;
+        const bool valid = row0 + row < row_hi;
+        cp_async16(tile_addr<HD>(sm, row, ch), base + (valid ? (int64_t)min(max(pre[it], 0), pool_rows - 1) * nb1 + ch * 16 : 0), valid);
+    }
+}
+
 // ---- bulk copies (one instruction per contiguous range) with a per-warp mbarrier per stage ----
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -748,6 +773,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         }
         __syncwarp();
     }
+    int pre_rows[kDecBN * (HD / 8) / kThreads];   // gathered keys: this thread's cache rows of the next tile to be issued
+    if (IDX && tile_lo < tile_hi) load_tile_index<HD>(pre_rows, index, tile_lo * kDecBN, len_b, tid);
     auto issue = [&](int tile) {
         if (MODE == kDecAsyncQ8) {
             if (tile < tile_hi && lane == 0) {
@@ -759,8 +786,15 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         }
         if (tile < tile_hi) {
             const int stage = (tile - tile_lo) % NS;
-            issue_tile_f16<HD, IDX>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid, index, a.Lk);
-            issue_tile_f16<HD, IDX>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid, index, a.Lk);
+            if (IDX) {
+                // tiles are issued in order: the list entries of this one were requested when the previous one was issued
+                issue_tile_f16_pre<HD>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid, pre_rows, a.Lk);
+                issue_tile_f16_pre<HD>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid, pre_rows, a.Lk);
+                if (tile + 1 < tile_hi) load_tile_index<HD>(pre_rows, index, (tile + 1) * kDecBN, len_b, tid);
+            } else {
+                issue_tile_f16<HD, false>(sKV + stage * 2 * TILE_HALVES, kbase, a.k.nb1, tile * kDecBN, len_b, tid);
+                issue_tile_f16<HD, false>(sKV + stage * 2 * TILE_HALVES + TILE_HALVES, vbase, a.v.nb1, tile * kDecBN, len_b, tid);
+            }
             if (stage_mask && tid < R * 8) {
                 const int rr = tid >> 3, ch = tid & 7;
                 const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
