@@ -292,6 +292,40 @@ def test_decode_forced_split_counts(b200, orc, n_splits, kv_kind):
     assert_close(got, ref, f"decode {kv_kind}, {n_splits} splits forced")
 
 
+@pytest.mark.parametrize("n_splits", [2, 5, 8])
+@pytest.mark.parametrize("shape", [("f16", 64, 5, 1, False), ("f16", 64, 5, 1, True), ("f16", 64, 3, 4, False), ("f16", 128, 4, 4, False),
+                                   ("q8_0", 128, 4, 4, False), ("q8_0", 64, 2, 4, False), ("q8_0", 128, 3, 4, True)])
+def test_cluster_merge_row_counts(b200, orc, n_splits, shape):
+    """The merge inside a thread-block cluster with 5, 8, 12 and 16 query rows per KV head (the receive area of a CTA
+    is sized by the row count), head dims 64 and 128, both cache types, with and without an explicit mask; ragged
+    lengths leave some CTAs of a cluster without a key."""
+    kv_kind, hd, Tq, gqa, masked = shape
+    rng = np.random.default_rng(900 + n_splits + hd + Tq)
+    S, Hkv, max_ctx, Lk = 2, 2, 704, 640
+    H = Hkv * gqa
+    lens = [640, 130]
+    q = randn_f16(rng, (S, H, Tq, hd)).astype(np.float32)
+    kw = dict(scale=hd ** -0.5, kv_len=lens)
+    if kv_kind == "q8_0":
+        kc, vc = _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx), _q8_cache(orc, rng, S, Hkv, max_ctx, hd, max_ctx)
+        kw["kv_type"] = abi.Q8_0
+    else:
+        kc, vc = randn_f16(rng, (S, Hkv, max_ctx, hd)), randn_f16(rng, (S, Hkv, max_ctx, hd))
+    kv, vv = kc[:, :, :Lk], vc[:, :, :Lk]
+    mask = None
+    if masked:
+        mask = np.where(rng.random((S, 1, Tq, Lk)) < 0.3, -np.inf, 0.0).astype(np.float16)
+        mask[..., 0] = 0
+    ref = orc.flash_attn_ext(q, kv, vv, mask, **kw)
+    assert b200.lib().b200_set_decode_splits(n_splits) == 0
+    try:
+        got = gpu_op(b200, q, cuda_view(kv, kc), cuda_view(vv, vc), mask, **kw)
+        assert b200.lib().b200_last_kernel() == abi.KERNEL_DECODE_SPLIT
+    finally:
+        assert b200.lib().b200_set_decode_splits(0) == 0
+    assert_close(got, ref, f"cluster merge {kv_kind} hd={hd} rows={Tq * gqa} mask={masked}, {n_splits} splits")
+
+
 def test_cfg4_decode_f16_cache_gqa(b200, orc, kernel):
     rng = np.random.default_rng(33)
     S, H, Hkv, hd, Lk = 4, 32, 8, 128, 535
