@@ -748,17 +748,6 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     const float ninf = -INFINITY;
     cluster_announce(a);
 
-    // launched with programmatic stream serialisation: the previous kernel of the stream has completed and flushed
-    // before anything is read or written (a no-op under an ordinary launch)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int len_b = clamp_len(a, b);
-    const int tq_b = q_rows_of(a, b);   // query rows at or beyond it give zeros
-    int kmax = tq_b > 0 ? len_b : 0;    // an entry without live rows reads no keys
-    const int n_past = n_past_of(a, len_b, tq_b);
-    if (a.causal) kmax = min(kmax, n_past + tq_b);
-    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
-    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
-    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
     const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
     const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
     const int32_t* index = a.kv_index ? a.kv_index + (int64_t)b * a.kv_index_stride : nullptr;   // this entry's key list
@@ -773,6 +762,18 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         }
         __syncwarp();
     }
+    // Launched with programmatic stream serialisation: everything above (kernel parameters, this CTA's own shared
+    // memory) ran while the previous kernel of the stream drained; from here on that kernel has completed and flushed
+    // (a no-op under an ordinary launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int len_b = clamp_len(a, b);
+    const int tq_b = q_rows_of(a, b);   // query rows at or beyond it give zeros
+    int kmax = tq_b > 0 ? len_b : 0;    // an entry without live rows reads no keys
+    const int n_past = n_past_of(a, len_b, tq_b);
+    if (a.causal) kmax = min(kmax, n_past + tq_b);
+    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
+    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
     int pre_rows[kDecBN * (HD / 8) / kThreads];   // gathered keys: this thread's cache rows of the next tile to be issued
     if (IDX && tile_lo < tile_hi) load_tile_index<HD>(pre_rows, index, tile_lo * kDecBN, len_b, tid);
     auto issue = [&](int tile) {
@@ -1392,16 +1393,6 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     const float ninf = -INFINITY;
     cluster_announce(a);
 
-    // launched with programmatic stream serialisation: the previous kernel of the stream has completed and flushed
-    // before anything is read or written (a no-op under an ordinary launch)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    Q8T_TRACE(1);
-    const int len_b = clamp_len(a, b);
-    const int tq_b = q_rows_of(a, b);
-    const int kmax = tq_b > 0 ? len_b : 0;
-    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
-    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
-    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
     const uint8_t* kbase = a.k.p + (int64_t)hk * a.k.nb2 + (int64_t)bk * a.k.nb3;
     const uint8_t* vbase = a.v.p + (int64_t)hk * a.v.nb2 + (int64_t)bk * a.v.nb3;
 
@@ -1416,6 +1407,17 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     }
     __syncwarp();
     Q8T_TRACE(15);
+    // Launched with programmatic stream serialisation: everything above (kernel parameters, this CTA's own shared
+    // memory) ran while the previous kernel of the stream drained; from here on that kernel has completed and flushed
+    // (a no-op under an ordinary launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    Q8T_TRACE(1);
+    const int len_b = clamp_len(a, b);
+    const int tq_b = q_rows_of(a, b);
+    const int kmax = tq_b > 0 ? len_b : 0;
+    const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
+    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
     // lanes 2s (K) and 2s+1 (V) of a warp copy the raw bytes of the warp's 16 keys of tile `tile0 + s`; lane 2s also
     // announces both copies to the stage's barrier.  Copies stop at the stream's length (whole 16-byte units).
     auto issue_lanes = [&](int tile0, int n_stages) {
@@ -1852,11 +1854,12 @@ void launch_split(Kern kern, dim3 grid, size_t smem, cudaStream_t st, const Fatt
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (!use_cluster_merge(a)) {   // clusters that become resident early measured slower (8 streams: 8.7 against 8.0 us per layer)
-        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[n].val.programmaticStreamSerializationAllowed = 1;
-        n++;
-    }
+    // also for the cluster form: with the pushed merge an early-resident cluster measures +3 to +4 % (8 / 16 streams
+    // of the Q8_0 cache, 1 / 4 Whisper segments); with the pulled merge, whose CTAs stayed resident through two cluster
+    // barriers, it had measured 8.7 against 8.0 us per layer
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
     if (use_cluster_merge(a)) {
         ac.cluster_merge = 1;
         attr[n].id = cudaLaunchAttributeClusterDimension;
