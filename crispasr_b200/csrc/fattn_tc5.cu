@@ -529,7 +529,7 @@ __device__ __forceinline__ void store_o_rows_coalesced(float* stage, int lane, f
 template <int HD, int NSTG, bool HASMASK, int EARLY = 0>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV) {
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQ, const int q_tma) {
     constexpr int PANELS = HD / 64;
     constexpr int TILE_BYTES = kPanelBytes * PANELS;
     constexpr uint32_t IDESC_S = idesc_f16(kTile, false);
@@ -545,8 +545,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8 * NSTG, bar_v_full = sBar + 16 * NSTG,
                    bar_v_empty = sBar + 24 * NSTG, bar_s_full = sBar + 32 * NSTG, bar_p_ready = bar_s_full + 8,
                    bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24, bar_s_read = bar_s_full + 32,
-                   bar_s_drain = bar_s_full + 40;
-    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 48;
+                   bar_s_drain = bar_s_full + 40, bar_q_full = bar_s_full + 48;
+    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 56;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
     constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
@@ -608,8 +608,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         mbar_init(bar_pv_done, 1);
         mbar_init(bar_s_read, 4);    // one arrival per softmax warp
         mbar_init(bar_s_drain, 1);
+        mbar_init(bar_q_full, 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (q_tma) {
+            // F16 query rows of one head (no group packing) go straight into the operand layout: one copy instead of
+            // a pass through the softmax warps' registers, which a CTA sharing its SM with another one in its key loop
+            // executes at a few tens of clocks per instruction.  Rows at or beyond Tq read as zeros.
+            mbar_arrive_expect_tx(bar_q_full, TILE_BYTES);
+#pragma unroll
+            for (int p = 0; p < PANELS; p++) tma_load_4d(sQ + p * kPanelBytes, &tmQ, bar_q_full, p * 64, q0, hk, b);
+        }
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
         // the first NSTG tiles need no empty-slot wait: start their copies before the CTA-wide set-up barrier
@@ -631,7 +640,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         if (lane == 0) TC5_TRACE(2, 61, 0);
     }
-    if (warp < 4) {
+    if (warp < 4 && !q_tma) {
         // Q tile -> shared memory (thread r writes row r)
         const int r = tid;
         const int iq = (q0 + r) / a.gqa, h = hk * a.gqa + (q0 + r) % a.gqa;
@@ -679,6 +688,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             }
             if (!ok) {
                 // drain: wait (bounded) for the copies this thread still has in flight
+                if (q_tma)
+                    for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_q_full, 0); ++it) __nanosleep(256);
                 for (int j = max(0, issued_k - NSTG); j < issued_k; j++)
                     for (uint32_t it = 0; it < 4096 && !mbar_try_wait(bar_k_full + 8 * (j % NSTG), (j / NSTG) & 1); ++it) __nanosleep(256);
                 for (int j = max(0, issued_v - NSTG); j < issued_v; j++)
@@ -784,6 +795,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, kPanelBytes);
             constexpr uint32_t desc_hi = smem_desc_hi(1024);
             bool ok = mbar_wait(bar_k_full, 0, s_abort);
+            if (ok && q_tma) ok = mbar_wait(bar_q_full, 0, s_abort);
             if (ok) {
                 TC5_TRACE(1, 0, 0);
                 tc_fence_after();
@@ -1916,7 +1928,17 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
         return B200_E_CUDA;
     }
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
-    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 40 + 16;
+    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 56 + 8;
+    // F16 query rows of one head per tile, 16-byte aligned: the Q tile is one tensor copy (B200_PREFILL_QTMA=0: through registers)
+    static const bool q_tma_on = [] {
+        const char* e = getenv("B200_PREFILL_QTMA");
+        return !(e && e[0] == '0');
+    }();
+    CUtensorMap tmQ = tmK;
+    int q_tma = 0;
+    if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && a.gqa == 1 && !a.bias_u && early_scores_mode() != 2 &&
+        a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
+        q_tma = encode_kv_map(&tmQ, a.q, a.hd, a.Tq, a.H, a.B) ? 1 : 0;
     cudaError_t e;
     dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
     if (a.has_mask) {
@@ -1924,28 +1946,28 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
         }
     } else if (HD == 64 && early_scores_mode() == 2) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 2 : 0>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
         }
     } else if (HD == 64 && early_scores_mode() == 1) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 1 : 0>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
         }
     } else {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
         }
     }
     if (e != cudaSuccess) {
