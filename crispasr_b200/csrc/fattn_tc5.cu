@@ -109,6 +109,19 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Tensor store shared -> global as its own bulk group; the caller waits for the group's reads of shared memory
+// before the CTA ends.  The innermost coordinate times the element size must be a multiple of 16 bytes, and no
+// coordinate may be negative.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1 (sm_100).
 //   K-major operand : rows of 128 bytes, 8-row groups 1024 bytes apart  -> LBO = 16 B (unused), SBO = 1024 B
 //   MN-major operand: 64-element chunks `lbo` bytes apart, 8-k groups 1024 bytes apart
@@ -529,7 +542,8 @@ __device__ __forceinline__ void store_o_rows_coalesced(float* stage, int lane, f
 template <int HD, int NSTG, bool HASMASK, int EARLY = 0>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQ, const int q_tma) {
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQ, const int q_tma,
+                         const __grid_constant__ CUtensorMap tmO, const int o_tma) {
     constexpr int PANELS = HD / 64;
     constexpr int TILE_BYTES = kPanelBytes * PANELS;
     constexpr uint32_t IDESC_S = idesc_f16(kTile, false);
@@ -1258,19 +1272,45 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             const float inv = row_live && l_run > 0.0f ? 1.0f / l_run : 0.0f;
             float* out = (row_live || row_zero) ? a.dst + (((int64_t)b * a.Tq + iq_dst) * a.H + h) * HD : nullptr;
             float* stage = reinterpret_cast<float*>(smem_gen + TILE_BYTES) + warp * 32 * HD;
+            if (o_tma) {
+                // One head per tile: a warp's 32 rows x 32 columns are a box of dst [hd, H, Tq, B]; the warp parks them as
+                // 128-byte rows with the 16-byte chunks swizzled by the row (the copy's own pattern, conflict-free for
+                // the stores) and one lane hands each panel to a tensor store, which also clips the rows beyond Tq.
 #pragma unroll
-            for (int q4 = 0; q4 < HD / 32; q4++) {
-                uint32_t oreg[32];
-                tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
-                tmem_wait_ld();
+                for (int q4 = 0; q4 < HD / 32; q4++) {
+                    uint32_t oreg[32];
+                    tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4*>(stage + lane * HD + ((((q4 * 32 + i) >> 2) ^ (lane & 7)) << 2)) =
-                        row_live ? make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
-                                               __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv)
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(stage + q4 * 32 * 32 + lane * 32 + (((i >> 2) ^ (lane & 7)) << 2)) =
+                            row_live ? make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
+                                                   __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0 && q0 + warp * 32 < a.Tq) {
+#pragma unroll
+                    for (int q4 = 0; q4 < HD / 32; q4++)
+                        tma_store_4d(&tmO, smem_u32(stage + q4 * 32 * 32), q4 * 32, hk, q0 + warp * 32, b);
+                    tma_store_commit_and_wait_read();
+                }
+            } else {
+#pragma unroll
+                for (int q4 = 0; q4 < HD / 32; q4++) {
+                    uint32_t oreg[32];
+                    tmem_ld32(tmem_O + lane_base + q4 * 32, oreg);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(stage + lane * HD + ((((q4 * 32 + i) >> 2) ^ (lane & 7)) << 2)) =
+                            row_live ? make_float4(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv,
+                                                   __uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                store_o_rows_coalesced<HD>(stage, lane, out);
             }
-            store_o_rows_coalesced<HD>(stage, lane, out);
         }
     }
 
@@ -1749,6 +1789,18 @@ bool encode_kv_map(CUtensorMap* m, const View& v, int hd, int Lk, int Hkv, int B
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// dst as a rank-4 F32 tensor [hd, H, Tq, B] (contiguous); box = 32 columns x one head x 32 query rows.
+bool encode_o_map(CUtensorMap* m, const FattnArgs& a) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.hd, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.hd * 4, (cuuint64_t)a.hd * 4 * a.H, (cuuint64_t)a.hd * 4 * a.H * a.Tq};
+    const cuuint32_t box[4] = {32, 1, 32, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // R as a rank-4 F16 tensor [hd, 2T-1, H, 1|B]; box = 64 columns x 128 rows.
 bool encode_r_map(CUtensorMap* m, const FattnArgs& a) {
     EncodeTiledFn fn = encode_fn();
@@ -1939,6 +1991,14 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && a.gqa == 1 && !a.bias_u && early_scores_mode() != 2 &&
         a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
         q_tma = encode_kv_map(&tmQ, a.q, a.hd, a.Tq, a.H, a.B) ? 1 : 0;
+    // one head per tile: a warp's rows of the output are a box of dst, written by tensor stores (B200_PREFILL_OTMA=0: by the threads)
+    static const bool o_tma_on = [] {
+        const char* e = getenv("B200_PREFILL_OTMA");
+        return !(e && e[0] == '0');
+    }();
+    CUtensorMap tmO = tmK;
+    int o_tma = 0;
+    if (o_tma_on && a.gqa == 1 && (uintptr_t)a.dst % 16 == 0) o_tma = encode_o_map(&tmO, a) ? 1 : 0;
     cudaError_t e;
     dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
     if (a.has_mask) {
@@ -1946,28 +2006,28 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
         }
     } else if (HD == 64 && early_scores_mode() == 2) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 2 : 0>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
         }
     } else if (HD == 64 && early_scores_mode() == 1) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 1 : 0>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
         }
     } else {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);
         if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma);
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
         }
     }
     if (e != cudaSuccess) {
