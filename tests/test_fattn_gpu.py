@@ -82,6 +82,40 @@ def test_cfg1_whisper_strided_padded_views(b200, orc, kernel):
     assert_close(got, ref, "cfg1 whisper-strided, Lk 1536 with 36 zero rows")
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("form", ["plain", "causal", "q_len", "mask"])
+def test_prefill_f16_query_views(b200, orc, hd, form):
+    """F16 query rows of one head per tile take the tensor-copy path in and out of the tcgen05 kernel: token-major
+    strided Q views (nb1 = H * hd * 2), two batch entries, a last query tile of 44 rows (Q rows beyond Tq read as
+    zeros, output rows beyond Tq are clipped), ragged q_len (rows at or beyond it are written as zeros), the causal
+    tile order, an explicit mask."""
+    rng = np.random.default_rng(4100 + hd)
+    B, T, H = 2, 300, 3
+    qbuf = randn_f16(rng, (B, T, H, hd))
+    kbuf, vbuf = randn_f16(rng, (B, T, H, hd)), randn_f16(rng, (B, T, H, hd))
+    qv, kv, vv = (x.transpose(0, 2, 1, 3) for x in (qbuf, kbuf, vbuf))     # (B, H, T, hd) strided
+    kw = dict(scale=hd ** -0.5)
+    mask = None
+    if form == "causal":
+        kw.update(causal=True, n_past=0)
+        mask_ref = np.triu(np.full((T, T), -np.inf, np.float32), 1).astype(np.float16)[None, None]
+        ref = orc.flash_attn_ext(qv, kv, vv, mask_ref, scale=kw["scale"])
+    elif form == "q_len":
+        kw.update(q_len=[T, 130], kv_len=[T, 130])
+        ref = orc.flash_attn_ext(qv, kv, vv, scale=kw["scale"], kv_len=[T, 130])
+        ref[1, 130:] = 0.0   # (B, Tq, H, hd)
+    else:
+        if form == "mask":
+            mask = np.where(rng.random((1, 1, T, T)) < 0.3, -np.inf, 0.0).astype(np.float16)
+            mask[..., 0] = 0
+        ref = orc.flash_attn_ext(qv, kv, vv, mask, **kw)
+    got = gpu_op(b200, cuda_view(qv, qbuf), cuda_view(kv, kbuf), cuda_view(vv, vbuf), mask, **kw)
+    assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5
+    if form == "q_len":
+        assert not got[1, 130:].any(), "rows at or beyond q_len must be zeros"
+    assert_close(got, ref, f"F16 strided Q views hd={hd} {form}")
+
+
 # ---- config 2: Whisper large-v3 decoder step, beam 5 ------------------------------------------------
 @pytest.mark.parametrize("L", [1, 64, 224, 448])
 def test_cfg2_decoder_self_attention_beam_cells(b200, orc, kernel, L):
