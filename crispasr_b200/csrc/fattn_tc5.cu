@@ -626,12 +626,13 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (q_tma) {
-            // F16 query rows of one head (no group packing) go straight into the operand layout: one copy instead of
-            // a pass through the softmax warps' registers, which a CTA sharing its SM with another one in its key loop
-            // executes at a few tens of clocks per instruction.  Rows at or beyond Tq read as zeros.
+            // F16 query rows go straight into the operand layout: one copy instead of a pass through the softmax warps'
+            // registers, which a CTA sharing its SM with another one in its key loop executes at a few tens of clocks
+            // per instruction.  The box is [64 columns, the gqa heads of the group, 128 / gqa tokens]: its rows land in
+            // packed order (token-major, head of the group minor).  Tokens at or beyond Tq read as zeros.
             mbar_arrive_expect_tx(bar_q_full, TILE_BYTES);
 #pragma unroll
-            for (int p = 0; p < PANELS; p++) tma_load_4d(sQ + p * kPanelBytes, &tmQ, bar_q_full, p * 64, q0, hk, b);
+            for (int p = 0; p < PANELS; p++) tma_load_4d(sQ + p * kPanelBytes, &tmQ, bar_q_full, p * 64, hk * a.gqa, q0 / a.gqa, b);
         }
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
@@ -1273,9 +1274,10 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             float* out = (row_live || row_zero) ? a.dst + (((int64_t)b * a.Tq + iq_dst) * a.H + h) * HD : nullptr;
             float* stage = reinterpret_cast<float*>(smem_gen + TILE_BYTES) + warp * 32 * HD;
             if (o_tma) {
-                // One head per tile: a warp's 32 rows x 32 columns are a box of dst [hd, H, Tq, B]; the warp parks them as
-                // 128-byte rows with the 16-byte chunks swizzled by the row (the copy's own pattern, conflict-free for
-                // the stores) and one lane hands each panel to a tensor store, which also clips the rows beyond Tq.
+                // A warp's 32 packed rows x 32 columns are a box [32 columns, gqa heads, 32 / gqa tokens] of
+                // dst [hd, H, Tq, B]; the warp parks them as 128-byte rows with the 16-byte chunks swizzled by the row (the
+                // copy's own pattern, conflict-free for the stores) and one lane hands each panel to a tensor store,
+                // which also clips the tokens beyond Tq.
 #pragma unroll
                 for (int q4 = 0; q4 < HD / 32; q4++) {
                     uint32_t oreg[32];
@@ -1290,10 +1292,10 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                 }
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0 && q0 + warp * 32 < a.Tq) {
+                if (lane == 0 && q0 + warp * 32 < rows_total) {
 #pragma unroll
                     for (int q4 = 0; q4 < HD / 32; q4++)
-                        tma_store_4d(&tmO, smem_u32(stage + q4 * 32 * 32), q4 * 32, hk, q0 + warp * 32, b);
+                        tma_store_4d(&tmO, smem_u32(stage + q4 * 32 * 32), q4 * 32, hk * a.gqa, (q0 + warp * 32) / a.gqa, b);
                     tma_store_commit_and_wait_read();
                 }
             } else {
@@ -1789,13 +1791,28 @@ bool encode_kv_map(CUtensorMap* m, const View& v, int hd, int Lk, int Hkv, int B
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// dst as a rank-4 F32 tensor [hd, H, Tq, B] (contiguous); box = 32 columns x one head x 32 query rows.
+// Q as a rank-4 F16 tensor [hd, H, Tq, B] (head stride nb2, token stride nb1); box = 64 columns x the gqa heads of a
+// group x 128 / gqa tokens: the rows of a box are the packed rows of a query tile.
+bool encode_q_map(CUtensorMap* m, const FattnArgs& a) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.hd, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)a.q.nb2, (cuuint64_t)a.q.nb1, (cuuint64_t)a.q.nb3};
+    const cuuint32_t box[4] = {64, (cuuint32_t)a.gqa, (cuuint32_t)(kTile / a.gqa), 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<uint8_t*>(a.q.p), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// dst as a rank-4 F32 tensor [hd, H, Tq, B] (contiguous); box = 32 columns x gqa heads x 32 / gqa tokens: a warp's
+// 32 packed rows.
 bool encode_o_map(CUtensorMap* m, const FattnArgs& a) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)a.hd, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
     const cuuint64_t strides[3] = {(cuuint64_t)a.hd * 4, (cuuint64_t)a.hd * 4 * a.H, (cuuint64_t)a.hd * 4 * a.H * a.Tq};
-    const cuuint32_t box[4] = {32, 1, 32, 1};
+    const cuuint32_t box[4] = {32, (cuuint32_t)a.gqa, (cuuint32_t)(32 / a.gqa), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -1981,24 +1998,25 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     }
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
     const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 56 + 8;
-    // F16 query rows of one head per tile, 16-byte aligned: the Q tile is one tensor copy (B200_PREFILL_QTMA=0: through registers)
+    // F16 query rows, 16-byte aligned: the Q tile is one tensor copy (B200_PREFILL_QTMA=0: through registers)
     static const bool q_tma_on = [] {
         const char* e = getenv("B200_PREFILL_QTMA");
         return !(e && e[0] == '0');
     }();
     CUtensorMap tmQ = tmK;
     int q_tma = 0;
-    if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && a.gqa == 1 && !a.bias_u && early_scores_mode() != 2 &&
+    const bool gqa_box = a.gqa >= 1 && a.gqa <= 32 && 32 % a.gqa == 0;   // a warp's 32 packed rows are whole tokens
+    if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && gqa_box && !a.bias_u && early_scores_mode() != 2 &&
         a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
-        q_tma = encode_kv_map(&tmQ, a.q, a.hd, a.Tq, a.H, a.B) ? 1 : 0;
-    // one head per tile: a warp's rows of the output are a box of dst, written by tensor stores (B200_PREFILL_OTMA=0: by the threads)
+        q_tma = encode_q_map(&tmQ, a) ? 1 : 0;
+    // a warp's rows of the output are a box of dst, written by tensor stores (B200_PREFILL_OTMA=0: by the threads)
     static const bool o_tma_on = [] {
         const char* e = getenv("B200_PREFILL_OTMA");
         return !(e && e[0] == '0');
     }();
     CUtensorMap tmO = tmK;
     int o_tma = 0;
-    if (o_tma_on && a.gqa == 1 && (uintptr_t)a.dst % 16 == 0) o_tma = encode_o_map(&tmO, a) ? 1 : 0;
+    if (o_tma_on && gqa_box && (uintptr_t)a.dst % 16 == 0) o_tma = encode_o_map(&tmO, a) ? 1 : 0;
     cudaError_t e;
     dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
     if (a.has_mask) {

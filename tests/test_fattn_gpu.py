@@ -83,16 +83,18 @@ def test_cfg1_whisper_strided_padded_views(b200, orc, kernel):
 
 
 @pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("gqa", [1, 2, 4])
 @pytest.mark.parametrize("form", ["plain", "causal", "q_len", "mask"])
-def test_prefill_f16_query_views(b200, orc, hd, form):
-    """F16 query rows of one head per tile take the tensor-copy path in and out of the tcgen05 kernel: token-major
-    strided Q views (nb1 = H * hd * 2), two batch entries, a last query tile of 44 rows (Q rows beyond Tq read as
-    zeros, output rows beyond Tq are clipped), ragged q_len (rows at or beyond it are written as zeros), the causal
-    tile order, an explicit mask."""
-    rng = np.random.default_rng(4100 + hd)
-    B, T, H = 2, 300, 3
+def test_prefill_f16_query_views(b200, orc, hd, gqa, form):
+    """F16 query rows take the tensor-copy path in and out of the tcgen05 kernel, as boxes of [columns, heads of the
+    group, tokens]: token-major strided Q views (nb1 = H * hd * 2), one to four heads per KV head, two batch entries,
+    a last query tile that ends inside the box (Q rows beyond Tq read as zeros, output rows beyond Tq are clipped),
+    ragged q_len (rows at or beyond it are written as zeros), the causal tile order, an explicit mask."""
+    rng = np.random.default_rng(4100 + hd + gqa)
+    B, T, H = 2, 300, 4
+    Hkv = H // gqa
     qbuf = randn_f16(rng, (B, T, H, hd))
-    kbuf, vbuf = randn_f16(rng, (B, T, H, hd)), randn_f16(rng, (B, T, H, hd))
+    kbuf, vbuf = randn_f16(rng, (B, T, Hkv, hd)), randn_f16(rng, (B, T, Hkv, hd))
     qv, kv, vv = (x.transpose(0, 2, 1, 3) for x in (qbuf, kbuf, vbuf))     # (B, H, T, hd) strided
     kw = dict(scale=hd ** -0.5)
     mask = None
@@ -113,7 +115,7 @@ def test_prefill_f16_query_views(b200, orc, hd, form):
     assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5
     if form == "q_len":
         assert not got[1, 130:].any(), "rows at or beyond q_len must be zeros"
-    assert_close(got, ref, f"F16 strided Q views hd={hd} {form}")
+    assert_close(got, ref, f"F16 strided Q views hd={hd} gqa={gqa} {form}")
 
 
 # ---- config 2: Whisper large-v3 decoder step, beam 5 ------------------------------------------------
