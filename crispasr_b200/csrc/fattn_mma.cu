@@ -1438,12 +1438,14 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
     auto issue = [&](int tile) { issue_lanes(tile, 1); };
     issue_lanes(tile_lo, NS);
     Q8T_TRACE(2);
-    // Q rows (tiny): one 8-element chunk per loop step; rows >= R are zero
-    for (int idx = tid; idx < kDecRows * (HD / 8); idx += kThreads) {
-        const int rr = idx / (HD / 8), ch = idx % (HD / 8);
+    // Q rows (tiny): the eight rows this kernel has, one 8-element chunk per thread; rows >= R are zero.  A single
+    // new token per stream (the usual decode step) needs no division by the group size.
+    static_assert(8 * (HD / 8) <= kThreads, "one chunk per thread");
+    if (tid < 8 * (HD / 8)) {
+        const int rr = tid / (HD / 8), ch = tid % (HD / 8);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (rr < R) {
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            const int iq = a.Tq == 1 ? 0 : rr / a.gqa, hq = hk * a.gqa + (a.Tq == 1 ? rr : rr % a.gqa);
             val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
                                 a.q.type, ch * 8, a.hd, a.q.vec16);
         }
