@@ -612,6 +612,15 @@ __device__ __forceinline__ void cluster_announce(const FattnArgs& a) {
     if (a.n_splits > 1 && a.cluster_merge) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
 
+// Row rr of a KV head's packed query rows is (query position iq, head hq) with rr = iq * gqa + (hq - hk * gqa).  One
+// query head per KV head, or one new token per step, need no division - and a decode CTA runs this code once, at
+// instruction-fetch pace.
+__device__ __forceinline__ void row_to_query(const FattnArgs& a, int hk, int rr, int& iq, int& hq) {
+    if (a.gqa == 1) iq = rr, hq = hk;
+    else if (a.Tq == 1) iq = 0, hq = hk * a.gqa + rr;
+    else iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+}
+
 // Receive area of the merge inside a cluster: shared memory of its own behind a kernel's stages (a peer may push while
 // this CTA is still in its key loop): [n_splits][slots] 16-byte column groups this CTA owns (rows * hd / 4 of them over the
 // cluster, rounded up per split), then [8][16] (M, L).
@@ -662,7 +671,8 @@ __device__ __forceinline__ void decode_write_out(const FattnArgs& a, const float
             v.z = (w0 * x0.z + w1 * x1.z) + (w2 * x2.z + w3 * x3.z), v.w = (w0 * x0.w + w1 * x1.w) + (w2 * x2.w + w3 * x3.w);
         }
         if (a.n_splits == 1) {
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            int iq, hq;
+            row_to_query(a, hk, rr, iq, hq);
             const float inv = (L > 0.0f && iq < tq_b) ? 1.0f / L : 0.0f;
             float* drow = a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd;
             if (lane < G) {
@@ -711,7 +721,8 @@ __device__ __forceinline__ void decode_write_out(const FattnArgs& a, const float
                     acc.x = fmaf(w, x.x, acc.x), acc.y = fmaf(w, x.y, acc.y), acc.z = fmaf(w, x.z, acc.z), acc.w = fmaf(w, x.w, acc.w);
                 }
             }
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            int iq, hq;
+            row_to_query(a, hk, rr, iq, hq);
             const float inv = (L > 0.0f && iq < tq_b) ? 1.0f / L : 0.0f;
             *reinterpret_cast<float4*>(a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * HD + 4 * cg) =
                 make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);   // the cluster form is offered for a.hd == HD only
@@ -798,7 +809,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             }
             if (stage_mask && tid < R * 8) {
                 const int rr = tid >> 3, ch = tid & 7;
-                const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+                int iq, hq;
+                row_to_query(a, hk, rr, iq, hq);
                 const int key0 = tile * kDecBN + ch * 8;
                 const int n_logical = a.kv_index ? a.kv_index_stride : a.Lk;   // a mask row holds one value per logical key
                 const int nbytes = max(0, min(8, n_logical - key0)) * 2;          // the rest reads as 0
@@ -821,7 +833,8 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
         const int rr = idx / (HD / 8), ch = idx % (HD / 8);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (rr < R) {
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            int iq, hq;
+            row_to_query(a, hk, rr, iq, hq);
             val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
                                 a.q.type, ch * 8, a.hd, a.q.vec16);
         }
@@ -1100,7 +1113,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8reg_kernel(const F
         const int rr = idx / (HD / 8), ch = idx % (HD / 8);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (rr < R) {
-            const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+            int iq, hq;
+            row_to_query(a, hk, rr, iq, hq);
             val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
                                 a.q.type, ch * 8, a.hd, a.q.vec16);
         }
@@ -1445,7 +1459,8 @@ __global__ void __launch_bounds__(kThreads, 4) fattn_decode_q8t_kernel(const Fat
         const int rr = tid / (HD / 8), ch = tid % (HD / 8);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (rr < R) {
-            const int iq = a.Tq == 1 ? 0 : rr / a.gqa, hq = hk * a.gqa + (a.Tq == 1 ? rr : rr % a.gqa);
+            int iq, hq;
+            row_to_query(a, hk, rr, iq, hq);
             val = load8_as_half(a.q.p + (int64_t)iq * a.q.nb1 + (int64_t)hq * a.q.nb2 + (int64_t)b * a.q.nb3,
                                 a.q.type, ch * 8, a.hd, a.q.vec16);
         }
@@ -1793,7 +1808,8 @@ __global__ void __launch_bounds__(kThreads) fattn_merge_kernel(const FattnArgs a
             for (int i = 0; i < HD / 32; i++) acc[i] += w * po[u][i];
         }
     }
-    const int iq = rr / a.gqa, hq = hk * a.gqa + rr % a.gqa;
+    int iq, hq;
+    row_to_query(a, hk, rr, iq, hq);
     float* out = a.dst + (((int64_t)b * a.Tq + iq) * a.H + hq) * a.hd;
     const float inv = (L > 0.0f && iq < q_rows_of(a, b)) ? 1.0f / L : 0.0f;
 #pragma unroll
