@@ -785,6 +785,15 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
     const int n_tiles = (kmax + kDecBN - 1) / kDecBN;
     const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
     const int tile_lo = split * tps, tile_hi = min(n_tiles, tile_lo + tps);
+    // staged mask: the row of the mask this thread copies pieces of (the head and batch broadcasts are remainders by
+    // run-time values: computed once, not per tile)
+    const int n_logical = a.kv_index ? a.kv_index_stride : a.Lk;   // a mask row holds one value per logical key
+    const uint8_t* mask_row = nullptr;
+    if (stage_mask && tid < R * 8) {
+        int iq, hq;
+        row_to_query(a, hk, tid >> 3, iq, hq);
+        mask_row = a.mask.p + (int64_t)iq * a.mask.nb1 + (int64_t)(hq % a.mask_ne2) * a.mask.nb2 + (int64_t)(b % a.mask_ne3) * a.mask.nb3;
+    }
     int pre_rows[kDecBN * (HD / 8) / kThreads];   // gathered keys: this thread's cache rows of the next tile to be issued
     if (IDX && tile_lo < tile_hi) load_tile_index<HD>(pre_rows, index, tile_lo * kDecBN, len_b, tid);
     auto issue = [&](int tile) {
@@ -809,13 +818,9 @@ __global__ void __launch_bounds__(kThreads, MODE == kDecAsyncQ8 ? 4 : 1) fattn_d
             }
             if (stage_mask && tid < R * 8) {
                 const int rr = tid >> 3, ch = tid & 7;
-                int iq, hq;
-                row_to_query(a, hk, rr, iq, hq);
                 const int key0 = tile * kDecBN + ch * 8;
-                const int n_logical = a.kv_index ? a.kv_index_stride : a.Lk;   // a mask row holds one value per logical key
                 const int nbytes = max(0, min(8, n_logical - key0)) * 2;          // the rest reads as 0
-                const uint8_t* src = a.mask.p + (int64_t)iq * a.mask.nb1 + (int64_t)(hq % a.mask_ne2) * a.mask.nb2 +
-                                     (int64_t)(b % a.mask_ne3) * a.mask.nb3 + (int64_t)(nbytes ? key0 : 0) * 2;
+                const uint8_t* src = mask_row + (int64_t)(nbytes ? key0 : 0) * 2;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(sMask + ((stage * R + rr) * kDecBN + ch * 8))),
                              "l"(src), "r"(nbytes)
                              : "memory");
