@@ -559,8 +559,12 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t bar_k_full = sBar, bar_k_empty = sBar + 8 * NSTG, bar_v_full = sBar + 16 * NSTG,
                    bar_v_empty = sBar + 24 * NSTG, bar_s_full = sBar + 32 * NSTG, bar_p_ready = bar_s_full + 8,
                    bar_o_done = bar_s_full + 16, bar_pv_done = bar_s_full + 24, bar_s_read = bar_s_full + 32,
-                   bar_s_drain = bar_s_full + 40, bar_q_full = bar_s_full + 48;
-    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 56;
+                   bar_s_drain = bar_s_full + 40, bar_q_full = bar_s_full + 48, bar_q_conv = bar_s_full + 56;
+    uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 64;
+    // q_tma: 0 = the softmax warps load and convert the Q tile; 1 = F16 rows by one tensor copy into the operand tile;
+    // 2 (head_dim 64) = F32 rows by tensor copies into the two V stages, converted from there by the softmax warps (the
+    // first V tiles are requested after the conversion; they are not needed before the first P.V product)
+    const bool q_raw = HD == 64 && NSTG == 2 && q_tma == 2;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
     constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
@@ -623,9 +627,15 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         mbar_init(bar_s_read, 4);    // one arrival per softmax warp
         mbar_init(bar_s_drain, 1);
         mbar_init(bar_q_full, 1);
+        mbar_init(bar_q_conv, 4);    // one arrival per softmax warp
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (q_tma) {
+        if (q_raw) {
+            // two panels of 128 rows x 32 floats, rows in packed order like the F16 box
+            mbar_arrive_expect_tx(bar_q_full, 2 * TILE_BYTES);
+#pragma unroll
+            for (int p = 0; p < 2; p++) tma_load_4d(sV + p * TILE_BYTES, &tmQ, bar_q_full, p * 32, hk * a.gqa, q0 / a.gqa, b);
+        } else if (q_tma) {
             // F16 query rows go straight into the operand layout: one copy instead of a pass through the softmax warps'
             // registers, which a CTA sharing its SM with another one in its key loop executes at a few tens of clocks
             // per instruction.  The box is [64 columns, the gqa heads of the group, 128 / gqa tokens]: its rows land in
@@ -642,6 +652,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
 #pragma unroll
             for (int p = 0; p < PANELS; p++)
                 tma_load_4d(sK + j * TILE_BYTES + p * kPanelBytes, &tmK, bar_k_full + 8 * j, p * 64, j * kTile, hk, bk);
+            if (q_raw) continue;   // the V stages hold the raw Q tile for now
             mbar_arrive_expect_tx(bar_v_full + 8 * j, TILE_BYTES);
 #pragma unroll
             for (int p = 0; p < PANELS; p++)
@@ -675,12 +686,44 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t tmem_S = tmem_base;            // cols [0,128)
     const uint32_t tmem_P = SEP_P ? tmem_base + kTile + HD : tmem_base;  // f16x2: cols [192,256) (hd 64) or aliasing S [0,64)
     const uint32_t tmem_O = tmem_base + kTile;    // cols [128,128+HD)
+    if constexpr (HD == 64 && NSTG == 2) {
+        if (q_raw && warp < 4) {
+            // raw F32 row r (two panels of 128-byte swizzled rows) -> F16 row r of the operand tile: 16 loads, 32
+            // conversions, 8 stores per thread, all from shared memory
+            if (mbar_wait(bar_q_full, 0, s_abort)) {
+                const int r = tid;
+                const uint8_t* raw = smem_gen + (1 + NSTG) * TILE_BYTES + r * 128;
+                uint8_t* qrow = smem_gen + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {   // F16 chunk c = columns 8c .. 8c+7 = F32 chunks 2c, 2c+1 of panel c / 4
+                    const int f0 = (2 * c) & 7;
+                    const float4 x0 = *reinterpret_cast<const float4*>(raw + (c >> 2) * TILE_BYTES + ((f0 ^ (r & 7)) << 4));
+                    const float4 x1 = *reinterpret_cast<const float4*>(raw + (c >> 2) * TILE_BYTES + (((f0 + 1) ^ (r & 7)) << 4));
+                    *reinterpret_cast<uint4*>(qrow + ((c ^ (r & 7)) << 4)) =
+                        make_uint4(pack_half2(x0.x, x0.y), pack_half2(x0.z, x0.w), pack_half2(x1.x, x1.y), pack_half2(x1.z, x1.w));
+                }
+                fence_proxy_async();   // the operand tile is read, and the V stages are overwritten, through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_q_conv);
+            }
+        }
+    }
 
     if (EARLY != 2 && warp == 4) {
         // ================= TMA producer =================
         if (lane == 0) {
             bool ok = true;
-            int issued_k = min(NSTG, n_tiles), issued_v = min(NSTG, n_tiles);
+            int issued_k = min(NSTG, n_tiles), issued_v = q_raw ? 0 : min(NSTG, n_tiles);
+            if (q_raw) {
+                ok = mbar_wait(bar_q_conv, 0, s_abort);
+                for (int j = 0; j < NSTG && j < n_tiles && ok; j++) {
+                    mbar_arrive_expect_tx(bar_v_full + 8 * j, TILE_BYTES);
+#pragma unroll
+                    for (int p = 0; p < PANELS; p++)
+                        tma_load_4d(sV + j * TILE_BYTES + p * kPanelBytes, &tmV, bar_v_full + 8 * j, p * 64, j * kTile, hk, bk);
+                    issued_v = j + 1;
+                }
+            }
             for (int j = NSTG; j < n_tiles && ok; j++) {
                 const int slot = j % NSTG, use = j / NSTG;
                 const int k0 = j * kTile;
@@ -810,7 +853,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
             const uint32_t q_lo = smem_desc_lo(sQ, 16), k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, kPanelBytes);
             constexpr uint32_t desc_hi = smem_desc_hi(1024);
             bool ok = mbar_wait(bar_k_full, 0, s_abort);
-            if (ok && q_tma) ok = mbar_wait(bar_q_full, 0, s_abort);
+            if (ok && q_tma) ok = mbar_wait(q_raw ? bar_q_conv : bar_q_full, 0, s_abort);
             if (ok) {
                 TC5_TRACE(1, 0, 0);
                 tc_fence_after();
@@ -1791,16 +1834,17 @@ bool encode_kv_map(CUtensorMap* m, const View& v, int hd, int Lk, int Hkv, int B
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Q as a rank-4 F16 tensor [hd, H, Tq, B] (head stride nb2, token stride nb1); box = 64 columns x the gqa heads of a
-// group x 128 / gqa tokens: the rows of a box are the packed rows of a query tile.
+// Q as a rank-4 F16 or F32 tensor [hd, H, Tq, B] (head stride nb2, token stride nb1); box = 128 bytes of columns x the gqa
+// heads of a group x 128 / gqa tokens: the rows of a box are the packed rows of a query tile.
 bool encode_q_map(CUtensorMap* m, const FattnArgs& a) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)a.hd, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
     const cuuint64_t strides[3] = {(cuuint64_t)a.q.nb2, (cuuint64_t)a.q.nb1, (cuuint64_t)a.q.nb3};
-    const cuuint32_t box[4] = {64, (cuuint32_t)a.gqa, (cuuint32_t)(kTile / a.gqa), 1};
+    const bool f32 = a.q.type == B200_TYPE_F32;   // 128-byte box rows either way: 64 halves or 32 floats
+    const cuuint32_t box[4] = {f32 ? 32u : 64u, (cuuint32_t)a.gqa, (cuuint32_t)(kTile / a.gqa), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<uint8_t*>(a.q.p), dims, strides, box, estr,
+    return fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<uint8_t*>(a.q.p), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1997,7 +2041,7 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
         return B200_E_CUDA;
     }
     constexpr int TILE_BYTES = kPanelBytes * (HD / 64);
-    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 56 + 8;
+    const size_t smem = 1024 + (size_t)(1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 64 + 8;
     // F16 query rows, 16-byte aligned: the Q tile is one tensor copy (B200_PREFILL_QTMA=0: through registers)
     static const bool q_tma_on = [] {
         const char* e = getenv("B200_PREFILL_QTMA");
@@ -2009,6 +2053,10 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && gqa_box && !a.bias_u && early_scores_mode() != 2 &&
         a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
         q_tma = encode_q_map(&tmQ, a) ? 1 : 0;
+    else if (q_tma_on && HD == 64 && NSTG == 2 && a.q.type == B200_TYPE_F32 && a.q.vec16 && gqa_box && !a.bias_u &&
+             early_scores_mode() == 0 && a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 &&
+             a.q.nb3 > 0)
+        q_tma = encode_q_map(&tmQ, a) ? 2 : 0;   // F32 rows: raw tile into the V stages, converted from shared memory
     // a warp's rows of the output are a box of dst, written by tensor stores (B200_PREFILL_OTMA=0: by the threads)
     static const bool o_tma_on = [] {
         const char* e = getenv("B200_PREFILL_OTMA");
