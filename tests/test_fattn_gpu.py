@@ -85,15 +85,19 @@ def test_cfg1_whisper_strided_padded_views(b200, orc, kernel):
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("gqa", [1, 2, 4])
 @pytest.mark.parametrize("form", ["plain", "causal", "q_len", "mask"])
-def test_prefill_f16_query_views(b200, orc, hd, gqa, form):
-    """F16 query rows take the tensor-copy path in and out of the tcgen05 kernel, as boxes of [columns, heads of the
-    group, tokens]: token-major strided Q views (nb1 = H * hd * 2), one to four heads per KV head, two batch entries,
+@pytest.mark.parametrize("q_f32", [False, True])
+def test_prefill_query_views(b200, orc, hd, gqa, form, q_f32):
+    """Query rows take the tensor-copy path in and out of the tcgen05 kernel, as boxes of [columns, heads of the
+    group, tokens] (F16 straight into the operand tile; F32 at head_dim 64 raw into the V stages and converted from
+    there): token-major strided Q views (nb1 = H * hd * elements), one to four heads per KV head, two batch entries,
     a last query tile that ends inside the box (Q rows beyond Tq read as zeros, output rows beyond Tq are clipped),
     ragged q_len (rows at or beyond it are written as zeros), the causal tile order, an explicit mask."""
     rng = np.random.default_rng(4100 + hd + gqa)
     B, T, H = 2, 300, 4
     Hkv = H // gqa
     qbuf = randn_f16(rng, (B, T, H, hd))
+    if q_f32:
+        qbuf = qbuf.astype(np.float32)
     kbuf, vbuf = randn_f16(rng, (B, T, Hkv, hd)), randn_f16(rng, (B, T, Hkv, hd))
     qv, kv, vv = (x.transpose(0, 2, 1, 3) for x in (qbuf, kbuf, vbuf))     # (B, H, T, hd) strided
     kw = dict(scale=hd ** -0.5)
@@ -115,7 +119,7 @@ def test_prefill_f16_query_views(b200, orc, hd, gqa, form):
     assert b200.lib().b200_last_kernel() == abi.KERNEL_PREFILL_TC5
     if form == "q_len":
         assert not got[1, 130:].any(), "rows at or beyond q_len must be zeros"
-    assert_close(got, ref, f"F16 strided Q views hd={hd} gqa={gqa} {form}")
+    assert_close(got, ref, f"strided Q views hd={hd} gqa={gqa} {form} f32={q_f32}")
 
 
 # ---- config 2: Whisper large-v3 decoder step, beam 5 ------------------------------------------------
