@@ -562,9 +562,14 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
                    bar_s_drain = bar_s_full + 40, bar_q_full = bar_s_full + 48, bar_q_conv = bar_s_full + 56;
     uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 64;
     // q_tma: 0 = the softmax warps load and convert the Q tile; 1 = F16 rows by one tensor copy into the operand tile;
-    // 2 (head_dim 64) = F32 rows by tensor copies into the two V stages, converted from there by the softmax warps (the
-    // first V tiles are requested after the conversion; they are not needed before the first P.V product)
-    const bool q_raw = HD == 64 && NSTG == 2 && q_tma == 2;
+    // 2 = F32 rows by tensor copies into stages that are not needed yet, converted from there by the softmax warps.
+    // head_dim 64: the raw tile (32 KB) takes the two V stages, whose first tiles are requested after the conversion
+    // (the first P.V product comes a tile later); head_dim 128: it takes the K and the V stage (64 KB), so the first
+    // K tile waits for the conversion too - still ahead of a register pass, whose global loads a CTA next to one in its
+    // key loop issues at a few tens of clocks per instruction.
+    constexpr bool RAW_OK = (HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1);
+    constexpr int RAW_OFF = HD == 64 ? (1 + NSTG) * TILE_BYTES : TILE_BYTES;   // V stages / K stage onwards
+    const bool q_raw = RAW_OK && q_tma == 2;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
     constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
@@ -631,10 +636,11 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (q_raw) {
-            // two panels of 128 rows x 32 floats, rows in packed order like the F16 box
-            mbar_arrive_expect_tx(bar_q_full, 2 * TILE_BYTES);
+            // HD / 32 panels of 128 rows x 32 floats, rows in packed order like the F16 box
+            mbar_arrive_expect_tx(bar_q_full, (HD / 32) * kPanelBytes);
 #pragma unroll
-            for (int p = 0; p < 2; p++) tma_load_4d(sV + p * TILE_BYTES, &tmQ, bar_q_full, p * 32, hk * a.gqa, q0 / a.gqa, b);
+            for (int p = 0; p < HD / 32; p++)
+                tma_load_4d(sQ + RAW_OFF + p * kPanelBytes, &tmQ, bar_q_full, p * 32, hk * a.gqa, q0 / a.gqa, b);
         } else if (q_tma) {
             // F16 query rows go straight into the operand layout: one copy instead of a pass through the softmax warps'
             // registers, which a CTA sharing its SM with another one in its key loop executes at a few tens of clocks
@@ -648,6 +654,7 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
         // the first NSTG tiles need no empty-slot wait: start their copies before the CTA-wide set-up barrier
         for (int j = 0; j < NSTG && j < n_tiles; j++) {
+            if (q_raw && HD == 128) continue;   // the K stage holds raw Q rows for now
             mbar_arrive_expect_tx(bar_k_full + 8 * j, TILE_BYTES);
 #pragma unroll
             for (int p = 0; p < PANELS; p++)
@@ -686,20 +693,20 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     const uint32_t tmem_S = tmem_base;            // cols [0,128)
     const uint32_t tmem_P = SEP_P ? tmem_base + kTile + HD : tmem_base;  // f16x2: cols [192,256) (hd 64) or aliasing S [0,64)
     const uint32_t tmem_O = tmem_base + kTile;    // cols [128,128+HD)
-    if constexpr (HD == 64 && NSTG == 2) {
+    if constexpr (RAW_OK) {
         if (q_raw && warp < 4) {
-            // raw F32 row r (two panels of 128-byte swizzled rows) -> F16 row r of the operand tile: 16 loads, 32
-            // conversions, 8 stores per thread, all from shared memory
+            // raw F32 row r (panels of 128-byte swizzled rows) -> F16 row r of the operand tile: HD / 4 loads, HD / 2
+            // conversions, HD / 8 stores per thread, all from shared memory
             if (mbar_wait(bar_q_full, 0, s_abort)) {
                 const int r = tid;
-                const uint8_t* raw = smem_gen + (1 + NSTG) * TILE_BYTES + r * 128;
+                const uint8_t* raw = smem_gen + RAW_OFF + r * 128;
                 uint8_t* qrow = smem_gen + r * 128;
 #pragma unroll
-                for (int c = 0; c < 8; c++) {   // F16 chunk c = columns 8c .. 8c+7 = F32 chunks 2c, 2c+1 of panel c / 4
+                for (int c = 0; c < HD / 8; c++) {   // F16 chunk c = columns 8c .. 8c+7 = F32 chunks 2c, 2c+1 of raw panel c / 4
                     const int f0 = (2 * c) & 7;
-                    const float4 x0 = *reinterpret_cast<const float4*>(raw + (c >> 2) * TILE_BYTES + ((f0 ^ (r & 7)) << 4));
-                    const float4 x1 = *reinterpret_cast<const float4*>(raw + (c >> 2) * TILE_BYTES + (((f0 + 1) ^ (r & 7)) << 4));
-                    *reinterpret_cast<uint4*>(qrow + ((c ^ (r & 7)) << 4)) =
+                    const float4 x0 = *reinterpret_cast<const float4*>(raw + (c >> 2) * kPanelBytes + ((f0 ^ (r & 7)) << 4));
+                    const float4 x1 = *reinterpret_cast<const float4*>(raw + (c >> 2) * kPanelBytes + (((f0 + 1) ^ (r & 7)) << 4));
+                    *reinterpret_cast<uint4*>(qrow + (c >> 3) * kPanelBytes + (((c & 7) ^ (r & 7)) << 4)) =
                         make_uint4(pack_half2(x0.x, x0.y), pack_half2(x0.z, x0.w), pack_half2(x1.x, x1.y), pack_half2(x1.z, x1.w));
                 }
                 fence_proxy_async();   // the operand tile is read, and the V stages are overwritten, through the async proxy
@@ -713,10 +720,17 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
         // ================= TMA producer =================
         if (lane == 0) {
             bool ok = true;
-            int issued_k = min(NSTG, n_tiles), issued_v = q_raw ? 0 : min(NSTG, n_tiles);
+            int issued_k = (q_raw && HD == 128) ? 0 : min(NSTG, n_tiles), issued_v = q_raw ? 0 : min(NSTG, n_tiles);
             if (q_raw) {
                 ok = mbar_wait(bar_q_conv, 0, s_abort);
                 for (int j = 0; j < NSTG && j < n_tiles && ok; j++) {
+                    if (HD == 128) {
+                        mbar_arrive_expect_tx(bar_k_full + 8 * j, TILE_BYTES);
+#pragma unroll
+                        for (int p = 0; p < PANELS; p++)
+                            tma_load_4d(sK + j * TILE_BYTES + p * kPanelBytes, &tmK, bar_k_full + 8 * j, p * 64, j * kTile, hk, bk);
+                        issued_k = j + 1;
+                    }
                     mbar_arrive_expect_tx(bar_v_full + 8 * j, TILE_BYTES);
 #pragma unroll
                     for (int p = 0; p < PANELS; p++)
@@ -2053,10 +2067,10 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && gqa_box && !a.bias_u && early_scores_mode() != 2 &&
         a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
         q_tma = encode_q_map(&tmQ, a) ? 1 : 0;
-    else if (q_tma_on && HD == 64 && NSTG == 2 && a.q.type == B200_TYPE_F32 && a.q.vec16 && gqa_box && !a.bias_u &&
+    else if (q_tma_on && ((HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1)) && a.q.type == B200_TYPE_F32 && a.q.vec16 && gqa_box && !a.bias_u &&
              early_scores_mode() == 0 && a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 &&
              a.q.nb3 > 0)
-        q_tma = encode_q_map(&tmQ, a) ? 2 : 0;   // F32 rows: raw tile into the V stages, converted from shared memory
+        q_tma = encode_q_map(&tmQ, a) ? 2 : 0;   // F32 rows: raw tile into stages not needed yet, converted from shared memory
     // a warp's rows of the output are a box of dst, written by tensor stores (B200_PREFILL_OTMA=0: by the threads)
     static const bool o_tma_on = [] {
         const char* e = getenv("B200_PREFILL_OTMA");
