@@ -539,7 +539,7 @@ __device__ __forceinline__ void store_o_rows_coalesced(float* stage, int lane, f
 //      that outgrew the reference maximum is redone from registers and the other half's probabilities are scaled.
 //      The score MMAs and the P.V MMAs are issued from two warps on two schedulers, each refilling the K (V) slots
 //      its own MMAs free.  Tile period of a traced CTA about equal to EARLY = 0; whole launches 0.79x.
-template <int HD, int NSTG, bool HASMASK, int EARLY = 0>
+template <int HD, int NSTG, bool HASMASK, int EARLY = 0, bool QRAW = false>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQ, const int q_tma,
@@ -563,13 +563,16 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     uint8_t* misc = smem_gen + (1 + 2 * NSTG) * TILE_BYTES + 32 * NSTG + 64;
     // q_tma: 0 = the softmax warps load and convert the Q tile; 1 = F16 rows by one tensor copy into the operand tile;
     // 2 = F32 rows by tensor copies into stages that are not needed yet, converted from there by the softmax warps.
-    // head_dim 64: the raw tile (32 KB) takes the two V stages, whose first tiles are requested after the conversion
-    // (the first P.V product comes a tile later); head_dim 128: it takes the K and the V stage (64 KB), so the first
-    // K tile waits for the conversion too - still ahead of a register pass, whose global loads a CTA next to one in its
-    // key loop issues at a few tens of clocks per instruction.
-    constexpr bool RAW_OK = (HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1);
+    // head_dim 128 (the form that is launched): the raw tile (64 KB) takes the K and the V stage, so the first K tile
+    // waits for the conversion too - still ahead of a register pass, whose global loads a CTA next to one in its key
+    // loop issues at a few tens of clocks per instruction (T = 407 GQA prefill with an F32 Q: 4807 -> 5034 streams/s).
+    // head_dim 64 (the raw tile in the two V stages) measured 1459 against 1481 segments/s for the register pass on the
+    // encoder and is not launched.
+    // The raw form is an instantiation of its own (QRAW, launched with q_tma == 2): compiled into the common kernel it
+    // cost the F16-Q launches 5 % on the encoder and 9 % on the T = 407 prefill.
+    constexpr bool RAW_OK = QRAW && EARLY == 0 && ((HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1));
     constexpr int RAW_OFF = HD == 64 ? (1 + NSTG) * TILE_BYTES : TILE_BYTES;   // V stages / K stage onwards
-    const bool q_raw = RAW_OK && q_tma == 2;
+    constexpr bool q_raw = RAW_OK;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
     constexpr bool SEP_P = (HD == 64);
     volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(misc);
@@ -2061,13 +2064,14 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
         const char* e = getenv("B200_PREFILL_QTMA");
         return !(e && e[0] == '0');
     }();
+    constexpr bool RAW_INST = HD == 128 && NSTG == 1;   // the raw F32 form exists (and pays) at head_dim 128 only
     CUtensorMap tmQ = tmK;
     int q_tma = 0;
     const bool gqa_box = a.gqa >= 1 && a.gqa <= 32 && 32 % a.gqa == 0;   // a warp's 32 packed rows are whole tokens
     if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && gqa_box && !a.bias_u && early_scores_mode() != 2 &&
         a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
         q_tma = encode_q_map(&tmQ, a) ? 1 : 0;
-    else if (q_tma_on && ((HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1)) && a.q.type == B200_TYPE_F32 && a.q.vec16 && gqa_box && !a.bias_u &&
+    else if (q_tma_on && RAW_INST && a.q.type == B200_TYPE_F32 && a.q.vec16 && gqa_box && !a.bias_u &&
              early_scores_mode() == 0 && a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 &&
              a.q.nb3 > 0)
         q_tma = encode_q_map(&tmQ, a) ? 2 : 0;   // F32 rows: raw tile into stages not needed yet, converted from shared memory
@@ -2081,7 +2085,21 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     if (o_tma_on && gqa_box && (uintptr_t)a.dst % 16 == 0) o_tma = encode_o_map(&tmO, a) ? 1 : 0;
     cudaError_t e;
     dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
-    if (a.has_mask) {
+    if (q_tma == 2 && a.has_mask) {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true, 0, RAW_INST>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
+        }
+    } else if (q_tma == 2) {
+        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, 0, RAW_INST>;
+        static bool smem_set[64] = {false};
+        e = set_smem_once(kern, smem, smem_set);
+        if (e == cudaSuccess) {
+            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
+        }
+    } else if (a.has_mask) {
         auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true>;
         static bool smem_set[64] = {false};
         e = set_smem_once(kern, smem, smem_set);

@@ -88,8 +88,8 @@ def test_cfg1_whisper_strided_padded_views(b200, orc, kernel):
 @pytest.mark.parametrize("q_f32", [False, True])
 def test_prefill_query_views(b200, orc, hd, gqa, form, q_f32):
     """Query rows take the tensor-copy path in and out of the tcgen05 kernel, as boxes of [columns, heads of the
-    group, tokens] (F16 straight into the operand tile; F32 at head_dim 64 raw into the V stages and converted from
-    there): token-major strided Q views (nb1 = H * hd * elements), one to four heads per KV head, two batch entries,
+    group, tokens] (F16 straight into the operand tile; F32 at head_dim 128 raw into the K and V stages and converted
+    from there, at head_dim 64 through registers): token-major strided Q views (nb1 = H * hd * elements), one to four heads per KV head, two batch entries,
     a last query tile that ends inside the box (Q rows beyond Tq read as zeros, output rows beyond Tq are clipped),
     ragged q_len (rows at or beyond it are written as zeros), the causal tile order, an explicit mask."""
     rng = np.random.default_rng(4100 + hd + gqa)
