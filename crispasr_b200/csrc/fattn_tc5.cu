@@ -539,11 +539,16 @@ __device__ __forceinline__ void store_o_rows_coalesced(float* stage, int lane, f
 //      that outgrew the reference maximum is redone from registers and the other half's probabilities are scaled.
 //      The score MMAs and the P.V MMAs are issued from two warps on two schedulers, each refilling the K (V) slots
 //      its own MMAs free.  Tile period of a traced CTA about equal to EARLY = 0; whole launches 0.79x.
-template <int HD, int NSTG, bool HASMASK, int EARLY = 0, bool QRAW = false>
+// QMODE / OTMA: how the query tile comes in and the output tile goes out (see q_tma below).  Template parameters, not
+// run-time flags: every path compiled into one kernel costs the others (the raw F32 form behind a flag took 5 % off the
+// F16-Q encoder launches and 9 % off the T = 407 prefill).
+template <int HD, int NSTG, bool HASMASK, int EARLY = 0, int QMODE = 0, bool OTMA = false>
 __global__ void __launch_bounds__(kThreadsTc5, 2)
 fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQ, const int q_tma,
-                         const __grid_constant__ CUtensorMap tmO, const int o_tma) {
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQ,
+                         const __grid_constant__ CUtensorMap tmO) {
+    constexpr int q_tma = QMODE;
+    constexpr bool o_tma = OTMA;
     constexpr int PANELS = HD / 64;
     constexpr int TILE_BYTES = kPanelBytes * PANELS;
     constexpr uint32_t IDESC_S = idesc_f16(kTile, false);
@@ -568,9 +573,8 @@ fattn_prefill_tc5_kernel(const FattnArgs a, const __grid_constant__ CUtensorMap 
     // loop issues at a few tens of clocks per instruction (T = 407 GQA prefill with an F32 Q: 4807 -> 5034 streams/s).
     // head_dim 64 (the raw tile in the two V stages) measured 1459 against 1481 segments/s for the register pass on the
     // encoder and is not launched.
-    // The raw form is an instantiation of its own (QRAW, launched with q_tma == 2): compiled into the common kernel it
-    // cost the F16-Q launches 5 % on the encoder and 9 % on the T = 407 prefill.
-    constexpr bool RAW_OK = QRAW && EARLY == 0 && ((HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1));
+    constexpr bool RAW_OK = QMODE == 2 && EARLY == 0 && ((HD == 64 && NSTG == 2) || (HD == 128 && NSTG == 1));
+    static_assert(QMODE != 2 || RAW_OK, "the raw form needs stages to park the tile in");
     constexpr int RAW_OFF = HD == 64 ? (1 + NSTG) * TILE_BYTES : TILE_BYTES;   // V stages / K stage onwards
     constexpr bool q_raw = RAW_OK;
     // head_dim 64 leaves 64 spare TMEM columns: P gets its own, so S of the next tile can be issued before P.V
@@ -2049,6 +2053,15 @@ int early_scores_mode() {
     return mode;
 }
 
+// One instantiation per kernel: its own "shared-memory attribute raised" flags per device.
+template <auto Kern, typename... Args>
+cudaError_t launch_inst(dim3 grid, size_t smem, cudaStream_t st, Args... args) {
+    static bool smem_set[64] = {false};
+    cudaError_t e = set_smem_once(Kern, smem, smem_set);
+    if (e == cudaSuccess) e = launch_pdl(Kern, grid, kThreadsTc5, smem, st, args...);
+    return e;
+}
+
 template <int HD, int NSTG>
 int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen) {
     const FattnArgs& a = a_in;
@@ -2068,7 +2081,8 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     CUtensorMap tmQ = tmK;
     int q_tma = 0;
     const bool gqa_box = a.gqa >= 1 && a.gqa <= 32 && 32 % a.gqa == 0;   // a warp's 32 packed rows are whole tokens
-    if (q_tma_on && a.q.type == B200_TYPE_F16 && a.q.vec16 && gqa_box && !a.bias_u && early_scores_mode() != 2 &&
+    const bool early = HD == 64 && !a.has_mask && early_scores_mode() != 0;   // the A/B variants move their tiles through the threads
+    if (q_tma_on && !early && a.q.type == B200_TYPE_F16 && a.q.vec16 && gqa_box && !a.bias_u &&
         a.q.nb1 % 16 == 0 && a.q.nb2 % 16 == 0 && a.q.nb3 % 16 == 0 && a.q.nb1 > 0 && a.q.nb2 > 0 && a.q.nb3 > 0)
         q_tma = encode_q_map(&tmQ, a) ? 1 : 0;
     else if (q_tma_on && RAW_INST && a.q.type == B200_TYPE_F32 && a.q.vec16 && gqa_box && !a.bias_u &&
@@ -2082,52 +2096,28 @@ int launch_t(const FattnArgs& a_in, cudaStream_t st, char* errbuf, size_t errlen
     }();
     CUtensorMap tmO = tmK;
     int o_tma = 0;
-    if (o_tma_on && gqa_box && (uintptr_t)a.dst % 16 == 0) o_tma = encode_o_map(&tmO, a) ? 1 : 0;
+    if (o_tma_on && !early && gqa_box && (uintptr_t)a.dst % 16 == 0) o_tma = encode_o_map(&tmO, a) ? 1 : 0;
     cudaError_t e;
     dim3 grid((a.Tq * a.gqa + kTile - 1) / kTile, a.Hkv, a.B);   // packed (query, group head) rows per KV head
-    if (q_tma == 2 && a.has_mask) {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true, 0, RAW_INST>;
-        static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
-        if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
-        }
-    } else if (q_tma == 2) {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, 0, RAW_INST>;
-        static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
-        if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
-        }
+    // launch_inst is instantiated per kernel (the kernels share one function-pointer type, so a generic lambda would
+    // share its "attribute set" flags between them)
+    auto args = [&](auto launch) { e = launch(grid, smem, st, a, tmK, tmV, tmQ, tmO); };
+    constexpr int QRAW = RAW_INST ? 2 : 0;
+#define B200_GO(...) args(launch_inst<fattn_prefill_tc5_kernel<__VA_ARGS__>, FattnArgs, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap>)
+    if (HD == 64 && !a.has_mask && early_scores_mode() == 2) {
+        B200_GO(HD, NSTG, false, HD == 64 ? 2 : 0);
+    } else if (HD == 64 && !a.has_mask && early_scores_mode() == 1) {
+        B200_GO(HD, NSTG, false, HD == 64 ? 1 : 0);
     } else if (a.has_mask) {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, true>;
-        static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
-        if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
-        }
-    } else if (HD == 64 && early_scores_mode() == 2) {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 2 : 0>;
-        static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
-        if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
-        }
-    } else if (HD == 64 && early_scores_mode() == 1) {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false, HD == 64 ? 1 : 0>;
-        static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
-        if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
-        }
+        if (q_tma == 2) { if (o_tma) B200_GO(HD, NSTG, true, 0, QRAW, true); else B200_GO(HD, NSTG, true, 0, QRAW, false); }
+        else if (q_tma == 1) { if (o_tma) B200_GO(HD, NSTG, true, 0, 1, true); else B200_GO(HD, NSTG, true, 0, 1, false); }
+        else { if (o_tma) B200_GO(HD, NSTG, true, 0, 0, true); else B200_GO(HD, NSTG, true, 0, 0, false); }
     } else {
-        auto kern = fattn_prefill_tc5_kernel<HD, NSTG, false>;
-        static bool smem_set[64] = {false};
-        e = set_smem_once(kern, smem, smem_set);
-        if (e == cudaSuccess) {
-            e = launch_pdl(kern, grid, kThreadsTc5, smem, st, a, tmK, tmV, tmQ, q_tma, tmO, o_tma);
-        }
+        if (q_tma == 2) { if (o_tma) B200_GO(HD, NSTG, false, 0, QRAW, true); else B200_GO(HD, NSTG, false, 0, QRAW, false); }
+        else if (q_tma == 1) { if (o_tma) B200_GO(HD, NSTG, false, 0, 1, true); else B200_GO(HD, NSTG, false, 0, 1, false); }
+        else { if (o_tma) B200_GO(HD, NSTG, false, 0, 0, true); else B200_GO(HD, NSTG, false, 0, 0, false); }
     }
+#undef B200_GO
     if (e != cudaSuccess) {
         snprintf(errbuf, errlen, "tcgen05 prefill launch: %s", cudaGetErrorString(e));
         return B200_E_CUDA;
